@@ -1,0 +1,28 @@
+"""asymgemm_b200: B200 (sm_100a) implementation of AsymGEMM's m-grouped asymmetric MoE GEMM.
+
+Exports the operator names of the reference package (asym_gemm/__init__.py:37-96) for this path.
+Importing the package does not touch the GPU; the first operator call loads ``libasymgemm_b200.so`` and
+raises if it has not been built.
+"""
+from .api import (  # noqa: F401
+    check_status,
+    get_mk_alignment_for_contiguous_layout,
+    get_num_sms,
+    m_grouped_bf16_asym_gemm_nt_contiguous,
+    m_grouped_bf16_asym_gemm_nt_masked,
+    m_grouped_fp8_asym_gemm_nt_contiguous,
+    m_grouped_fp8_asym_gemm_nt_masked,
+    m_grouped_int8_asym_gemm_nt_contiguous,
+    m_grouped_int8_asym_gemm_nt_masked,
+    set_num_sms,
+    set_use_scratch,
+    set_wait_limit_ms,
+)
+from . import testing, utils  # noqa: F401
+
+__version__ = "0.1.0"
+
+
+def init(*_args, **_kwargs) -> None:
+    """Kept for drop-in compatibility: the reference initialises its JIT here (csrc/apis/runtime.hpp:44-47)."""
+    return None

@@ -1,0 +1,125 @@
+"""ctypes binding of the C ABI declared in ``include/asymgemm_b200.h``.
+
+There is no CPU or eager fallback: if the shared library is missing, loading fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int32, c_int64, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libasymgemm_b200.so"
+
+AG_OK = 0
+AG_E_INVALID = -1
+AG_E_UNSUPPORTED = -2
+AG_E_CUDA = -3
+AG_E_NOT_MAPPED = -4
+AG_E_DEVICE = -5
+
+LAYOUT_CONTIGUOUS = 0
+LAYOUT_MASKED = 1
+D_BF16 = 0
+D_FP32 = 1
+
+KIND_BF16, KIND_FP8, KIND_INT8, KIND_NVFP4 = 0, 1, 2, 3
+
+
+class GemmDesc(Structure):
+    """Mirror of ``ag_gemm_desc_t``."""
+
+    _fields_ = [
+        ("layout", c_int32),
+        ("d_dtype", c_int32),
+        ("a", c_void_p),
+        ("sfa", c_void_p),
+        ("b", c_void_p),
+        ("sfb", c_void_p),
+        ("d", c_void_p),
+        ("offsets", c_void_p),
+        ("experts", c_void_p),
+        ("max_segments", c_int32),
+        ("masked_m", c_void_p),
+        ("m", c_int64),
+        ("n", c_int64),
+        ("k", c_int64),
+        ("num_groups", c_int32),
+        ("scratch", c_void_p),
+        ("scratch_bytes", c_uint64),
+        ("status", c_void_p),
+        ("stream", c_void_p),
+        ("num_sms", c_int32),
+        ("timeout_ms", c_uint32),
+        ("raw_dump", c_void_p),
+        ("alpha", c_float),
+    ]
+
+
+EXPORTS = [
+    "ag_m_grouped_bf16_gemm_nt",
+    "ag_m_grouped_fp8_gemm_nt",
+    "ag_m_grouped_int8_gemm_nt",
+    "ag_m_grouped_fp4_gemm_nt",
+    "ag_scratch_bytes",
+    "ag_read_status",
+    "ag_set_num_sms",
+    "ag_get_num_sms",
+    "ag_get_mk_alignment_for_contiguous_layout",
+    "ag_fp4_sf_blocked_bytes",
+    "ag_fp4_sf_to_blocked",
+    "ag_measure_host_link",
+    "ag_last_error",
+    "ag_version",
+]
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m asymgemm_b200.build`. "
+            "asymgemm_b200 has no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name in ("ag_m_grouped_bf16_gemm_nt", "ag_m_grouped_fp8_gemm_nt", "ag_m_grouped_int8_gemm_nt",
+                 "ag_m_grouped_fp4_gemm_nt"):
+        fn = getattr(lib, name)
+        fn.argtypes = [POINTER(GemmDesc)]
+        fn.restype = c_int32
+    lib.ag_scratch_bytes.argtypes = [c_int32, c_int64, c_int64, c_int32]
+    lib.ag_scratch_bytes.restype = c_uint64
+    lib.ag_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
+    lib.ag_read_status.restype = c_int32
+    lib.ag_set_num_sms.argtypes = [c_int32]
+    lib.ag_set_num_sms.restype = None
+    lib.ag_get_num_sms.argtypes = []
+    lib.ag_get_num_sms.restype = c_int32
+    lib.ag_get_mk_alignment_for_contiguous_layout.argtypes = []
+    lib.ag_get_mk_alignment_for_contiguous_layout.restype = c_int32
+    lib.ag_fp4_sf_blocked_bytes.argtypes = [c_int64, c_int64, c_int64]
+    lib.ag_fp4_sf_blocked_bytes.restype = c_uint64
+    lib.ag_fp4_sf_to_blocked.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]
+    lib.ag_fp4_sf_to_blocked.restype = c_int32
+    lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]
+    lib.ag_measure_host_link.restype = c_int32
+    lib.ag_last_error.argtypes = []
+    lib.ag_last_error.restype = c_char_p
+    lib.ag_version.argtypes = []
+    lib.ag_version.restype = c_char_p
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().ag_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    """Turn a negative status into the RuntimeError the reference API raises."""
+    if rc != AG_OK:
+        raise RuntimeError(f"asymgemm_b200: {last_error()} (code {rc})")

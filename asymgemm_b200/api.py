@@ -1,0 +1,306 @@
+"""Operator API of the m-grouped asymmetric GEMM, with the reference's names, argument order and meaning.
+
+Mirrors ``asym_gemm.m_grouped_{bf16,fp8,fp4,int8}_asym_gemm_nt_{contiguous,masked}`` (pybind signatures in
+csrc/apis/gemm.hpp:1034-1115 of the reference): tensors are caller-owned, ``d`` is written in place, the
+launch is asynchronous on torch's current CUDA stream, failures raise ``RuntimeError``. Every call goes
+through the C ABI of ``libasymgemm_b200.so``; there is no PyTorch or CPU fallback.
+
+Differences from the reference, all on the permissive side:
+  * ``compiled_dims`` is accepted and ignored (kernels are compiled ahead of time).
+  * ``list_size`` may be an int or a one-element tensor; passing ``None`` avoids the device sync that
+    reading a CUDA tensor costs (the kernel stops at the -1 terminator of ``experts`` by itself).
+  * fp32 FP8 scales are applied exactly in fp32; ``disable_ue8m0_cast`` therefore changes nothing.
+  * INT8 runs on sm_100a (the reference raises there) and ``d`` may be bf16 or fp32.
+  * B that is neither CUDA nor pinned raises instead of faulting.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from ._lib import GemmDesc
+
+_MK_ALIGNMENT = 128
+_state = {"timeout_ms": 0, "use_scratch": True}
+_scratch_cache: dict = {}
+_status_cache: dict = {}
+_dev_copy_cache: dict = {}
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(f"Assertion error (asymgemm_b200): {msg}")
+
+
+def get_mk_alignment_for_contiguous_layout() -> int:
+    """Rows every contiguous-layout segment must be padded to (csrc/utils/layout.hpp:108-110)."""
+    return _MK_ALIGNMENT
+
+
+def set_num_sms(num_sms: int) -> None:
+    """Cap the CTAs each launch may use (csrc/apis/runtime.hpp:15-21)."""
+    _lib.load().ag_set_num_sms(int(num_sms))
+
+
+def get_num_sms() -> int:
+    return int(_lib.load().ag_get_num_sms())
+
+
+def set_wait_limit_ms(ms: int) -> None:
+    """Bound (milliseconds) on every in-kernel barrier wait; 0 restores the default."""
+    _state["timeout_ms"] = int(ms)
+
+
+def set_use_scratch(flag: bool) -> None:
+    """Whether long segments replay their weight column from device scratch (default) or re-read B."""
+    _state["use_scratch"] = bool(flag)
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_cache.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_cache[key] = t
+    return t
+
+
+def check_status(device: Union[torch.device, int, None] = None, reset: bool = True) -> None:
+    """Synchronise and raise ``RuntimeError`` if any kernel since the last check reported a status word."""
+    dev = torch.device("cuda", torch.cuda.current_device() if device is None else (device if isinstance(device, int) else device.index))
+    word = _status_word(dev)
+    torch.cuda.synchronize(dev)
+    v = int(word.item())
+    if v != 0:
+        lib = _lib.load()
+        out = _lib.c_int32(0)
+        lib.ag_read_status(word.data_ptr(), torch.cuda.current_stream(dev).cuda_stream, out)
+        msg = _lib.last_error()
+        if reset:
+            word.zero_()
+        raise RuntimeError(f"asymgemm_b200: {msg}")
+
+
+def _scratch(kind: int, n: int, k: int, device: torch.device) -> Optional[torch.Tensor]:
+    if not _state["use_scratch"]:
+        return None
+    lib = _lib.load()
+    need = int(lib.ag_scratch_bytes(kind, n, k, 0))
+    key = device.index
+    t = _scratch_cache.get(key)
+    if t is None or t.numel() < need + 1024:
+        t = torch.empty(need + 1024, dtype=torch.uint8, device=device)
+        _scratch_cache[key] = t
+    off = (-t.data_ptr()) % 1024
+    return t[off:off + need]
+
+
+def _device_copy(t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """Device-resident copy of a small host tensor (weight scales), cached until the source changes."""
+    if t.is_cuda:
+        return t
+    key = (t.data_ptr(), tuple(t.shape), t.dtype, device.index)
+    hit = _dev_copy_cache.get(key)
+    if hit is not None and hit[0] == t._version:
+        return hit[1]
+    dev = t.to(device, non_blocking=t.is_pinned())
+    if len(_dev_copy_cache) > 256:
+        _dev_copy_cache.clear()
+    _dev_copy_cache[key] = (t._version, dev)
+    return dev
+
+
+def _list_size_to_segments(list_size, offsets: torch.Tensor, experts: torch.Tensor) -> int:
+    cap = min(offsets.numel() // 2, experts.numel())
+    if list_size is None:
+        return cap
+    if isinstance(list_size, torch.Tensor):
+        _require(list_size.numel() == 1, "list_size tensor must have one element")
+        list_size = int(list_size.item())
+    # list_size counts the -1 terminator (tests/m_grouped/...:47-51 of the reference)
+    return max(0, min(int(list_size), cap))
+
+
+def _check_b_residency(b: torch.Tensor) -> None:
+    _require(b.is_cuda or b.is_pinned(), "b must be a CUDA tensor or pinned host memory (b.is_cuda() or b.is_pinned())")
+
+
+def _common_checks(a, b, d, masked: bool, k_div: int = 1):
+    if masked:
+        _require(a.dim() == 3 and b.dim() == 3 and d.dim() == 3, "masked layout wants a [G,M,K], b [G,N,K], d [G,M,N]")
+        g, m, k = a.shape
+        g_, n, k_ = b.shape
+        g__, m_, n_ = d.shape
+        _require(g == g_ == g__ and m == m_ and n == n_ and k == k_, "shape mismatch between a, b and d")
+    else:
+        _require(a.dim() == 2 and b.dim() == 3 and d.dim() == 2, "contiguous layout wants a [M,K], b [G,N,K], d [M,N]")
+        m, k = a.shape
+        g, n, k_ = b.shape
+        m_, n_ = d.shape
+        _require(m == m_ and n == n_ and k == k_, "shape mismatch between a, b and d")
+    _require(n > 0 and k > 0 and g > 0, "n, k and num_groups must be positive")
+    _require(a.is_cuda and d.is_cuda, "a and d must be CUDA tensors")
+    _require(a.is_contiguous(), "a must be K-major (contiguous)")
+    _require(b.is_contiguous(), "b must be K-major [G, N, K] (contiguous)")
+    _require(d.is_contiguous(), "d must be row-major (contiguous)")
+    _require(d.dtype in (torch.bfloat16, torch.float32), "d must be bfloat16 or float32")
+    _check_b_residency(b)
+    return int(g), int(m), int(n), int(k * k_div)
+
+
+def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
+            masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0) -> None:
+    lib = _lib.load()
+    dev = a.device
+    with torch.cuda.device(dev):
+        desc = GemmDesc()
+        desc.layout = layout
+        desc.d_dtype = _lib.D_FP32 if d.dtype == torch.float32 else _lib.D_BF16
+        desc.a = a.data_ptr()
+        desc.sfa = sfa.data_ptr() if sfa is not None else None
+        desc.b = b.data_ptr()
+        desc.sfb = sfb.data_ptr() if sfb is not None else None
+        desc.d = d.data_ptr()
+        desc.offsets = offsets.data_ptr() if offsets is not None else None
+        desc.experts = experts.data_ptr() if experts is not None else None
+        desc.max_segments = max_segments
+        desc.masked_m = masked_m.data_ptr() if masked_m is not None else None
+        desc.m, desc.n, desc.k, desc.num_groups = m, n, k, g
+        scratch = _scratch(kind, n, k, dev)
+        if scratch is not None:
+            desc.scratch = scratch.data_ptr()
+            desc.scratch_bytes = scratch.numel()
+        desc.status = _status_word(dev).data_ptr()
+        desc.stream = torch.cuda.current_stream(dev).cuda_stream
+        desc.num_sms = 0
+        desc.timeout_ms = _state["timeout_ms"]
+        desc.raw_dump = raw_dump.data_ptr() if raw_dump is not None else None
+        desc.alpha = alpha
+        _lib.check(getattr(lib, fn_name)(desc))
+
+
+def _check_index_tensors(offsets, experts, g):
+    _require(offsets.is_cuda and experts.is_cuda, "offsets and experts must be CUDA tensors")
+    _require(offsets.is_contiguous() and experts.is_contiguous(), "offsets and experts must be contiguous")
+    _require(offsets.dtype == torch.int32 and experts.dtype == torch.int32, "offsets and experts must be int32")
+
+
+# --------------------------------------------------------------------------------------------- BF16
+def m_grouped_bf16_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=None, compiled_dims: str = "nk",
+                                           transpose_b: bool = False) -> None:
+    """``d[rows of segment i] = a[rows] @ b[experts[i]].T`` in bf16 (csrc/apis/gemm.hpp:370-418, 679-732)."""
+    _require(not transpose_b, "transpose_b=True (MN-major B) is not supported")
+    g, m, n, k = _common_checks(a, b, d, masked=False)
+    _require(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "a and b must be bfloat16")
+    _check_index_tensors(offsets, experts, g)
+    if m == 0:
+        return
+    segs = _list_size_to_segments(list_size, offsets, experts)
+    _launch(_lib.KIND_BF16, "ag_m_grouped_bf16_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a, sfa=None, b=b, sfb=None, d=d,
+            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
+
+
+def m_grouped_bf16_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, compiled_dims: str = "nk") -> None:
+    """Masked layout: group ``g`` multiplies its first ``masked_m[g]`` rows (csrc/apis/gemm.hpp:420-486)."""
+    g, m, n, k = _common_checks(a, b, d, masked=True)
+    _require(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "a and b must be bfloat16")
+    _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
+             "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
+    if m == 0 or expected_m == 0:
+        return
+    _launch(_lib.KIND_BF16, "ag_m_grouped_bf16_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a, sfa=None, b=b, sfb=None, d=d,
+            masked_m=masked_m, m=m, n=n, k=k, g=g)
+
+
+# --------------------------------------------------------------------------------------------- FP8
+def _fp8_scales(a, b, g, rows_shape, n, k, recipe):
+    a_q, sfa = a
+    b_q, sfb = b
+    _require(a_q.dtype == torch.float8_e4m3fn and b_q.dtype == torch.float8_e4m3fn, "a and b must be float8_e4m3fn")
+    if recipe is not None:
+        _require(tuple(recipe) == (1, 128, 128), f"Unknown SF transformation for recipe {tuple(recipe)}")
+    kb = (k + 127) // 128
+    _require(sfa.dtype == torch.float32 and sfb.dtype == torch.float32, "scales must be float32")
+    _require(tuple(sfa.shape) == (*rows_shape, kb), f"sfa must be {(*rows_shape, kb)}, got {tuple(sfa.shape)}")
+    _require(tuple(sfb.shape) == (g, (n + 127) // 128, kb), f"sfb must be {(g, (n + 127) // 128, kb)}, got {tuple(sfb.shape)}")
+    _require(sfa.is_cuda, "sfa must be a CUDA tensor")
+    return sfa.contiguous(), _device_copy(sfb.contiguous(), a_q.device)
+
+
+def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor], d,
+                                          offsets, experts, list_size=None,
+                                          recipe: Optional[Tuple[int, int, int]] = None, compiled_dims: str = "nk",
+                                          disable_ue8m0_cast: bool = False) -> None:
+    """FP8 E4M3 with 1x128 (A) and 128x128 (B) fp32 scales, bf16 out (csrc/apis/gemm.hpp:81-157)."""
+    g, m, n, k = _common_checks(a[0], b[0], d, masked=False)
+    _check_index_tensors(offsets, experts, g)
+    sfa, sfb = _fp8_scales(a, b, g, (m,), n, k, recipe)
+    if m == 0:
+        return
+    segs = _list_size_to_segments(list_size, offsets, experts)
+    _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
+            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
+
+
+def m_grouped_fp8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk",
+                                      disable_ue8m0_cast: bool = False) -> None:
+    """Masked FP8 (csrc/apis/gemm.hpp:159-235)."""
+    g, m, n, k = _common_checks(a[0], b[0], d, masked=True)
+    sfa, sfb = _fp8_scales(a, b, g, (g, m), n, k, recipe)
+    _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
+             "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
+    if m == 0 or expected_m == 0:
+        return
+    _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
+            masked_m=masked_m, m=m, n=n, k=k, g=g)
+
+
+# --------------------------------------------------------------------------------------------- INT8
+def _int8_scales(a, b, g, rows_shape, n, k):
+    a_q, sfa = a
+    b_q, sfb = b
+    _require(a_q.dtype == torch.int8 and b_q.dtype == torch.int8, "a and b must be int8")
+    _require(k % 128 == 0, "k must be a multiple of 128")  # sm90_int8_asym_gemm_1d1d.hpp:226-227
+    kb = k // 128
+    _require(sfa.dtype == torch.float32 and sfb.dtype == torch.float32, "scales must be float32")
+    _require(tuple(sfa.shape) == (*rows_shape, kb), f"sfa must be {(*rows_shape, kb)}, got {tuple(sfa.shape)}")
+    _require(tuple(sfb.shape) == (g, n, kb), f"sfb must be {(g, n, kb)}, got {tuple(sfb.shape)}")
+    _require(sfa.is_cuda, "sfa must be a CUDA tensor")
+    return sfa.contiguous(), _device_copy(sfb.contiguous(), a_q.device)
+
+
+def m_grouped_int8_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=None, recipe=None,
+                                           compiled_dims: str = "nk", *, raw_accumulators: Optional[torch.Tensor] = None) -> None:
+    """INT8 with per-token (A) and per-channel (B) fp32 scales per 128-wide K block (csrc/apis/gemm.hpp:569-600).
+
+    ``raw_accumulators`` (extension): int32 CUDA tensor ``[K/128, M, N]`` that receives the exact block sums.
+    """
+    g, m, n, k = _common_checks(a[0], b[0], d, masked=False)
+    _check_index_tensors(offsets, experts, g)
+    sfa, sfb = _int8_scales(a, b, g, (m,), n, k)
+    if raw_accumulators is not None:
+        _require(raw_accumulators.is_cuda and raw_accumulators.dtype == torch.int32 and raw_accumulators.is_contiguous()
+                 and tuple(raw_accumulators.shape) == (k // 128, m, n), "raw_accumulators must be int32 [K/128, M, N] on CUDA")
+    if m == 0:
+        return
+    segs = _list_size_to_segments(list_size, offsets, experts)
+    _launch(_lib.KIND_INT8, "ag_m_grouped_int8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
+            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, raw_dump=raw_accumulators)
+
+
+def m_grouped_int8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk", *,
+                                       raw_accumulators: Optional[torch.Tensor] = None) -> None:
+    """Masked INT8 (csrc/apis/gemm.hpp:602-630)."""
+    g, m, n, k = _common_checks(a[0], b[0], d, masked=True)
+    sfa, sfb = _int8_scales(a, b, g, (g, m), n, k)
+    _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
+             "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
+    if raw_accumulators is not None:
+        _require(raw_accumulators.is_cuda and raw_accumulators.dtype == torch.int32 and raw_accumulators.is_contiguous()
+                 and tuple(raw_accumulators.shape) == (k // 128, g * m, n), "raw_accumulators must be int32 [K/128, G*M, N] on CUDA")
+    if m == 0 or expected_m == 0:
+        return
+    _launch(_lib.KIND_INT8, "ag_m_grouped_int8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
+            masked_m=masked_m, m=m, n=n, k=k, g=g, raw_dump=raw_accumulators)

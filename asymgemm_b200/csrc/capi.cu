@@ -1,0 +1,320 @@
+// C ABI over the sm_100a grouped-GEMM kernels: argument validation, residency checks for B, tensor-map
+// encoding, grid sizing and launch. Mirrors the host-side contract of the reference operator API
+// (csrc/apis/gemm.hpp) without torch types; see include/asymgemm_b200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/asymgemm_b200.h"
+#include "launch.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<int> g_num_sms{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define AG_REQUIRE(cond, ...)                                  \
+  do {                                                         \
+    if (!(cond)) return fail(AG_E_INVALID, __VA_ARGS__);       \
+  } while (0)
+
+#define AG_CUDA(call)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t e_ = (call);                                                                            \
+    if (e_ != cudaSuccess) return fail(AG_E_CUDA, "CUDA error (%s): %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }();
+  return fn;
+}
+
+// Byte-typed 2-D map [rows, row_bytes] with a (128 B x box_rows) box and the 128-byte swizzle.
+int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t pitch_bytes,
+                    uint32_t box_rows, const char* what) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return fail(AG_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {row_bytes, rows};
+  cuuint64_t gstr[1] = {pitch_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(AG_E_CUDA, "cuTensorMapEncodeTiled failed for %s (CUresult %d; base %p, row_bytes %llu, rows %llu)", what,
+                static_cast<int>(r), base, static_cast<unsigned long long>(row_bytes), static_cast<unsigned long long>(rows));
+  return AG_OK;
+}
+
+enum Residency { RES_DEVICE, RES_HOST_MAPPED, RES_UNREACHABLE };
+
+// Where does `p` live, and under which address can the current device read it?
+Residency classify(const void* p, const void** dev_alias) {
+  cudaPointerAttributes at;
+  *dev_alias = p;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    cudaGetLastError();
+    return RES_UNREACHABLE;
+  }
+  if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) return RES_DEVICE;
+  if (at.type == cudaMemoryTypeHost) {
+    *dev_alias = at.devicePointer != nullptr ? at.devicePointer : p;
+    return RES_HOST_MAPPED;
+  }
+  return RES_UNREACHABLE;  // pageable host memory: an x86 GPU cannot address it
+}
+
+int* default_status_word() {
+  // One word per device, allocated on first use and kept for the life of the process.
+  static std::mutex mu;
+  static int* words[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (words[dev] == nullptr) {
+    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int));
+  }
+  return words[dev];
+}
+
+int device_sm_count(int* out) {
+  static int cached[64] = {};
+  int dev = 0;
+  AG_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+    *out = cached[dev];
+    return AG_OK;
+  }
+  int major = 0, sms = 0;
+  AG_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  AG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (major != 10) return fail(AG_E_UNSUPPORTED, "this library is built for sm_100a only (device compute capability major %d)", major);
+  if (dev >= 0 && dev < 64) cached[dev] = sms;
+  *out = sms;
+  return AG_OK;
+}
+
+uint64_t k_bytes_of(int kind, int64_t k) {
+  switch (kind) {
+    case 0: return static_cast<uint64_t>(k) * 2;
+    case 3: return static_cast<uint64_t>(k) / 2;
+    default: return static_cast<uint64_t>(k);
+  }
+}
+
+int run(int kind, const ag_gemm_desc_t* g) {
+  AG_REQUIRE(g != nullptr, "desc is NULL");
+  AG_REQUIRE(g->layout == AG_LAYOUT_CONTIGUOUS || g->layout == AG_LAYOUT_MASKED, "unknown layout %d", g->layout);
+  AG_REQUIRE(g->d_dtype == AG_D_BF16 || g->d_dtype == AG_D_FP32, "unknown d_dtype %d", g->d_dtype);
+  AG_REQUIRE(g->n > 0 && g->k > 0 && g->num_groups > 0, "n, k and num_groups must be positive (n=%lld k=%lld G=%d)",
+             static_cast<long long>(g->n), static_cast<long long>(g->k), g->num_groups);
+  AG_REQUIRE(g->m >= 0, "m must be non-negative");
+  const bool masked = g->layout == AG_LAYOUT_MASKED;
+  const int64_t rows_total = masked ? g->m * g->num_groups : g->m;
+  if (rows_total == 0) return AG_OK;  // empty problem: nothing to do (csrc/apis/gemm.hpp:114-115)
+  if (!masked && g->max_segments <= 0) return AG_OK;
+  AG_REQUIRE(g->a != nullptr && g->b != nullptr && g->d != nullptr, "a, b and d must be non-NULL");
+  AG_REQUIRE(rows_total < (1LL << 31) && g->n * g->num_groups < (1LL << 31), "row counts must fit in int32");
+  AG_REQUIRE(g->n % 8 == 0, "n must be a multiple of 8 (got %lld)", static_cast<long long>(g->n));
+  if (masked) AG_REQUIRE(g->masked_m != nullptr, "masked layout needs masked_m");
+  else AG_REQUIRE(g->offsets != nullptr && g->experts != nullptr, "contiguous layout needs offsets and experts");
+  if (kind == 1 || kind == 2 || kind == 3) AG_REQUIRE(g->sfa != nullptr && g->sfb != nullptr, "quantised kinds need sfa and sfb");
+  if (kind == 3) return fail(AG_E_UNSUPPORTED, "nvfp4 kernel is not built into this library yet");
+
+  const uint64_t kbytes = k_bytes_of(kind, g->k);
+  AG_REQUIRE(kbytes % 16 == 0, "K must make rows a multiple of 16 bytes (row bytes %llu)", static_cast<unsigned long long>(kbytes));
+  AG_REQUIRE((reinterpret_cast<uintptr_t>(g->a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g->d) & 15) == 0,
+             "a and d must be 16-byte aligned");
+
+  int sms = 0;
+  if (int rc = device_sm_count(&sms)) return rc;
+  int cap = g->num_sms > 0 ? g->num_sms : g_num_sms.load();
+  int grid_cap = cap > 0 && cap < sms ? cap : sms;
+
+  const void* b_dev = nullptr;
+  const Residency res = classify(g->b, &b_dev);
+  if (res == RES_UNREACHABLE)
+    return fail(AG_E_NOT_MAPPED, "b (%p) is neither device memory nor pinned/registered host memory: pin it "
+                "(cudaHostAlloc / cudaHostRegister / torch pin_memory) before the call", g->b);
+  AG_REQUIRE((reinterpret_cast<uintptr_t>(b_dev) & 15) == 0, "b must be 16-byte aligned");
+
+  agb::GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.sfa = static_cast<const float*>(g->sfa);
+  const void* sfb_dev = g->sfb;
+  if (g->sfb != nullptr) {
+    const Residency rs = classify(g->sfb, &sfb_dev);
+    if (rs == RES_UNREACHABLE) return fail(AG_E_NOT_MAPPED, "sfb (%p) is not addressable by the device", g->sfb);
+  }
+  p.sfb = static_cast<const float*>(sfb_dev);
+  p.d = g->d;
+  p.offsets = g->offsets;
+  p.experts = g->experts;
+  p.masked_m = g->masked_m;
+  p.status = g->status != nullptr ? g->status : default_status_word();
+  if (p.status == nullptr) return fail(AG_E_CUDA, "could not allocate the status word");
+  p.raw_dump = kind == 2 ? g->raw_dump : nullptr;
+  p.timeout_ns = static_cast<unsigned long long>(g->timeout_ms ? g->timeout_ms : 4000u) * 1000000ull;
+  p.rows_total = rows_total;
+  p.layout = masked ? agb::LAYOUT_MASKED : agb::LAYOUT_CONTIGUOUS;
+  p.max_segments = masked ? g->num_groups : g->max_segments;
+  p.m_max = masked ? static_cast<int>(g->m) : 0;
+  p.num_groups = g->num_groups;
+  p.n = static_cast<int>(g->n);
+  p.n_tiles = static_cast<int>((g->n + agb::kBlockN - 1) / agb::kBlockN);
+  p.kb_count = static_cast<int>((kbytes + 127) / 128);
+  p.sf_k = static_cast<int>((g->k + 127) / 128);
+  p.sfb_rows = kind == 1 ? static_cast<int>((g->n + 127) / 128) : static_cast<int>(g->n);
+  p.d_fp32 = g->d_dtype == AG_D_FP32;
+  p.b_streaming = res == RES_HOST_MAPPED;
+  p.alpha = g->alpha == 0.f ? 1.f : g->alpha;
+
+  const long long items = static_cast<long long>(p.max_segments) * p.n_tiles;
+  const int grid = static_cast<int>(items < grid_cap ? items : grid_cap);
+  if (grid <= 0) return AG_OK;
+
+  const uint64_t kpad = static_cast<uint64_t>(p.kb_count) * 128;
+  const uint64_t need = static_cast<uint64_t>(grid) * agb::kBlockN * kpad;
+  p.use_scratch = (g->scratch != nullptr && g->scratch_bytes >= need) ? 1 : 0;
+  if (g->scratch != nullptr)
+    AG_REQUIRE((reinterpret_cast<uintptr_t>(g->scratch) & 1023) == 0, "scratch must be 1024-byte aligned");
+
+  CUtensorMap ma, mb, ms;
+  if (int rc = encode_bytes_2d(&ma, g->a, kbytes, static_cast<uint64_t>(rows_total), kbytes, 128, "a")) return rc;
+  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * g->num_groups, kbytes, agb::kBlockN, "b")) return rc;
+  if (p.use_scratch) {
+    if (int rc = encode_bytes_2d(&ms, g->scratch, kpad, static_cast<uint64_t>(grid) * agb::kBlockN, kpad, agb::kBlockN, "scratch")) return rc;
+  } else {
+    ms = mb;
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(g->stream);
+  cudaError_t e = agb::launch_mgrouped(kind, grid, stream, ma, mb, ms, p);
+  if (e != cudaSuccess) return fail(AG_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return AG_OK;
+}
+
+const char* status_text(int code) {
+  switch (code & 0xff) {
+    case agb::ST_TIMEOUT_B_EMPTY: return "timed out waiting for a free weight stage";
+    case agb::ST_TIMEOUT_A_EMPTY: return "timed out waiting for a free activation stage";
+    case agb::ST_TIMEOUT_B_FULL: return "timed out waiting for a weight tile to arrive";
+    case agb::ST_TIMEOUT_A_FULL: return "timed out waiting for an activation tile to arrive";
+    case agb::ST_TIMEOUT_TM_EMPTY: return "timed out waiting for a free accumulator";
+    case agb::ST_TIMEOUT_TM_FULL: return "timed out waiting for an accumulator to complete";
+    case agb::ST_TIMEOUT_DRAIN: return "timed out draining copies in flight";
+    case agb::ST_BAD_EXPERT: return "an expert id in `experts` is >= num_groups";
+    case agb::ST_TIMEOUT_PROBE: return "wait-limit self test expired (expected)";
+    default: return "unknown status";
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int ag_m_grouped_bf16_gemm_nt(const ag_gemm_desc_t* desc) { return run(0, desc); }
+int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc) { return run(1, desc); }
+int ag_m_grouped_int8_gemm_nt(const ag_gemm_desc_t* desc) { return run(2, desc); }
+int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc) { return run(3, desc); }
+
+uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms) {
+  (void)n;
+  int sms = num_sms;
+  if (sms <= 0) {
+    if (device_sm_count(&sms) != AG_OK) sms = 148;
+  }
+  const uint64_t kpad = (k_bytes_of(kind, k) + 127) / 128 * 128;
+  return static_cast<uint64_t>(sms) * agb::kBlockN * kpad;
+}
+
+int ag_read_status(const int32_t* status_dev, void* stream, int32_t* out) {
+  const int32_t* src = status_dev != nullptr ? status_dev : default_status_word();
+  if (src == nullptr) return fail(AG_E_CUDA, "no status word");
+  int32_t v = 0;
+  AG_CUDA(cudaMemcpyAsync(&v, src, sizeof(v), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  AG_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (out != nullptr) *out = v;
+  if (v != 0) return fail(AG_E_DEVICE, "kernel status 0x%x: CTA %d %s", v, v >> 8, status_text(v));
+  return AG_OK;
+}
+
+void ag_set_num_sms(int32_t num_sms) { g_num_sms.store(num_sms > 0 ? num_sms : 0); }
+int32_t ag_get_num_sms(void) {
+  int v = g_num_sms.load();
+  if (v > 0) return v;
+  int sms = 0;
+  return device_sm_count(&sms) == AG_OK ? sms : 0;
+}
+int32_t ag_get_mk_alignment_for_contiguous_layout(void) { return 128; }
+
+uint64_t ag_fp4_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t k16) {
+  const uint64_t row_tiles = static_cast<uint64_t>((rows + 127) / 128);
+  const uint64_t k4 = static_cast<uint64_t>((k16 + 3) / 4);
+  return static_cast<uint64_t>(groups) * row_tiles * k4 * 512;
+}
+
+int ag_fp4_sf_to_blocked(const void*, void*, int64_t, int64_t, int64_t, void*) {
+  return fail(AG_E_UNSUPPORTED, "nvfp4 kernel is not built into this library yet");
+}
+
+int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out) {
+  AG_REQUIRE(gbps_out != nullptr && bytes > 0, "bad arguments");
+  void *h = nullptr, *d = nullptr;
+  AG_CUDA(cudaHostAlloc(&h, bytes, cudaHostAllocDefault));
+  if (cudaMalloc(&d, bytes) != cudaSuccess) {
+    cudaFreeHost(h);
+    return fail(AG_E_CUDA, "cudaMalloc(%llu) failed", static_cast<unsigned long long>(bytes));
+  }
+  std::memset(h, 1, bytes);
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  double best = 0;
+  for (int r = 0; r < (reps > 0 ? reps : 3); ++r) {
+    cudaEventRecord(e0, 0);
+    cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, 0);
+    cudaEventRecord(e1, 0);
+    cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (ms > 0) {
+      const double g = static_cast<double>(bytes) / (ms * 1e6);
+      if (g > best) best = g;
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(d);
+  cudaFreeHost(h);
+  *gbps_out = best;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(AG_E_CUDA, "CUDA error while measuring the host link: %s", cudaGetErrorString(e));
+  return AG_OK;
+}
+
+const char* ag_last_error(void) { return g_err; }
+const char* ag_version(void) { return "asymgemm_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,517 @@
+// m-grouped asymmetric GEMM for sm_100a: D[rows of segment s] = A[rows of s] x B[expert(s)]^T, where the
+// weight tensor B [G, N, K] (K-major) may live in pinned, device-mapped host memory and is streamed by
+// TMA straight into a shared-memory ring, while A and D live in HBM.
+//
+// Work decomposition (replaces the reference's one-CTA-per-(n-block, segment) grid and its single B
+// slot, asym_gemm/include/asym_gemm/common/asymScheduler.cuh:92-124 and
+// asym_gemm/include/asym_gemm/impls/sm100_fp8_asym_gemm_1d1d.cuh:255-330,471):
+//   * an item is (segment, n-tile); a persistent CTA takes items c, c+grid, ... with the n-tile index
+//     fastest, so CTAs that run together share the same activation rows in L2;
+//   * an item's weight column (BN rows x K) is fetched over the host link exactly once. The segment's
+//     rows are processed in chunks of CHUNK_TILES 128-row tiles whose fp32/int32 accumulators stay in
+//     TMEM across the whole K loop (K outer, M inner inside a chunk). Segments longer than one chunk
+//     replay the column from a per-CTA scratch copy in device memory that the first pass writes with a
+//     TMA store of the very shared-memory stage the MMA consumes (no second trip over the host link);
+//   * no atomics, no partial sums in D: every output element is written once, from fp32.
+//
+// Warp roles (256 threads): warp 0 = B producer (+ scratch spill), warp 1 = A producer,
+// warp 2 = TMEM allocator + single-thread tcgen05.mma issuer, warp 3 idle, warps 4-7 = TMEM drain.
+//
+// Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
+// shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
+#pragma once
+#include <cuda_bf16.h>
+#include "ptx.cuh"
+
+namespace agb {
+
+enum class Kind : int { BF16 = 0, FP8 = 1, INT8 = 2, NVFP4 = 3 };
+enum : int { LAYOUT_CONTIGUOUS = 0, LAYOUT_MASKED = 1 };
+
+// status codes written to GemmParams::status (low byte = code, upper bits = CTA index)
+enum : int {
+  ST_OK = 0,
+  ST_TIMEOUT_B_EMPTY = 1,
+  ST_TIMEOUT_A_EMPTY = 2,
+  ST_TIMEOUT_B_FULL = 3,
+  ST_TIMEOUT_A_FULL = 4,
+  ST_TIMEOUT_TM_EMPTY = 5,
+  ST_TIMEOUT_TM_FULL = 6,
+  ST_TIMEOUT_DRAIN = 7,
+  ST_BAD_EXPERT = 8,
+  ST_TIMEOUT_PROBE = 9,
+};
+
+struct GemmParams {
+  const float* sfa;        // FP8/INT8: [rows, sf_k] fp32.  NVFP4: blocked UE4M3 bytes (see sf_layout.cuh)
+  const float* sfb;        // FP8: [G, ceil(N/128), sf_k]; INT8: [G, N, sf_k]; NVFP4: blocked UE4M3 bytes
+  void* d;                 // [rows, N] bf16 or fp32
+  const int* offsets;      // contiguous: (start, end) row pairs per segment
+  const int* experts;      // contiguous: weight index per segment, list ends at the first negative entry
+  const int* masked_m;     // masked: valid rows per group
+  int* status;             // one word, 0 = ok
+  int* raw_dump;           // INT8 debug hook: int32 block sums [sf_k, rows, N] before scaling, or null
+  unsigned long long timeout_ns;
+  long long rows_total;    // rows of A / D (contiguous: M, masked: G * m_max)
+  int layout;
+  int max_segments;        // contiguous: upper bound on segments to visit; masked: G
+  int m_max;               // masked: rows per group
+  int num_groups;
+  int n;
+  int n_tiles;             // ceil(N / BN)
+  int kb_count;            // ceil(K bytes / 128)
+  int sf_k;                // scale blocks along K (FP8/INT8: ceil(K/128))
+  int sfb_rows;            // FP8: ceil(N/128); INT8: N
+  int d_fp32;
+  int use_scratch;         // 1 = replay long segments from the scratch copy, 0 = re-read B from its source
+  int b_streaming;         // 1 = B is host memory: mark its lines evict-first in L2
+  float alpha;             // NVFP4 global scale (product of the two tensor-level scales), 1.0 otherwise
+};
+
+struct Item {
+  int expert;
+  int row0;
+  int rows;
+  int nt;
+};
+
+// Returns 0 when the CTA has run out of work, 1 otherwise (rows may still be 0: skip).
+__device__ __forceinline__ int fetch_item(const GemmParams& p, long long item, Item& it) {
+  const int seg = static_cast<int>(item / p.n_tiles);
+  it.nt = static_cast<int>(item - static_cast<long long>(seg) * p.n_tiles);
+  if (seg >= p.max_segments) return 0;
+  if (p.layout == LAYOUT_MASKED) {
+    it.expert = seg;
+    it.row0 = seg * p.m_max;
+    int r = __ldg(p.masked_m + seg);
+    it.rows = r < 0 ? 0 : (r > p.m_max ? p.m_max : r);
+  } else {
+    const int e = __ldg(p.experts + seg);
+    if (e < 0) return 0;
+    it.expert = e;
+    int r0 = __ldg(p.offsets + 2 * seg), r1 = __ldg(p.offsets + 2 * seg + 1);
+    if (r0 < 0) r0 = 0;
+    if (r1 > p.rows_total) r1 = static_cast<int>(p.rows_total);
+    it.row0 = r0;
+    it.rows = r1 > r0 ? r1 - r0 : 0;
+    if (e >= p.num_groups) {  // would read outside B: flag it and skip
+      atomicCAS(p.status, 0, ST_BAD_EXPERT | (static_cast<int>(blockIdx.x) << 8));
+      it.rows = 0;
+    }
+  }
+  return 1;
+}
+
+struct WaitCtx {
+  int* status;
+  volatile int* abort_flag;
+  unsigned long long timeout_ns;
+};
+
+// Bounded wait. Returns false if the CTA is aborting (either this wait expired or another role's did).
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const WaitCtx& c, int code, bool honor_abort = true) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t n = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++n & 63u) == 0) {
+      if (honor_abort && *c.abort_flag) return false;
+      if (global_timer_ns() - t0 > c.timeout_ns) {
+        atomicCAS(c.status, 0, code | (static_cast<int>(blockIdx.x) << 8));
+        *c.abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+template <Kind KIND>
+struct KindTraits;
+template <>
+struct KindTraits<Kind::BF16> {
+  static constexpr MmaKind mma = MmaKind::F16;
+  static constexpr bool sw_scale = false;
+  static constexpr uint32_t d_fmt = 1, ab_fmt = 1;
+};
+template <>
+struct KindTraits<Kind::FP8> {
+  static constexpr MmaKind mma = MmaKind::F8F6F4;
+  static constexpr bool sw_scale = true;
+  static constexpr uint32_t d_fmt = 1, ab_fmt = 0;
+};
+template <>
+struct KindTraits<Kind::INT8> {
+  static constexpr MmaKind mma = MmaKind::I8;
+  static constexpr bool sw_scale = true;
+  static constexpr uint32_t d_fmt = 2, ab_fmt = 1;
+};
+
+constexpr int BM = 128;            // rows per MMA tile
+constexpr int ATOM_BYTES = 128;    // bytes of K per pipeline stage row (one 128-byte swizzle atom)
+constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
+constexpr int NUM_THREADS = 256;
+constexpr int TMEM_COLS = 512;
+
+template <int BN, int SA, int SB>
+struct SmemLayout {
+  static constexpr int a_stage = BM * ATOM_BYTES;
+  static constexpr int b_stage = BN * ATOM_BYTES;
+  static constexpr int a_off = 0;
+  static constexpr int b_off = a_off + SA * a_stage;
+  static constexpr int bar_off = b_off + SB * b_stage;
+  static constexpr int num_bars = 2 * SA + 2 * SB + 8 + 1;
+  static constexpr int sfb_off = bar_off + num_bars * 8;          // 4 warps x BN floats (INT8 column scales)
+  static constexpr int misc_off = sfb_off + 4 * BN * 4;           // tmem base, abort flag
+  static constexpr int total = misc_off + 16;
+  static constexpr int dyn_bytes = total + 1024;                  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Store 32 consecutive output columns of one row. `vals` are fp32 bit patterns.
+__device__ __forceinline__ void store_row32(const GemmParams& p, long long grow, int col0, const uint32_t (&vals)[32]) {
+  if (p.d_fp32) {
+    float* dst = reinterpret_cast<float*>(p.d) + grow * p.n + col0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (col0 + j * 4 < p.n) {
+        uint4 v = make_uint4(vals[4 * j], vals[4 * j + 1], vals[4 * j + 2], vals[4 * j + 3]);
+        *reinterpret_cast<uint4*>(dst + 4 * j) = v;
+      }
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.n + col0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col0 + j * 8 < p.n) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(vals[8 * j + 0]), __uint_as_float(vals[8 * j + 1]));
+        v.y = pack_bf16(__uint_as_float(vals[8 * j + 2]), __uint_as_float(vals[8 * j + 3]));
+        v.z = pack_bf16(__uint_as_float(vals[8 * j + 4]), __uint_as_float(vals[8 * j + 5]));
+        v.w = pack_bf16(__uint_as_float(vals[8 * j + 6]), __uint_as_float(vals[8 * j + 7]));
+        *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+      }
+    }
+  }
+}
+
+template <Kind KIND, int BN, int SA, int SB>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
+  using T = KindTraits<KIND>;
+  using L = SmemLayout<BN, SA, SB>;
+  static_assert(BN == 128, "the TMEM plan below assumes 128-column accumulators");
+  // TMEM plan: 4 slots of BN columns. Hardware-accumulated kinds keep up to 4 output tiles; software-scaled
+  // kinds keep 2 scaled fp32 tiles (slots 0,1) and double-buffer the raw per-K-block product (slots 2,3).
+  constexpr int CHUNK_TILES = T::sw_scale ? 2 : 4;
+  constexpr uint32_t IDESC = make_idesc(T::d_fmt, T::ab_fmt, BN);
+  constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
+
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_a = smem + L::a_off;
+  uint8_t* smem_b = smem + L::b_off;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint64_t* a_full = bars;
+  uint64_t* a_empty = a_full + SA;
+  uint64_t* b_full = a_empty + SA;
+  uint64_t* b_empty = b_full + SB;
+  uint64_t* tm_full = b_empty + SB;   // [4]  bf16: per accumulator slot; sw_scale: [0..1] = raw slots
+  uint64_t* tm_empty = tm_full + 4;   // [4]
+  uint64_t* done_bar = tm_empty + 4;  // MMA thread drains its own pipeline through this one on abort
+  float* sfb_smem = reinterpret_cast<float*>(smem + L::sfb_off);
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(smem + L::misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], 4); }
+    mbar_init(done_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_s);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_base_smem, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_smem;
+  const WaitCtx wc{p.status, abort_flag, p.timeout_ns};
+  const int kb_count = p.kb_count;
+
+  if (warp == 0) {
+    // ===================================================================== B producer (+ scratch spill)
+    if (lane == 0) {
+      uint32_t jt = 0;  // stage uses so far
+      bool ok = true;
+      const uint64_t pol_stream = l2_policy_evict_first();
+      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+        Item it;
+        if (!fetch_item(p, item, it)) break;
+        if (it.rows <= 0) continue;
+        const int mtiles = (it.rows + BM - 1) / BM;
+        const int chunks = (mtiles + CHUNK_TILES - 1) / CHUNK_TILES;
+        const bool spill = p.use_scratch && chunks > 1;
+        const int b_row = it.expert * p.n + it.nt * BN;
+        const int s_row = static_cast<int>(blockIdx.x) * BN;
+        if (spill) {
+          // Loads of the previous item may still be reading this CTA's scratch rows: let them land first.
+          const uint32_t first = jt > SB ? jt - SB : 0;
+          for (uint32_t q = first; q < jt && ok; ++q) ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+        }
+        const uint32_t jt_item = jt;
+        for (int chunk = 0; chunk < chunks && ok; ++chunk) {
+          const bool from_scratch = spill && chunk > 0;
+          if (spill && chunk == 1) bulk_wait_group0();  // the scratch copy is complete and visible
+          int next_store = 0;
+          for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+            const uint32_t s = jt % SB;
+            ok = wait_bar(&b_empty[s], ((jt / SB) & 1) ^ 1, wc, ST_TIMEOUT_B_EMPTY);
+            if (!ok) break;
+            if (spill && chunk == 0) bulk_wait_group_read0();  // earlier spill stores have finished reading their stages
+            mbar_arrive_expect_tx(&b_full[s], L::b_stage);
+            if (from_scratch) tma_load_2d(smem_b + s * L::b_stage, &tmap_s, &b_full[s], kb * ATOM_BYTES, s_row);
+            else if (p.b_streaming) tma_load_2d_hint(smem_b + s * L::b_stage, &tmap_b, &b_full[s], kb * ATOM_BYTES, b_row, pol_stream);
+            else tma_load_2d(smem_b + s * L::b_stage, &tmap_b, &b_full[s], kb * ATOM_BYTES, b_row);
+            if (spill && chunk == 0) {
+              while (next_store + SPILL_DELAY <= kb && ok) {
+                const uint32_t q = jt_item + next_store;
+                ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+                if (ok) { tma_store_2d(&tmap_s, smem_b + (q % SB) * L::b_stage, next_store * ATOM_BYTES, s_row); bulk_commit_group(); }
+                ++next_store;
+              }
+            }
+          }
+          if (spill && chunk == 0) {
+            while (next_store < kb_count && ok) {
+              const uint32_t q = jt_item + next_store;
+              ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+              if (ok) { tma_store_2d(&tmap_s, smem_b + (q % SB) * L::b_stage, next_store * ATOM_BYTES, s_row); bulk_commit_group(); }
+              ++next_store;
+            }
+          }
+        }
+      }
+      bulk_wait_group0();
+      if (!ok) {  // aborting: let this thread's own loads land before the CTA goes away
+        const uint32_t first = jt > SB ? jt - SB : 0;
+        for (uint32_t q = first; q < jt; ++q) wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_DRAIN, false);
+      }
+    }
+  } else if (warp == 1) {
+    // ===================================================================== A producer
+    if (lane == 0) {
+      uint32_t it_a = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+        Item it;
+        if (!fetch_item(p, item, it)) break;
+        if (it.rows <= 0) continue;
+        const int mtiles = (it.rows + BM - 1) / BM;
+        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
+          const int mc = min(CHUNK_TILES, mtiles - m0);
+          for (int kb = 0; kb < kb_count && ok; ++kb) {
+            for (int mt = 0; mt < mc; ++mt, ++it_a) {
+              const uint32_t s = it_a % SA;
+              ok = wait_bar(&a_empty[s], ((it_a / SA) & 1) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&a_full[s], L::a_stage);
+              tma_load_2d(smem_a + s * L::a_stage, &tmap_a, &a_full[s], kb * ATOM_BYTES, it.row0 + (m0 + mt) * BM);
+            }
+          }
+        }
+      }
+      if (!ok) {
+        const uint32_t first = it_a > SA ? it_a - SA : 0;
+        for (uint32_t q = first; q < it_a; ++q) wait_bar(&a_full[q % SA], (q / SA) & 1, wc, ST_TIMEOUT_DRAIN, false);
+      }
+    }
+  } else if (warp == 2) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      uint32_t it_a = 0, jt = 0, rt = 0, slot_phase = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+        Item it;
+        if (!fetch_item(p, item, it)) break;
+        if (it.rows <= 0) continue;
+        const int mtiles = (it.rows + BM - 1) / BM;
+        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
+          const int mc = min(CHUNK_TILES, mtiles - m0);
+          for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+            const uint32_t sb = jt % SB;
+            ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+            if (!ok) break;
+            const uint32_t b_addr = smem_u32(smem_b + sb * L::b_stage);
+            for (int mt = 0; mt < mc; ++mt, ++it_a) {
+              const uint32_t sa = it_a % SA;
+              ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
+              if (!ok) break;
+              uint32_t d_col;
+              if constexpr (T::sw_scale) {
+                const uint32_t rs = rt & 1;
+                ok = wait_bar(&tm_empty[rs], ((rt >> 1) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                d_col = (CHUNK_TILES + rs) * BN;
+              } else {
+                if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                d_col = mt * BN;
+              }
+              if (!ok) break;
+              tc_fence_after_sync();
+              const uint32_t a_addr = smem_u32(smem_a + sa * L::a_stage);
+#pragma unroll
+              for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
+                const uint64_t da = make_kmajor_sw128_desc(a_addr + j * MMA_K_BYTES);
+                const uint64_t db = make_kmajor_sw128_desc(b_addr + j * MMA_K_BYTES);
+                const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
+                umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+              }
+              umma_commit(&a_empty[sa]);
+              if constexpr (T::sw_scale) {
+                umma_commit(&tm_full[rt & 1]);
+                ++rt;
+              } else {
+                if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
+              }
+            }
+            if (ok) umma_commit(&b_empty[sb]);
+          }
+          if constexpr (!T::sw_scale) slot_phase ^= (1u << mc) - 1u;
+        }
+      }
+      if (!ok) {  // aborting: wait until the tensor pipe has retired what this thread issued
+        umma_commit(done_bar);
+        wait_bar(done_bar, 0, wc, ST_TIMEOUT_DRAIN, false);
+      }
+    }
+  } else if (warp >= 4) {
+    // ===================================================================== TMEM drain (epilogue)
+    const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    uint32_t rt = 0, slot_phase = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; ok; item += gridDim.x) {
+      Item it;
+      if (!fetch_item(p, item, it)) break;
+      if (it.rows <= 0) continue;
+      const int mtiles = (it.rows + BM - 1) / BM;
+      const int n0 = it.nt * BN;
+      const long long row_end = static_cast<long long>(it.row0) + it.rows;
+      for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
+        const int mc = min(CHUNK_TILES, mtiles - m0);
+        if constexpr (T::sw_scale) {
+          for (int kb = 0; kb < kb_count && ok; ++kb) {
+            // column scales of this K block
+            float sb_scalar = 0.f;
+            if constexpr (KIND == Kind::FP8) {
+              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + (n0 >> 7)) * p.sf_k + kb);
+            }
+            for (int mt = 0; mt < mc && ok; ++mt, ++rt) {
+              const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
+              const bool valid = grow < row_end;
+              const float sa = valid ? __ldg(p.sfa + grow * p.sf_k + kb) : 0.f;
+              float* sfb_buf = sfb_smem + q * BN;  // private to this warp: no cross-warp barrier on any path
+              if constexpr (KIND == Kind::INT8) {
+#pragma unroll
+                for (int j = 0; j < BN / 32; ++j) {
+                  const int col = n0 + j * 32 + lane;
+                  sfb_buf[j * 32 + lane] =
+                      col < p.n ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + col) * p.sf_k + kb) : 0.f;
+                }
+                __syncwarp();
+              }
+              const uint32_t rs = rt & 1;
+              ok = wait_bar(&tm_full[rs], (rt >> 1) & 1, wc, ST_TIMEOUT_TM_FULL);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              tc_fence_after_sync();
+              const uint32_t raw_addr = lane_addr + (CHUNK_TILES + rs) * BN;
+              const uint32_t acc_addr = lane_addr + mt * BN;
+              const bool last = kb == kb_count - 1;
+#pragma unroll 1
+              for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32], a[32];
+                tmem_ld_32x32b_x32(raw_addr + cc * 32, r);
+                if (kb > 0) tmem_ld_32x32b_x32(acc_addr + cc * 32, a);
+                tmem_wait_ld();
+                if constexpr (KIND == Kind::INT8) {
+                  if (p.raw_dump != nullptr && valid) {
+                    int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + cc * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (n0 + cc * 32 + j < p.n) dst[j] = static_cast<int>(r[j]);
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  float prod, scale;
+                  if constexpr (KIND == Kind::INT8) {
+                    prod = static_cast<float>(static_cast<int>(r[j]));
+                    scale = sa * sfb_buf[cc * 32 + j];
+                  } else {
+                    prod = __uint_as_float(r[j]);
+                    scale = sa * sb_scalar;
+                  }
+                  const float prev = kb > 0 ? __uint_as_float(a[j]) : 0.f;
+                  a[j] = __float_as_uint(fmaf(prod, scale, prev));
+                }
+                if (last) {
+                  if (valid) store_row32(p, grow, n0 + cc * 32, a);
+                } else {
+                  tmem_st_32x32b_x32(acc_addr + cc * 32, a);
+                }
+              }
+              if (!last) tmem_wait_st();
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tm_empty[rs]);
+            }
+          }
+        } else {
+          for (int mt = 0; mt < mc && ok; ++mt) {
+            ok = wait_bar(&tm_full[mt], (slot_phase >> mt) & 1, wc, ST_TIMEOUT_TM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
+            const bool valid = grow < row_end;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(lane_addr + mt * BN + cc * 32, r);
+              tmem_wait_ld();
+              if (valid) store_row32(p, grow, n0 + cc * 32, r);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tm_empty[mt]);
+          }
+          slot_phase ^= (1u << mc) - 1u;
+        }
+      }
+    }
+  }
+
+  // ===================================================================== common exit: free TMEM on every path
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace agb

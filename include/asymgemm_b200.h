@@ -1,0 +1,136 @@
+/*
+ * asymgemm_b200.h -- C ABI of the B200 (sm_100a) m-grouped asymmetric MoE GEMM.
+ *
+ * "Asymmetric": the weight tensor B [G, N, K] (K-major) may stay in pinned / registered host memory and
+ * is streamed over the host link by TMA inside the kernel, while activations A and outputs D live in
+ * device memory. B may also be device-resident; the same entry points serve both.
+ *
+ * The entry points below are what a binding of the reference operator API (bytedance-iaas/AsymGEMM,
+ * csrc/apis/gemm.hpp, registered in csrc/python_api.cpp) would call for this path. Plain pointers and
+ * sizes only; no torch types. All launches are asynchronous on `stream`. Functions return 0 on success
+ * and a negative ag_status_t otherwise; ag_last_error() returns a thread-local message for the last
+ * failure (the reference raises "Assertion error (file:line): cond", csrc/utils/exception.hpp:14-47).
+ */
+#ifndef ASYMGEMM_B200_H
+#define ASYMGEMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ag_status {
+  AG_OK = 0,
+  AG_E_INVALID = -1,     /* malformed descriptor (null pointer, bad shape, misaligned pointer) */
+  AG_E_UNSUPPORTED = -2, /* combination not implemented on this device */
+  AG_E_CUDA = -3,        /* a CUDA runtime / driver call failed */
+  AG_E_NOT_MAPPED = -4,  /* B is host memory that the device cannot address (not pinned / registered) */
+  AG_E_DEVICE = -5       /* the kernel reported a status word != 0 (see ag_read_status) */
+} ag_status_t;
+
+typedef enum ag_layout {
+  AG_LAYOUT_CONTIGUOUS = 0, /* A [M, K], D [M, N]; segments given by (offsets, experts) */
+  AG_LAYOUT_MASKED = 1      /* A [G, M_max, K], D [G, M_max, N]; valid rows per group in masked_m */
+} ag_layout_t;
+
+typedef enum ag_d_dtype { AG_D_BF16 = 0, AG_D_FP32 = 1 } ag_d_dtype_t;
+
+/* One grouped-GEMM call. Unused fields must be zero / NULL. */
+typedef struct ag_gemm_desc {
+  int32_t layout;  /* ag_layout_t */
+  int32_t d_dtype; /* ag_d_dtype_t */
+
+  const void* a;   /* device. bf16 [rows, K] | fp8 e4m3 [rows, K] | int8 [rows, K] | packed e2m1 [rows, K/2] */
+  const void* sfa; /* device. fp8, int8: fp32 [rows, ceil(K/128)]; nvfp4: ue4m3 [rows, K/16]; bf16: NULL */
+  const void* b;   /* device, or pinned/registered host. [G, N, K] in A's element type, K-major */
+  const void* sfb; /* device or pinned host. fp8: fp32 [G, ceil(N/128), ceil(K/128)];
+                      int8: fp32 [G, N, K/128]; nvfp4: ue4m3 [G, N, K/16]; bf16: NULL */
+  void* d;         /* device. [rows, N] bf16 or fp32, row-major, written in place */
+
+  /* contiguous layout: segment i covers rows [offsets[2i], offsets[2i+1]) and uses weight experts[i];
+     the list ends at the first negative expert id or after max_segments entries. */
+  const int32_t* offsets; /* device */
+  const int32_t* experts; /* device */
+  int32_t max_segments;
+
+  /* masked layout: group g uses rows [g*m, g*m + masked_m[g]) and weight g. */
+  const int32_t* masked_m; /* device, [num_groups] */
+
+  int64_t m; /* contiguous: total rows of A and D; masked: M_max (rows per group) */
+  int64_t n;
+  int64_t k;
+  int32_t num_groups; /* G */
+
+  /* Optional device scratch for segments longer than one accumulator chunk (see ag_scratch_bytes).
+     NULL: such segments re-read their weight column from `b` once per chunk instead. */
+  void* scratch;
+  uint64_t scratch_bytes;
+
+  int32_t* status;     /* device int32, optional: 0 = ok, else (cta << 8) | code. Never reset by the call. */
+  void* stream;        /* cudaStream_t */
+  int32_t num_sms;     /* CTAs to launch at most; 0 = every SM (or the value set by ag_set_num_sms) */
+  uint32_t timeout_ms; /* bound on every in-kernel wait; 0 = default (4000 ms) */
+  int32_t* raw_dump;   /* int8 only, optional: device int32 [ceil(K/128), rows, N], the exact block sums */
+  float alpha;         /* nvfp4 only: product of the two tensor-level scales; 0 is read as 1 */
+} ag_gemm_desc_t;
+
+/* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked
+ * (csrc/apis/gemm.hpp:370-418, 420-486; kernel asym_gemm/include/asym_gemm/impls/sm100_bf16_asym_gemm.cuh:98-115). */
+int ag_m_grouped_bf16_gemm_nt(const ag_gemm_desc_t* desc);
+
+/* FP8 E4M3 with fp32 scales: A 1x128 per row, B 128x128 per block. Replaces
+ * m_grouped_fp8_asym_gemm_nt_contiguous / _masked (csrc/apis/gemm.hpp:81-157, 159-235; kernel
+ * asym_gemm/include/asym_gemm/impls/sm100_fp8_asym_gemm_1d1d.cuh:33-40). Scales are applied in fp32 exactly;
+ * the reference truncates them to powers of two first (impls/smxx_layout.cuh:96-100), which gives the same
+ * result whenever the quantiser produced power-of-two scales. */
+int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc);
+
+/* INT8 x INT8 -> exact int32 per 128-wide K block, then fp32 sfa[row,kb] * sfb[col,kb] * sum, summed over
+ * K blocks in ascending order. Replaces m_grouped_int8_asym_gemm_nt_contiguous / _masked
+ * (csrc/apis/gemm.hpp:569-630; kernel asym_gemm/include/asym_gemm/impls/sm90_int8_asym_gemm_1d1d.cuh:34-41). */
+int ag_m_grouped_int8_gemm_nt(const ag_gemm_desc_t* desc);
+
+/* NVFP4: packed E2M1 values, one UE4M3 scale per 16 elements of K. Replaces
+ * m_grouped_fp4_asym_gemm_nt_contiguous / _masked (csrc/apis/gemm.hpp:237-300, 302-365; kernel
+ * asym_gemm/include/asym_gemm/impls/sm100_fp4_asym_gemm_1d1d.cuh:44-51). */
+int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc);
+
+/* Bytes of scratch that let every long segment replay its weight column from device memory
+ * (kind: 0 bf16, 1 fp8, 2 int8, 3 nvfp4). Reference counterpart: none (the reference accumulates bf16
+ * partial sums in D instead, impls/sm100_fp8_asym_gemm_1d1d.cuh:648-659). */
+uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms);
+
+/* Synchronises `stream`, copies the status word to *out and returns AG_OK or AG_E_DEVICE (with a decoded
+ * message in ag_last_error). Replaces the reference's device-side trap (asym_gemm/include/asym_gemm/common/utils.cuh:24-40). */
+int ag_read_status(const int32_t* status_dev, void* stream, int32_t* out);
+
+/* Process-wide cap on CTAs per launch; 0 restores "all SMs". Replaces set_num_sms / get_num_sms
+ * (csrc/apis/runtime.hpp:15-33). */
+void ag_set_num_sms(int32_t num_sms);
+int32_t ag_get_num_sms(void);
+
+/* Row alignment callers must give every contiguous-layout segment (128). Replaces
+ * get_mk_alignment_for_contiguous_layout (csrc/utils/layout.hpp:108-110). */
+int32_t ag_get_mk_alignment_for_contiguous_layout(void);
+
+/* Re-lays NVFP4 UE4M3 scales [groups, rows, k16] (row-major bytes; device or pinned host) into the blocked
+ * form the kernel copies into TMEM: per group, per 128-row tile, per 4 scale columns one 512-byte block
+ * with byte (r % 32) * 16 + (r / 32) * 4 + c. dst is device memory of ag_fp4_sf_blocked_bytes() bytes.
+ * Replaces get_mn_major_tma_aligned_packed_byte_sf_tensor (csrc/apis/layout.hpp:14-35). */
+uint64_t ag_fp4_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t k16);
+int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t rows, int64_t k16, void* stream);
+
+/* Measures pinned-host -> device copy-engine bandwidth (GB/s) with cudaMemcpyAsync over `bytes`, best of
+ * `reps`: the denominator for "fraction of host link". Reference counterpart: none (its authors quote
+ * ~50 GB/s for the same copy, asym_gemm/unified_moe/runtime.py:115-116). */
+int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out);
+
+const char* ag_last_error(void);
+const char* ag_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASYMGEMM_B200_H */
