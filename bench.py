@@ -1,0 +1,394 @@
+#!/usr/bin/env python
+"""Benchmark of the m-grouped asymmetric GEMM: grouped-GEMM TFLOP/s and host->GPU weight GB/s against the measured
+host-link peak.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3_fp8|c2_bf16|c1_int8] [--impl ours|reference]
+
+One step = one grouped GEMM over one batch of synthetic, seeded input (the shapes of BASELINE.json's configs; no
+dataset or checkpoint is involved). The default workload is the DeepSeek-V3-shaped FP8 gate+up GEMM: 256 experts,
+K=7168, N=4096, 16384 tokens x top-8 with Zipf(0.8) expert popularity, B (7.5 GB) in pinned host memory.
+With N > 1 ranks the experts (and the rows routed to them) are split evenly across ranks; every rank streams its own
+shard over its own host link and there is no collective on the data path, so total work is fixed ("strong").
+
+Prints ONE JSON line on rank 0. `value` times the kernel with activations already in HBM; `e2e` times the public
+operator call with host buffers (pinned A in, D out) inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: kind, experts, K, N, tokens, top_k, zipf_s
+    "c3_fp8": dict(kind="fp8", experts=256, k=7168, n=4096, tokens=16384, top_k=8, zipf=0.8),
+    "c2_bf16": dict(kind="bf16", experts=128, k=2048, n=1536, tokens=8192, top_k=8, zipf=1.0),
+    "c1_int8": dict(kind="int8", experts=16, k=2048, n=1536, tokens=2048, top_k=4, zipf=0.0),
+}
+ELEM_BYTES = {"fp8": 1.0, "bf16": 2.0, "int8": 1.0, "fp4": 0.5}
+
+
+def rows_per_expert(cfg, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    e = cfg["experts"]
+    w = 1.0 / torch.arange(1, e + 1, dtype=torch.float64) ** cfg["zipf"]
+    picks = torch.multinomial(w.expand(cfg["tokens"], -1), cfg["top_k"], replacement=False, generator=gen)
+    return torch.bincount(picks.flatten(), minlength=e).tolist()
+
+
+def build_workload(cfg, rank, world, device, seed=0):
+    """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
+    from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
+                                     per_token_cast_to_fp8, per_token_cast_to_int8)
+    kind, k, n = cfg["kind"], cfg["k"], cfg["n"]
+    counts = rows_per_expert(cfg, seed)
+    e_total = cfg["experts"]
+    per = e_total // world
+    lo, hi = rank * per, (rank + 1) * per if rank < world - 1 else e_total
+    counts = counts[lo:hi]
+    g = len(counts)
+    offsets, experts, list_size, m_total, segs = build_contiguous_layout(counts, device=device)
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    valid = sum(c for c in counts)
+
+    a_dtype = {"fp8": torch.float8_e4m3fn, "bf16": torch.bfloat16, "int8": torch.int8}[kind]
+    a = torch.zeros((m_total, k), dtype=a_dtype, device=device)
+    sfa = None if kind == "bf16" else torch.zeros((m_total, (k + 127) // 128), dtype=torch.float32, device=device)
+    for e, start, rows in segs:
+        x = torch.randn((rows, k), device=device, generator=gen)
+        if kind == "fp8":
+            q, s = per_token_cast_to_fp8(x, use_ue8m0=False)
+            a[start:start + rows], sfa[start:start + rows] = q, s
+        elif kind == "int8":
+            q, s = per_token_cast_to_int8(x)
+            a[start:start + rows], sfa[start:start + rows] = q, s
+        else:
+            a[start:start + rows] = x.to(torch.bfloat16)
+
+    b_host = torch.empty((g, n, k), dtype=a_dtype).pin_memory()
+    sfb = None
+    if kind == "fp8":
+        sfb = torch.empty((g, (n + 127) // 128, (k + 127) // 128), dtype=torch.float32, device=device)
+    elif kind == "int8":
+        sfb = torch.empty((g, n, k // 128), dtype=torch.float32, device=device)
+    for e in range(g):
+        w = torch.randn((n, k), device=device, generator=gen) * 0.02
+        if kind == "fp8":
+            q, s = per_block_cast_to_fp8(w, use_ue8m0=False)
+            sfb[e] = s
+        elif kind == "int8":
+            q, s = per_channel_cast_to_int8(w)
+            sfb[e] = s
+        else:
+            q = w.to(torch.bfloat16)
+        b_host[e].copy_(q, non_blocking=True)
+    torch.cuda.synchronize(device)
+    d = torch.empty((m_total, n), dtype=torch.bfloat16, device=device)
+    active = sum(1 for c in counts if c > 0)
+    return dict(kind=kind, a=a, sfa=sfa, b=b_host, sfb=sfb, d=d, offsets=offsets, experts=experts, list_size=list_size,
+                m_total=m_total, valid_rows=valid, segs=segs, g=g, n=n, k=k,
+                flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
+
+
+def run_op(w, a=None, sfa=None, d=None):
+    import asymgemm_b200 as ag
+    a = w["a"] if a is None else a
+    sfa = w["sfa"] if sfa is None else sfa
+    d = w["d"] if d is None else d
+    if w["kind"] == "fp8":
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((a, sfa), (w["b"], w["sfb"]), d, w["offsets"], w["experts"], None)
+    elif w["kind"] == "int8":
+        ag.m_grouped_int8_asym_gemm_nt_contiguous((a, sfa), (w["b"], w["sfb"]), d, w["offsets"], w["experts"], None)
+    else:
+        ag.m_grouped_bf16_asym_gemm_nt_contiguous(a, w["b"], d, w["offsets"], w["experts"], None)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            for i, nm in enumerate(names):
+                if len(r) > 3 + i and r[3 + i].lower().startswith("active"):
+                    reasons.add(nm)
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_sample(cfg, w, threads, max_experts):
+    """The reference's CPU path on a bounded sample of this workload, all host threads.
+
+    INT8: the reference's own cg_gemm (oracle/_ref) called once per expert, as csrc/cpu/module.cpp:329-373 does.
+    Other dtypes: the reference's torch CPU loop `a[s:e] @ w.t()` (asym_gemm/training/frozen_linear.py:986-1008) on
+    operands dequantised to bf16 beforehand (dequantisation is not timed).
+    Returns (tflops, description, kind, cores).
+    """
+    import numpy as np
+    from oracle import oracle as O
+    kind, n, k = w["kind"], w["n"], w["k"]
+    segs = [s for s in w["segs"] if s[2] > 0][:max_experts]
+    torch.set_num_threads(threads)
+    flops = 0.0
+    if kind == "int8":
+        from oracle import ref_cpu_gemm as R
+        if R.available():
+            rt = R.runtime(0)
+            ops = []
+            for e, start, rows in segs:
+                a_f = (w["a"][start:start + rows].float() * w["sfa"][start:start + rows].repeat_interleave(128, 1)).cpu()
+                a_bits = O.f32_to_bf16_bits(a_f.numpy())
+                b_q = w["b"][e].numpy()
+                s = w["sfb"][e].cpu().numpy()[:, 0].copy()   # cg_gemm takes one scale per output channel
+                ops.append((a_bits, b_q, s))
+                flops += 2.0 * rows * n * k
+            t0 = time.perf_counter()
+            for a_bits, b_q, s in ops:
+                R.gemm_bf16_int8_f32(a_bits, b_q, s, rt)
+            dt = time.perf_counter() - t0
+            return flops / dt / 1e12, f"{len(segs)} experts of this workload through cg_gemm ({R.backend_name()})", "reference", R.threads(rt)
+    ops = []
+    for e, start, rows in segs:
+        a_t = w["a"][start:start + rows]
+        b_t = w["b"][e]
+        if kind == "fp8":
+            a_f = a_t.float() * w["sfa"][start:start + rows].repeat_interleave(128, 1)[:, :k]
+            b_f = b_t.to(a_t.device).float() * w["sfb"][e].repeat_interleave(128, 0).repeat_interleave(128, 1)[:n, :k]
+        elif kind == "int8":
+            a_f = a_t.float() * w["sfa"][start:start + rows].repeat_interleave(128, 1)
+            b_f = b_t.to(a_t.device).float() * w["sfb"][e].repeat_interleave(128, 1)
+        else:
+            a_f, b_f = a_t.float(), b_t.to(a_t.device).float()
+        ops.append((a_f.to(torch.bfloat16).cpu(), b_f.to(torch.bfloat16).cpu()))
+        flops += 2.0 * rows * n * k
+    ops[0][0] @ ops[0][1].t()  # warm the thread pool
+    t0 = time.perf_counter()
+    for a_c, b_c in ops:
+        a_c @ b_c.t()
+    dt = time.perf_counter() - t0
+    return flops / dt / 1e12, f"{len(segs)} experts of this workload, torch CPU bf16 `a[s:e] @ w.t()` per expert", "port", threads
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c3_fp8", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--experts", type=int, default=0, help="shrink the expert count (tokens shrink in proportion); 0 = full size")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cfg = dict(WORKLOADS[args.workload])
+    if args.experts and args.experts < cfg["experts"]:
+        cfg["tokens"] = max(1, cfg["tokens"] * args.experts // cfg["experts"])
+        cfg["experts"] = args.experts
+    config = {"workload": f"{args.workload}: m-grouped contiguous {cfg['kind']} GEMM, {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
+                          f"{cfg['tokens']} tokens x top-{cfg['top_k']}, Zipf({cfg['zipf']}), B in pinned host DRAM",
+              "experts_per_gpu": cfg["experts"] // world, "l2": "inputs larger than L2 (weights are re-read from host memory every step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        return reference_arm(args, cfg, config)
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    import asymgemm_b200 as ag
+    from asymgemm_b200 import _lib
+
+    w = build_workload(cfg, rank, world, device)
+    lib = _lib.load()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # measured host-link peak (copy engine, pinned -> device), rank by rank so links are measured alone
+    peak = _lib.c_double(0.0)
+    _lib.check(lib.ag_measure_host_link(1 << 30, 3, peak))
+    link_peak = peak.value
+
+    for _ in range(args.warmup):
+        run_op(w)
+    ag.check_status()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_all0.record()
+    for s in range(args.steps):
+        evs[s][0].record()
+        run_op(w)
+        evs[s][1].record()
+    t_all1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ag.check_status()
+    total_ms = t_all0.elapsed_time(t_all1)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+
+    # end to end through the operator with host buffers: pinned A (+scales) in, D out, every step
+    a_host = w["a"].cpu().pin_memory()
+    sfa_host = w["sfa"].cpu().pin_memory() if w["sfa"] is not None else None
+    d_host = torch.empty(w["d"].shape, dtype=w["d"].dtype).pin_memory()
+    a_dev, d_dev = torch.empty_like(w["a"]), torch.empty_like(w["d"])
+    sfa_dev = torch.empty_like(w["sfa"]) if w["sfa"] is not None else None
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        if sfa_dev is not None:
+            sfa_dev.copy_(sfa_host, non_blocking=True)
+        run_op(w, a_dev, sfa_dev, d_dev)
+        d_host.copy_(d_dev, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(1, min(args.steps, 3))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    ag.check_status()
+
+    stats = torch.tensor([total_ms / args.steps, e2e_ms, kernel_ms, w["flops"], w["host_bytes"], link_peak], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        mn = stats.clone()
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        ms_step, e2e_ms, kernel_ms = mx[0].item(), mx[1].item(), mx[2].item()
+        flops, host_bytes = sm[3].item(), sm[4].item()
+        link_peak_sum, link_peak_min = sm[5].item(), mn[5].item()
+    else:
+        ms_step, flops, host_bytes = stats[0].item(), w["flops"], w["host_bytes"]
+        link_peak_sum = link_peak_min = link_peak
+
+    if rank == 0:
+        tflops = flops / (ms_step * 1e-3) / 1e12
+        host_gbs = host_bytes / (ms_step * 1e-3) / 1e9
+        # roofline of the one kernel in the step, on this rank's launch (rank 0) -- bound by the host link
+        ach = w["host_bytes"] / (kernel_ms * 1e-3) / 1e9
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except Exception:
+            pass
+        tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
+        line = {
+            "metric": "grouped-GEMM TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)",
+            "value": round(tflops, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {"fp8": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)", "int8": "int8 (int32 accumulate)"}[cfg["kind"]],
+            "data": "synthetic (seeded; shapes of the named config, random weights)",
+            "config": config,
+            "host_link": {"weight_gbs": round(host_gbs, 2), "peak_gbs_sum": round(link_peak_sum, 2),
+                          "frac_of_measured_peak": round(host_gbs / link_peak_sum, 4), "per_gpu_peak_min_gbs": round(link_peak_min, 2),
+                          "peak_how": "cudaMemcpyAsync pinned->device, 1 GiB, best of 3, measured in this run on each rank"},
+            "roofline": {"bound": "host_link", "achieved": round(ach, 2), "peak": round(link_peak, 2), "unit": "GB/s",
+                         "frac": round(ach / link_peak, 4), "traffic": None,
+                         "note": "algorithmic bytes = each active expert's weights once (N*K*bytes); the kernel is bound by the PCIe "
+                                 "host link, not HBM or tensor throughput: peak is the copy-engine rate measured in this run",
+                         "tensor_frac_of_measured": round(w["flops"] / (kernel_ms * 1e-3) / 1e12 / tensor_peak, 5)},
+            "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
+                    "h2d_bytes_per_step": int(a_host.numel() * a_host.element_size() + (sfa_host.numel() * 4 if sfa_host is not None else 0)),
+                    "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
+                    "note": "weights are read from pinned host memory inside the kernel in both timings"},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, sample, kind, cores = cpu_reference_sample(cfg, w, threads, max_experts=8)
+            line["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def reference_arm(args, cfg, config):
+    """--impl reference: the reference's CPU implementation of this path on the host cores (see cpu_reference_sample)."""
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    small = dict(cfg)
+    # operands for a bounded sample only: the first experts of the workload, same shapes and routing
+    small_experts = min(cfg["experts"], 8)
+    w = None
+    if device.type == "cuda":
+        small["tokens"] = max(1, cfg["tokens"] * small_experts // cfg["experts"])
+        small["experts"] = small_experts
+        w = build_workload(small, 0, 1, device)
+    else:
+        print(json.dumps({"impl": "reference", "unavailable": "operands are generated on the GPU; no CUDA device visible"}))
+        return 0
+    threads = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        v, sample, kind, cores = cpu_reference_sample(small, w, threads, max_experts=small_experts)
+        if i >= args.warmup:
+            vals.append(v)
+    v = sum(vals) / len(vals)
+    flops_step = sum(2.0 * s[2] * w["n"] * w["k"] for s in w["segs"][:small_experts])
+    line = {"impl": "reference", "metric": "grouped-GEMM TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)", "value": round(v, 4),
+            "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(flops_step / (v * 1e12) * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": cfg["kind"], "data": "synthetic (seeded)", "config": config,
+            "cpu_baseline": {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": round(v, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

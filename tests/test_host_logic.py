@@ -1,0 +1,102 @@
+"""Host-side logic without a GPU: quantisers against the reference's (golden fixtures), layout builder, argument checks,
+and the C ABI's exported symbols."""
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import asymgemm_b200 as ag
+from asymgemm_b200 import _lib
+from asymgemm_b200.utils import (build_contiguous_layout, get_tma_aligned_size, per_block_cast_to_fp8, per_channel_cast_to_int8,
+                                 per_token_cast_to_fp8, per_token_cast_to_int8, per_token_cast_to_nvfp4_e4m3)
+from oracle import oracle
+
+ROOT = Path(__file__).resolve().parents[1]
+GOLD = ROOT / "tests" / "golden"
+
+
+def _inputs():
+    g = np.load(GOLD / "inputs.npz")
+    return torch.from_numpy(g["x"].astype(np.float32)), torch.from_numpy(g["w"].astype(np.float32))
+
+
+@pytest.mark.parametrize("ue", [False, True])
+def test_fp8_quantisers_match_reference(ue):
+    x, w = _inputs()
+    g = np.load(GOLD / ("fp8_ue8m0_contiguous.npz" if ue else "fp8_fp32scale_contiguous.npz"))
+    q, s = per_token_cast_to_fp8(x, ue)
+    assert np.array_equal(q.view(torch.uint8).numpy(), g["a"]) and np.array_equal(s.numpy(), g["sfa"])
+    for i in range(w.shape[0]):
+        q, s = per_block_cast_to_fp8(w[i], ue)
+        assert np.array_equal(q.view(torch.uint8).numpy(), g["b"][i]) and np.array_equal(s.numpy(), g["sfb"][i])
+
+
+def test_int8_quantisers_match_reference():
+    x, w = _inputs()
+    g = np.load(GOLD / "int8_contiguous.npz")
+    q, s = per_token_cast_to_int8(x)
+    assert np.array_equal(q.numpy(), g["a"]) and np.array_equal(s.numpy(), g["sfa"])
+    q, s = per_channel_cast_to_int8(w[3])
+    assert np.array_equal(q.numpy(), g["b"][3]) and np.array_equal(s.numpy(), g["sfb"][3])
+
+
+def test_nvfp4_quantiser_matches_reference():
+    x, _ = _inputs()
+    g = np.load(GOLD / "fp4_contiguous.npz")
+    q, s = per_token_cast_to_nvfp4_e4m3(x)
+    assert np.array_equal(q.numpy(), g["a_math"]) and np.array_equal(s.view(torch.uint8).numpy(), g["sfa_math"])
+    # dequantising it reproduces x to within half an E2M1 step of the block scale
+    deq = oracle.dequant_nvfp4(q.numpy(), s.view(torch.uint8).numpy())
+    scale = np.repeat(oracle.decode_e4m3(s.view(torch.uint8).numpy()), 16, axis=1)
+    assert (np.abs(deq - x.numpy()) <= scale * 1.0 + 1e-6).all()
+
+
+def test_contiguous_layout_builder():
+    off, exp, list_size, total, segs = build_contiguous_layout([130, 0, 1, 256], device="cpu")
+    assert off.tolist() == [0, 256, 256, 384, 384, 640]
+    assert exp.tolist() == [0, 2, 3, -1] and list_size == 4 and total == 640
+    assert segs == [(0, 0, 130), (2, 256, 1), (3, 384, 256)]
+    assert oracle.contiguous_segments(off.tolist(), exp.tolist()) == [(0, 0, 256), (2, 256, 384), (3, 384, 640)]
+    assert oracle.contiguous_segments(off.tolist(), exp.tolist(), max_segments=1) == [(0, 0, 256)]
+    assert ag.get_mk_alignment_for_contiguous_layout() == 128
+    assert get_tma_aligned_size(5, 4) == 8 and get_tma_aligned_size(16, 1) == 16
+
+
+def test_argument_checks_raise_runtime_error_on_cpu_tensors():
+    a = torch.zeros((128, 512), dtype=torch.bfloat16)
+    b = torch.zeros((2, 128, 512), dtype=torch.bfloat16)
+    d = torch.zeros((128, 128), dtype=torch.bfloat16)
+    off = torch.zeros(4, dtype=torch.int32)
+    exp = torch.zeros(3, dtype=torch.int32)
+    with pytest.raises(RuntimeError):
+        ag.m_grouped_bf16_asym_gemm_nt_contiguous(a, b, d, off, exp, 1)  # nothing is on the GPU
+    with pytest.raises(RuntimeError):
+        ag.m_grouped_bf16_asym_gemm_nt_contiguous(a, b, d, off, exp, 1, transpose_b=True)
+    with pytest.raises(RuntimeError):
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((a, a), (b, b), d, off, exp, 1, recipe=(1, 1, 128))
+
+
+def test_shared_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "asymgemm_b200.h").read_text()
+    declared = set(re.findall(r"\b(ag_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = _lib.load()
+    missing = [name for name in sorted(declared) if not hasattr(lib, name)]
+    assert not missing, f"declared but not exported: {missing}"
+    assert declared == set(_lib.EXPORTS)
+    assert lib.ag_get_mk_alignment_for_contiguous_layout() == 128
+    assert b"sm_100a" in lib.ag_version()
+
+
+def test_c_abi_rejects_bad_descriptors_without_a_gpu():
+    lib = _lib.load()
+    desc = _lib.GemmDesc()
+    desc.layout = 7
+    assert lib.ag_m_grouped_bf16_gemm_nt(desc) == _lib.AG_E_INVALID
+    assert "layout" in _lib.last_error()
+    desc.layout = 0
+    desc.n, desc.k, desc.num_groups, desc.m = 128, 512, 2, 0
+    assert lib.ag_m_grouped_bf16_gemm_nt(desc) == _lib.AG_OK  # m == 0: nothing to do
+    assert lib.ag_fp4_sf_blocked_bytes(2, 130, 16) == 2 * 2 * 4 * 512
