@@ -52,6 +52,7 @@ class GemmDesc(Structure):
         ("timeout_ms", c_uint32),
         ("raw_dump", c_void_p),
         ("alpha", c_float),
+        ("tile_config", c_int32),
     ]
 
 

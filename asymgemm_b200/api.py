@@ -23,7 +23,7 @@ from . import _lib
 from ._lib import GemmDesc
 
 _MK_ALIGNMENT = 128
-_state = {"timeout_ms": 0, "use_scratch": True}
+_state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0}
 _scratch_cache: dict = {}
 _status_cache: dict = {}
 _dev_copy_cache: dict = {}
@@ -51,6 +51,11 @@ def get_num_sms() -> int:
 def set_wait_limit_ms(ms: int) -> None:
     """Bound (milliseconds) on every in-kernel barrier wait; 0 restores the default."""
     _state["timeout_ms"] = int(ms)
+
+
+def set_tile_config(tile: int) -> None:
+    """Force a tile configuration (see ``ag_gemm_desc_t.tile_config``); 0 = choose from where B lives."""
+    _state["tile_config"] = int(tile)
 
 
 def set_use_scratch(flag: bool) -> None:
@@ -178,6 +183,7 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
         desc.timeout_ms = _state["timeout_ms"]
         desc.raw_dump = raw_dump.data_ptr() if raw_dump is not None else None
         desc.alpha = alpha
+        desc.tile_config = _state["tile_config"]
         _lib.check(getattr(lib, fn_name)(desc))
 
 

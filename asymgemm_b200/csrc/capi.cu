@@ -182,7 +182,10 @@ int run(int kind, const ag_gemm_desc_t* g) {
   p.m_max = masked ? static_cast<int>(g->m) : 0;
   p.num_groups = g->num_groups;
   p.n = static_cast<int>(g->n);
-  p.n_tiles = static_cast<int>((g->n + agb::kBlockN - 1) / agb::kBlockN);
+  int tile = g->tile_config > 0 ? g->tile_config - 1 : (res == RES_HOST_MAPPED ? agb::kTileHost : agb::kTileDevice);
+  AG_REQUIRE(tile >= 0 && tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
+  const int bn = agb::kTileConfigs[tile].bn, ka = agb::kTileConfigs[tile].ka;
+  p.n_tiles = static_cast<int>((g->n + bn - 1) / bn);
   p.kb_count = static_cast<int>((kbytes + 127) / 128);
   p.sf_k = static_cast<int>((g->k + 127) / 128);
   p.sfb_rows = kind == 1 ? static_cast<int>((g->n + 127) / 128) : static_cast<int>(g->n);
@@ -194,23 +197,23 @@ int run(int kind, const ag_gemm_desc_t* g) {
   const int grid = static_cast<int>(items < grid_cap ? items : grid_cap);
   if (grid <= 0) return AG_OK;
 
-  const uint64_t kpad = static_cast<uint64_t>(p.kb_count) * 128;
-  const uint64_t need = static_cast<uint64_t>(grid) * agb::kBlockN * kpad;
+  const uint64_t kpad = static_cast<uint64_t>((p.kb_count + ka - 1) / ka) * ka * 128;
+  const uint64_t need = static_cast<uint64_t>(grid) * bn * kpad;
   p.use_scratch = (g->scratch != nullptr && g->scratch_bytes >= need) ? 1 : 0;
   if (g->scratch != nullptr)
     AG_REQUIRE((reinterpret_cast<uintptr_t>(g->scratch) & 1023) == 0, "scratch must be 1024-byte aligned");
 
   CUtensorMap ma, mb, ms;
   if (int rc = encode_bytes_2d(&ma, g->a, kbytes, static_cast<uint64_t>(rows_total), kbytes, 128, "a")) return rc;
-  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * g->num_groups, kbytes, agb::kBlockN, "b")) return rc;
+  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * g->num_groups, kbytes, bn, "b")) return rc;
   if (p.use_scratch) {
-    if (int rc = encode_bytes_2d(&ms, g->scratch, kpad, static_cast<uint64_t>(grid) * agb::kBlockN, kpad, agb::kBlockN, "scratch")) return rc;
+    if (int rc = encode_bytes_2d(&ms, g->scratch, kpad, static_cast<uint64_t>(grid) * bn, kpad, bn, "scratch")) return rc;
   } else {
     ms = mb;
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(g->stream);
-  cudaError_t e = agb::launch_mgrouped(kind, grid, stream, ma, mb, ms, p);
+  cudaError_t e = agb::launch_mgrouped(kind, tile, grid, stream, ma, mb, ms, p);
   if (e != cudaSuccess) return fail(AG_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return AG_OK;
 }
@@ -245,8 +248,9 @@ uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms) {
   if (sms <= 0) {
     if (device_sm_count(&sms) != AG_OK) sms = 148;
   }
-  const uint64_t kpad = (k_bytes_of(kind, k) + 127) / 128 * 128;
-  return static_cast<uint64_t>(sms) * agb::kBlockN * kpad;
+  // large enough for every tile configuration: 128 rows per CTA, K padded to 8 atoms
+  const uint64_t kpad = (k_bytes_of(kind, k) + 1023) / 1024 * 1024;
+  return static_cast<uint64_t>(sms) * 128 * kpad;
 }
 
 int ag_read_status(const int32_t* status_dev, void* stream, int32_t* out) {

@@ -1,6 +1,6 @@
-// Instantiates the grouped-GEMM kernel for FP8 operands.
+// Instantiates the grouped-GEMM kernel for FP8 operands, one kernel per tile configuration.
 #include "launch.cuh"
 
 namespace agb {
-cudaError_t launch_fp8(AGB_LAUNCH_ARGS) { return launch_kind_impl<Kind::FP8>(grid, stream, ma, mb, ms, p); }
+cudaError_t launch_fp8(AGB_LAUNCH_ARGS) { return launch_kind_impl<Kind::FP8>(tile, grid, stream, ma, mb, ms, p); }
 }  // namespace agb

@@ -6,21 +6,34 @@
 
 namespace agb {
 
-constexpr int kBlockN = 128;   // output columns per item
-constexpr int kStagesA = 4;    // activation ring depth (16 KB stages)
-constexpr int kStagesB = 8;    // weight ring depth (16 KB stages): 128 KB of host reads in flight per CTA
+// Tile configurations. BN = output columns (= weight rows) per item, KA = 128-byte K atoms per weight stage,
+// SB = weight ring depth. Every configuration keeps 128 KB of weight reads in flight per CTA and a 64 KB
+// activation ring (SA = 4 stages of 128 rows x 128 B).
+struct TileConfig {
+  int bn, ka, sb;
+};
+constexpr int kNumTileConfigs = 4;
+constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
+    {128, 1, 8},  // 0: B resident in device memory (tensor-core efficiency)
+    {32, 4, 8},   // 1: B streamed from host memory, fewest host pages in flight per CTA
+    {32, 8, 4},   // 2: as 1 with longer contiguous runs per row
+    {64, 2, 8},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
+};
+constexpr int kStagesA = 4;
+constexpr int kTileDevice = 0;
+constexpr int kTileHost = 3;
 
-// One instantiation per dtype lives in its own translation unit (inst_*.cu).
-#define AGB_LAUNCH_ARGS int grid, cudaStream_t stream, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &ms, const GemmParams &p
+#define AGB_LAUNCH_ARGS int tile, int grid, cudaStream_t stream, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &ms, const GemmParams &p
+// One instantiation set per dtype lives in its own translation unit (inst_*.cu).
 cudaError_t launch_bf16(AGB_LAUNCH_ARGS);
 cudaError_t launch_fp8(AGB_LAUNCH_ARGS);
 cudaError_t launch_int8(AGB_LAUNCH_ARGS);
 
-template <Kind KIND>
-cudaError_t launch_kind_impl(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb,
-                             const CUtensorMap& ms, const GemmParams& p) {
-  using L = SmemLayout<kBlockN, kStagesA, kStagesB>;
-  auto kernel = mgrouped_gemm_kernel<KIND, kBlockN, kStagesA, kStagesB>;
+template <Kind KIND, int BN, int KA, int SB>
+cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ms,
+                       const GemmParams& p) {
+  using L = SmemLayout<BN, KA, kStagesA, SB>;
+  auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -34,12 +47,22 @@ cudaError_t launch_kind_impl(int grid, cudaStream_t stream, const CUtensorMap& m
   return cudaGetLastError();
 }
 
-inline cudaError_t launch_mgrouped(int kind, int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb,
-                                   const CUtensorMap& ms, const GemmParams& p) {
+template <Kind KIND>
+cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
+  switch (tile) {
+    case 0: return launch_one<KIND, 128, 1, 8>(grid, stream, ma, mb, ms, p);
+    case 1: return launch_one<KIND, 32, 4, 8>(grid, stream, ma, mb, ms, p);
+    case 2: return launch_one<KIND, 32, 8, 4>(grid, stream, ma, mb, ms, p);
+    case 3: return launch_one<KIND, 64, 2, 8>(grid, stream, ma, mb, ms, p);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+inline cudaError_t launch_mgrouped(int kind, AGB_LAUNCH_ARGS) {
   switch (kind) {
-    case 0: return launch_bf16(grid, stream, ma, mb, ms, p);
-    case 1: return launch_fp8(grid, stream, ma, mb, ms, p);
-    case 2: return launch_int8(grid, stream, ma, mb, ms, p);
+    case 0: return launch_bf16(tile, grid, stream, ma, mb, ms, p);
+    case 1: return launch_fp8(tile, grid, stream, ma, mb, ms, p);
+    case 2: return launch_int8(tile, grid, stream, ma, mb, ms, p);
     default: return cudaErrorInvalidValue;
   }
 }

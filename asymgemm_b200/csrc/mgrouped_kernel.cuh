@@ -14,6 +14,11 @@
 //     TMA store of the very shared-memory stage the MMA consumes (no second trip over the host link);
 //   * no atomics, no partial sums in D: every output element is written once, from fp32.
 //
+// Tile shape is chosen by where B lives. Streaming from the host, throughput drops once the rows being streamed at
+// the same time (CTAs x BN) spread over more than a few thousand 4 KB host pages (measured: 148 CTAs x 128 rows ->
+// 44.5 GB/s, 148 x 32 rows -> 51.4 GB/s of a 55.6 GB/s copy-engine peak), so host-resident B uses BN = 32 with
+// KA = several 128-byte K atoms per stage; device-resident B uses BN = 128, KA = 1 for tensor-core efficiency.
+//
 // Warp roles (256 threads): warp 0 = B producer (+ scratch spill), warp 1 = A producer,
 // warp 2 = TMEM allocator + single-thread tcgen05.mma issuer, warp 3 idle, warps 4-7 = TMEM drain.
 //
@@ -153,14 +158,15 @@ constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
 constexpr int NUM_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 
-template <int BN, int SA, int SB>
+template <int BN, int KA, int SA, int SB>
 struct SmemLayout {
   static constexpr int a_stage = BM * ATOM_BYTES;
-  static constexpr int b_stage = BN * ATOM_BYTES;
+  static constexpr int b_box = BN * ATOM_BYTES;       // one TMA box: BN rows x 128 bytes of K
+  static constexpr int b_stage = b_box * KA;          // KA K-adjacent boxes per stage
   static constexpr int a_off = 0;
   static constexpr int b_off = a_off + SA * a_stage;
   static constexpr int bar_off = b_off + SB * b_stage;
-  static constexpr int num_bars = 2 * SA + 2 * SB + 8 + 1;
+  static constexpr int num_bars = 2 * SA + 2 * SB + 32 + 1;
   static constexpr int sfb_off = bar_off + num_bars * 8;          // 4 warps x BN floats (INT8 column scales)
   static constexpr int misc_off = sfb_off + 4 * BN * 4;           // tmem base, abort flag
   static constexpr int total = misc_off + 16;
@@ -199,16 +205,17 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
   }
 }
 
-template <Kind KIND, int BN, int SA, int SB>
+template <Kind KIND, int BN, int KA, int SA, int SB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
   using T = KindTraits<KIND>;
-  using L = SmemLayout<BN, SA, SB>;
-  static_assert(BN == 128, "the TMEM plan below assumes 128-column accumulators");
-  // TMEM plan: 4 slots of BN columns. Hardware-accumulated kinds keep up to 4 output tiles; software-scaled
-  // kinds keep 2 scaled fp32 tiles (slots 0,1) and double-buffer the raw per-K-block product (slots 2,3).
-  constexpr int CHUNK_TILES = T::sw_scale ? 2 : 4;
+  using L = SmemLayout<BN, KA, SA, SB>;
+  static_assert(BN == 32 || BN == 64 || BN == 128, "BN must be 32, 64 or 128");
+  // TMEM plan: 512 / BN slots of BN columns. Hardware-accumulated kinds keep one output tile per slot; software-scaled
+  // kinds keep scaled fp32 tiles in slots [0, CHUNK_TILES) and double-buffer the raw per-K-block product in the last two.
+  constexpr int NUM_SLOTS = TMEM_COLS / BN;
+  constexpr int CHUNK_TILES = T::sw_scale ? NUM_SLOTS - 2 : NUM_SLOTS;
   constexpr uint32_t IDESC = make_idesc(T::d_fmt, T::ab_fmt, BN);
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
 
@@ -221,9 +228,9 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint64_t* a_empty = a_full + SA;
   uint64_t* b_full = a_empty + SA;
   uint64_t* b_empty = b_full + SB;
-  uint64_t* tm_full = b_empty + SB;   // [4]  bf16: per accumulator slot; sw_scale: [0..1] = raw slots
-  uint64_t* tm_empty = tm_full + 4;   // [4]
-  uint64_t* done_bar = tm_empty + 4;  // MMA thread drains its own pipeline through this one on abort
+  uint64_t* tm_full = b_empty + SB;    // [16] hardware-accumulated: per accumulator slot; sw_scale: [0..1] = raw slots
+  uint64_t* tm_empty = tm_full + 16;   // [16]
+  uint64_t* done_bar = tm_empty + 16;  // MMA thread drains its own pipeline through this one on abort
   float* sfb_smem = reinterpret_cast<float*>(smem + L::sfb_off);
   uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(smem + L::misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
@@ -234,7 +241,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (threadIdx.x == 0) {
     for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], 4); }
+    for (int i = 0; i < 16; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], 4); }
     mbar_init(done_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -251,7 +258,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_smem;
   const WaitCtx wc{p.status, abort_flag, p.timeout_ns};
-  const int kb_count = p.kb_count;
+  const int kb_count = p.kb_count;                       // 128-byte K atoms
+  const int ks_count = (kb_count + KA - 1) / KA;         // B stages along K
 
   if (warp == 0) {
     // ===================================================================== B producer (+ scratch spill)
@@ -274,33 +282,44 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (uint32_t q = first; q < jt && ok; ++q) ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
         }
         const uint32_t jt_item = jt;
+        // Copy stage `q` (K stage index `ks_i` of this item) from shared memory to this CTA's scratch rows.
+        auto spill_stage = [&](uint32_t q, int ks_i) -> bool {
+          if (!wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL)) return false;
+#pragma unroll
+          for (int bx = 0; bx < KA; ++bx)
+            tma_store_2d(&tmap_s, smem_b + (q % SB) * L::b_stage + bx * L::b_box, (ks_i * KA + bx) * ATOM_BYTES, s_row);
+          bulk_commit_group();
+          return true;
+        };
         for (int chunk = 0; chunk < chunks && ok; ++chunk) {
           const bool from_scratch = spill && chunk > 0;
           if (spill && chunk == 1) bulk_wait_group0();  // the scratch copy is complete and visible
           int next_store = 0;
-          for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+          for (int ks = 0; ks < ks_count && ok; ++ks, ++jt) {
             const uint32_t s = jt % SB;
             ok = wait_bar(&b_empty[s], ((jt / SB) & 1) ^ 1, wc, ST_TIMEOUT_B_EMPTY);
             if (!ok) break;
             if (spill && chunk == 0) bulk_wait_group_read0();  // earlier spill stores have finished reading their stages
             mbar_arrive_expect_tx(&b_full[s], L::b_stage);
-            if (from_scratch) tma_load_2d(smem_b + s * L::b_stage, &tmap_s, &b_full[s], kb * ATOM_BYTES, s_row);
-            else if (p.b_streaming) tma_load_2d_hint(smem_b + s * L::b_stage, &tmap_b, &b_full[s], kb * ATOM_BYTES, b_row, pol_stream);
-            else tma_load_2d(smem_b + s * L::b_stage, &tmap_b, &b_full[s], kb * ATOM_BYTES, b_row);
+#pragma unroll
+            for (int bx = 0; bx < KA; ++bx) {
+              // boxes past the end of K lie wholly outside the tensor and arrive as zeros
+              uint8_t* dst = smem_b + s * L::b_stage + bx * L::b_box;
+              const int c0 = (ks * KA + bx) * ATOM_BYTES;
+              if (from_scratch) tma_load_2d(dst, &tmap_s, &b_full[s], c0, s_row);
+              else if (p.b_streaming) tma_load_2d_hint(dst, &tmap_b, &b_full[s], c0, b_row, pol_stream);
+              else tma_load_2d(dst, &tmap_b, &b_full[s], c0, b_row);
+            }
             if (spill && chunk == 0) {
-              while (next_store + SPILL_DELAY <= kb && ok) {
-                const uint32_t q = jt_item + next_store;
-                ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
-                if (ok) { tma_store_2d(&tmap_s, smem_b + (q % SB) * L::b_stage, next_store * ATOM_BYTES, s_row); bulk_commit_group(); }
+              while (next_store + SPILL_DELAY <= ks && ok) {
+                ok = spill_stage(jt_item + next_store, next_store);
                 ++next_store;
               }
             }
           }
           if (spill && chunk == 0) {
-            while (next_store < kb_count && ok) {
-              const uint32_t q = jt_item + next_store;
-              ok = wait_bar(&b_full[q % SB], (q / SB) & 1, wc, ST_TIMEOUT_B_FULL);
-              if (ok) { tma_store_2d(&tmap_s, smem_b + (q % SB) * L::b_stage, next_store * ATOM_BYTES, s_row); bulk_commit_group(); }
+            while (next_store < ks_count && ok) {
+              ok = spill_stage(jt_item + next_store, next_store);
               ++next_store;
             }
           }
@@ -352,11 +371,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mtiles = (it.rows + BM - 1) / BM;
         for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
           const int mc = min(CHUNK_TILES, mtiles - m0);
-          for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+          for (int kb = 0; kb < kb_count && ok; ++kb) {
             const uint32_t sb = jt % SB;
-            ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+            const int bx = kb % KA;
+            if (bx == 0) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
             if (!ok) break;
-            const uint32_t b_addr = smem_u32(smem_b + sb * L::b_stage);
+            const uint32_t b_addr = smem_u32(smem_b + sb * L::b_stage + bx * L::b_box);
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
               const uint32_t sa = it_a % SA;
               ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
@@ -388,7 +408,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
               }
             }
-            if (ok) umma_commit(&b_empty[sb]);
+            if (ok && (bx == KA - 1 || kb == kb_count - 1)) {
+              umma_commit(&b_empty[sb]);
+              ++jt;
+            }
           }
           if constexpr (!T::sw_scale) slot_phase ^= (1u << mc) - 1u;
         }

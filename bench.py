@@ -214,6 +214,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--experts", type=int, default=0, help="shrink the expert count (tokens shrink in proportion); 0 = full size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
+    ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -242,6 +244,9 @@ def main():
 
     w = build_workload(cfg, rank, world, device)
     lib = _lib.load()
+    ag.set_tile_config(args.tile)
+    if args.sms:
+        ag.set_num_sms(args.sms)
 
     def barrier():
         if world > 1:

@@ -74,6 +74,9 @@ typedef struct ag_gemm_desc {
   uint32_t timeout_ms; /* bound on every in-kernel wait; 0 = default (4000 ms) */
   int32_t* raw_dump;   /* int8 only, optional: device int32 [ceil(K/128), rows, N], the exact block sums */
   float alpha;         /* nvfp4 only: product of the two tensor-level scales; 0 is read as 1 */
+  int32_t tile_config; /* 0 = choose from where b lives; 1.. = force tile configuration (tuning / tests):
+                          1 = 128 columns per item (device-resident b), 2 = 32 columns x 512 B of K per stage
+                          (host-resident b), 3 = 32 x 1024 B, 4 = 64 x 256 B */
 } ag_gemm_desc_t;
 
 /* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked

@@ -73,12 +73,23 @@ def test_contiguous_small(kind, b_on_host):
     _check(kind, d.float().cpu().numpy(), c["ref"], c["segments"])
 
 
+@pytest.fixture
+def tile(request):
+    """Forces one tile configuration for the test (0 = chosen from where B lives)."""
+    ag.set_tile_config(request.param)
+    yield request.param
+    ag.set_tile_config(0)
+
+
 @pytest.mark.parametrize("kind", KINDS)
-def test_contiguous_ragged_multi_tile(kind):
-    """Ragged row counts, empty experts, segments longer than one accumulator chunk (scratch replay), N and K tails."""
-    rows = [300, 0, 1, 129, 0, 1100, 64, 513]
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4], indirect=True)
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_contiguous_ragged_multi_tile(kind, tile, b_on_host):
+    """Ragged row counts, empty experts, segments longer than one accumulator chunk in every tile configuration
+    (scratch replay), N and K tails; every tile configuration with B on the host and on the device."""
+    rows = [300, 0, 1, 129, 0, 2300, 64, 513]
     n, k = 392, 640
-    c = H.make_contiguous_case(kind, rows, n, k, seed=2)
+    c = H.make_contiguous_case(kind, rows, n, k, seed=2, b_on_host=b_on_host)
     d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
     _run_contiguous(c, d)
     torch.cuda.synchronize()
@@ -86,9 +97,10 @@ def test_contiguous_ragged_multi_tile(kind):
 
 
 @pytest.mark.parametrize("kind", KINDS)
-def test_contiguous_no_scratch_matches(kind):
+@pytest.mark.parametrize("tile", [1, 2], indirect=True)
+def test_contiguous_no_scratch_matches(kind, tile):
     """Without scratch, long segments re-read B instead; the result must be bit-identical."""
-    rows = [700, 260]
+    rows = [2500, 260]
     n, k = 256, 512
     c = H.make_contiguous_case(kind, rows, n, k, seed=3)
     d1 = torch.zeros((c["m_total"], n), dtype=torch.bfloat16, device="cuda")
@@ -105,7 +117,8 @@ def test_contiguous_no_scratch_matches(kind):
 
 
 @pytest.mark.parametrize("kind", KINDS)
-def test_masked(kind):
+@pytest.mark.parametrize("tile", [0, 1, 3], indirect=True)
+def test_masked(kind, tile):
     """Masked layout incl. an empty group and a full group (reference case: tests/m_grouped/...:320-342)."""
     masked_m = [64, 0, 96, 384, 1]
     m_max, n, k = 384, 256, 512
