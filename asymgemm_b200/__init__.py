@@ -10,6 +10,8 @@ from .api import (  # noqa: F401
     get_num_sms,
     m_grouped_bf16_asym_gemm_nt_contiguous,
     m_grouped_bf16_asym_gemm_nt_masked,
+    m_grouped_fp4_asym_gemm_nt_contiguous,
+    m_grouped_fp4_asym_gemm_nt_masked,
     m_grouped_fp8_asym_gemm_nt_contiguous,
     m_grouped_fp8_asym_gemm_nt_masked,
     m_grouped_int8_asym_gemm_nt_contiguous,

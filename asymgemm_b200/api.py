@@ -310,3 +310,86 @@ def m_grouped_int8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recip
         return
     _launch(_lib.KIND_INT8, "ag_m_grouped_int8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
             masked_m=masked_m, m=m, n=n, k=k, g=g, raw_dump=raw_accumulators)
+
+
+# --------------------------------------------------------------------------------------------- NVFP4
+_blocked_cache: dict = {}
+
+
+def _fp4_blocked(sf: torch.Tensor, groups: int, rows: int, k16: int, device: torch.device, cache: bool) -> torch.Tensor:
+    """Scales [groups, rows, k16] (e4m3 / uint8 bytes, CUDA or pinned host) -> blocked device buffer for the kernel.
+
+    Weight scales are converted once and cached until the source tensor changes; activation scales every call
+    (the reference re-lays both on every call, csrc/apis/gemm.hpp:271-290).
+    """
+    lib = _lib.load()
+    key = (sf.data_ptr(), tuple(sf.shape), device.index)
+    if cache:
+        hit = _blocked_cache.get(key)
+        if hit is not None and hit[0] == sf._version:
+            return hit[1]
+    nbytes = int(lib.ag_fp4_sf_blocked_bytes(groups, rows, k16))
+    out = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _lib.check(lib.ag_fp4_sf_to_blocked(sf.data_ptr(), out.data_ptr(), groups, rows, k16,
+                                            torch.cuda.current_stream(device).cuda_stream))
+    if cache:
+        if len(_blocked_cache) > 256:
+            _blocked_cache.clear()
+        _blocked_cache[key] = (sf._version, out)
+    return out
+
+
+def _fp4_prepare(a, b, d, masked: bool, recipe):
+    a_q, sfa = a
+    b_q, sfb = b
+    g, m, n, k = _common_checks(a_q, b_q, d, masked=masked, k_div=2)
+    _require(a_q.dtype == torch.uint8 and b_q.dtype == torch.uint8, "a and b must be packed E2M1 in uint8 (two values per byte)")
+    if recipe is not None:
+        _require(tuple(recipe) == (1, 1, 16), f"Unknown SF transformation for recipe {tuple(recipe)}")
+    for t in (sfa, sfb):
+        _require(t.dtype in (torch.float8_e4m3fn, torch.uint8), "NVFP4 scales must be float8_e4m3fn (or their uint8 bytes)")
+    _require(k % 32 == 0, "k must be a multiple of 32")
+    k16 = k // 16
+    rows_shape = (g, m) if masked else (m,)
+    _require(tuple(sfa.shape) == (*rows_shape, k16), f"sfa must be {(*rows_shape, k16)}, got {tuple(sfa.shape)}")
+    _require(tuple(sfb.shape) == (g, n, k16), f"sfb must be {(g, n, k16)}, got {tuple(sfb.shape)}")
+    _require(sfa.is_cuda and sfa.is_contiguous(), "sfa must be a contiguous CUDA tensor")
+    _require(sfb.is_contiguous() and (sfb.is_cuda or sfb.is_pinned()), "sfb must be contiguous and on CUDA or pinned")
+    if masked:
+        _require(m % 128 == 0, "masked NVFP4 needs M_max to be a multiple of 128")
+    return g, m, n, k, k16
+
+
+def m_grouped_fp4_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=None, recipe=None, compiled_dims: str = "nk",
+                                          disable_ue8m0_cast: bool = True, *, alpha: float = 1.0) -> None:
+    """NVFP4 (packed E2M1 + one E4M3 scale per 16 elements), bf16 out (csrc/apis/gemm.hpp:237-300).
+
+    ``alpha`` (extension): product of the tensor-level fp32 scales, applied to the fp32 accumulator before rounding.
+    Every segment must start on a multiple of 128 rows (the contiguous layout's alignment).
+    """
+    g, m, n, k, k16 = _fp4_prepare(a, b, d, False, recipe)
+    _check_index_tensors(offsets, experts, g)
+    if m == 0:
+        return
+    dev = a[0].device
+    sfa_b = _fp4_blocked(a[1], 1, m, k16, dev, cache=False)
+    sfb_b = _fp4_blocked(b[1], g, n, k16, dev, cache=True)
+    segs = _list_size_to_segments(list_size, offsets, experts)
+    _launch(_lib.KIND_NVFP4, "ag_m_grouped_fp4_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
+            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, alpha=alpha)
+
+
+def m_grouped_fp4_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk",
+                                      disable_ue8m0_cast: bool = True, *, alpha: float = 1.0) -> None:
+    """Masked NVFP4 (csrc/apis/gemm.hpp:302-365)."""
+    g, m, n, k, k16 = _fp4_prepare(a, b, d, True, recipe)
+    _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
+             "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
+    if m == 0 or expected_m == 0:
+        return
+    dev = a[0].device
+    sfa_b = _fp4_blocked(a[1], 1, g * m, k16, dev, cache=False)
+    sfb_b = _fp4_blocked(b[1], g, n, k16, dev, cache=True)
+    _launch(_lib.KIND_NVFP4, "ag_m_grouped_fp4_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
+            masked_m=masked_m, m=m, n=n, k=k, g=g, alpha=alpha)

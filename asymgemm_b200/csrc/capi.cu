@@ -140,7 +140,6 @@ int run(int kind, const ag_gemm_desc_t* g) {
   if (masked) AG_REQUIRE(g->masked_m != nullptr, "masked layout needs masked_m");
   else AG_REQUIRE(g->offsets != nullptr && g->experts != nullptr, "contiguous layout needs offsets and experts");
   if (kind == 1 || kind == 2 || kind == 3) AG_REQUIRE(g->sfa != nullptr && g->sfb != nullptr, "quantised kinds need sfa and sfb");
-  if (kind == 3) return fail(AG_E_UNSUPPORTED, "nvfp4 kernel is not built into this library yet");
 
   const uint64_t kbytes = k_bytes_of(kind, g->k);
   AG_REQUIRE(kbytes % 16 == 0, "K must make rows a multiple of 16 bytes (row bytes %llu)", static_cast<unsigned long long>(kbytes));
@@ -184,11 +183,16 @@ int run(int kind, const ag_gemm_desc_t* g) {
   p.n = static_cast<int>(g->n);
   int tile = g->tile_config > 0 ? g->tile_config - 1 : (res == RES_HOST_MAPPED ? agb::kTileHost : agb::kTileDevice);
   AG_REQUIRE(tile >= 0 && tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
-  const int bn = agb::kTileConfigs[tile].bn, ka = agb::kTileConfigs[tile].ka;
+  if (kind == 3) {
+    AG_REQUIRE(agb::kTileConfigs[tile].bn >= 64, "nvfp4 supports tile_config 1 and 4 only (64 or 128 columns per item)");
+    AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
+    if (masked) AG_REQUIRE(g->m % 128 == 0, "nvfp4 masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
+  }
+  const int bn = agb::tile_config_of(kind, tile).bn, ka = agb::tile_config_of(kind, tile).ka;
   p.n_tiles = static_cast<int>((g->n + bn - 1) / bn);
   p.kb_count = static_cast<int>((kbytes + 127) / 128);
-  p.sf_k = static_cast<int>((g->k + 127) / 128);
-  p.sfb_rows = kind == 1 ? static_cast<int>((g->n + 127) / 128) : static_cast<int>(g->n);
+  p.sf_k = kind == 3 ? static_cast<int>(agb::fp4_sf_k4_padded_host((g->k + 15) / 16)) : static_cast<int>((g->k + 127) / 128);
+  p.sfb_rows = kind == 2 ? static_cast<int>(g->n) : static_cast<int>((g->n + 127) / 128);
   p.d_fp32 = g->d_dtype == AG_D_FP32;
   p.b_streaming = res == RES_HOST_MAPPED;
   p.alpha = g->alpha == 0.f ? 1.f : g->alpha;
@@ -275,12 +279,19 @@ int32_t ag_get_mk_alignment_for_contiguous_layout(void) { return 128; }
 
 uint64_t ag_fp4_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t k16) {
   const uint64_t row_tiles = static_cast<uint64_t>((rows + 127) / 128);
-  const uint64_t k4 = static_cast<uint64_t>((k16 + 3) / 4);
+  const uint64_t k4 = static_cast<uint64_t>(agb::fp4_sf_k4_padded_host(k16));
   return static_cast<uint64_t>(groups) * row_tiles * k4 * 512;
 }
 
-int ag_fp4_sf_to_blocked(const void*, void*, int64_t, int64_t, int64_t, void*) {
-  return fail(AG_E_UNSUPPORTED, "nvfp4 kernel is not built into this library yet");
+int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t rows, int64_t k16, void* stream) {
+  AG_REQUIRE(src != nullptr && dst != nullptr && groups > 0 && rows > 0 && k16 > 0, "bad arguments");
+  const void* src_dev = src;
+  if (classify(src, &src_dev) == RES_UNREACHABLE)
+    return fail(AG_E_NOT_MAPPED, "scale tensor (%p) is neither device memory nor pinned/registered host memory", src);
+  AG_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dst must be 16-byte aligned");
+  cudaError_t e = agb::fp4_sf_to_blocked(src_dev, dst, groups, rows, k16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(AG_E_CUDA, "scale re-layout launch failed: %s", cudaGetErrorString(e));
+  return AG_OK;
 }
 
 int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out) {

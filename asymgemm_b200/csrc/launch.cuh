@@ -19,6 +19,10 @@ constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
     {32, 8, 4},   // 2: as 1 with longer contiguous runs per row
     {64, 2, 8},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
 };
+// NVFP4 also stages 2 KB of scale factors per K atom and operand, so its host-streaming configuration uses
+// single-atom stages in a deeper ring to stay inside the 227 KB of shared memory.
+constexpr TileConfig kTileFp4Host = {64, 1, 12};
+constexpr TileConfig tile_config_of(int kind, int tile) { return (kind == 3 && tile == 3) ? kTileFp4Host : kTileConfigs[tile]; }
 constexpr int kStagesA = 4;
 constexpr int kTileDevice = 0;
 constexpr int kTileHost = 3;
@@ -28,11 +32,15 @@ constexpr int kTileHost = 3;
 cudaError_t launch_bf16(AGB_LAUNCH_ARGS);
 cudaError_t launch_fp8(AGB_LAUNCH_ARGS);
 cudaError_t launch_int8(AGB_LAUNCH_ARGS);
+cudaError_t launch_fp4(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
+cudaError_t fp4_sf_to_blocked(const void* src, void* dst, long long groups, long long rows, long long k16, cudaStream_t stream);
+long long fp4_sf_k4_padded_host(long long k16);
 
 template <Kind KIND, int BN, int KA, int SB>
 cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ms,
                        const GemmParams& p) {
-  using L = SmemLayout<BN, KA, kStagesA, SB>;
+  using L = SmemLayout<BN, KA, kStagesA, SB, KindTraits<KIND>::block_scaled>;
+  static_assert(L::dyn_bytes <= 232448, "tile configuration does not fit in shared memory");
   auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB>;
   static bool configured[64] = {};
   int dev = 0;
@@ -63,6 +71,7 @@ inline cudaError_t launch_mgrouped(int kind, AGB_LAUNCH_ARGS) {
     case 0: return launch_bf16(tile, grid, stream, ma, mb, ms, p);
     case 1: return launch_fp8(tile, grid, stream, ma, mb, ms, p);
     case 2: return launch_int8(tile, grid, stream, ma, mb, ms, p);
+    case 3: return launch_fp4(tile, grid, stream, ma, mb, ms, p);
     default: return cudaErrorInvalidValue;
   }
 }

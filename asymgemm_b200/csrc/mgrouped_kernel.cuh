@@ -65,8 +65,8 @@ struct GemmParams {
   int n;
   int n_tiles;             // ceil(N / BN)
   int kb_count;            // ceil(K bytes / 128)
-  int sf_k;                // scale blocks along K (FP8/INT8: ceil(K/128))
-  int sfb_rows;            // FP8: ceil(N/128); INT8: N
+  int sf_k;                // scale blocks along K (FP8/INT8: ceil(K/128); NVFP4: padded count of 64-element blocks)
+  int sfb_rows;            // FP8: ceil(N/128); INT8: N; NVFP4: ceil(N/128)
   int d_fp32;
   int use_scratch;         // 1 = replay long segments from the scratch copy, 0 = re-read B from its source
   int b_streaming;         // 1 = B is host memory: mark its lines evict-first in L2
@@ -137,19 +137,30 @@ template <>
 struct KindTraits<Kind::BF16> {
   static constexpr MmaKind mma = MmaKind::F16;
   static constexpr bool sw_scale = false;
+  static constexpr bool block_scaled = false;
   static constexpr uint32_t d_fmt = 1, ab_fmt = 1;
 };
 template <>
 struct KindTraits<Kind::FP8> {
   static constexpr MmaKind mma = MmaKind::F8F6F4;
   static constexpr bool sw_scale = true;
+  static constexpr bool block_scaled = false;
   static constexpr uint32_t d_fmt = 1, ab_fmt = 0;
 };
 template <>
 struct KindTraits<Kind::INT8> {
   static constexpr MmaKind mma = MmaKind::I8;
   static constexpr bool sw_scale = true;
+  static constexpr bool block_scaled = false;
   static constexpr uint32_t d_fmt = 2, ab_fmt = 1;
+};
+// NVFP4: the tensor core applies one UE4M3 scale per 16 elements of K to each operand; scales are read from TMEM.
+template <>
+struct KindTraits<Kind::NVFP4> {
+  static constexpr MmaKind mma = MmaKind::F16;  // unused: block-scaled MMAs are issued through umma_nvfp4
+  static constexpr bool sw_scale = false;
+  static constexpr bool block_scaled = true;
+  static constexpr uint32_t d_fmt = 1, ab_fmt = 1;
 };
 
 constexpr int BM = 128;            // rows per MMA tile
@@ -157,15 +168,25 @@ constexpr int ATOM_BYTES = 128;    // bytes of K per pipeline stage row (one 128
 constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
 constexpr int NUM_THREADS = 256;
 constexpr int TMEM_COLS = 512;
+// NVFP4 scale factors. One tcgen05.mma covers 64 elements of K = 4 scales per row; the scales of 128 rows for one
+// MMA form a 512-byte block laid out as byte (r % 32) * 16 + (r / 32) * 4 + c, which tcgen05.cp (32x128b.warpx4)
+// turns into 4 TMEM columns. One 128-byte K atom (256 elements) needs 4 such blocks per operand = 2 KB.
+constexpr int SF_BLOCK_BYTES = 512;
+constexpr int SF_ATOM_BYTES = 4 * SF_BLOCK_BYTES;
+constexpr int SF_TMEM_COLS = 64;   // A: 2 x 16 columns, B: 2 x 16 columns (double-buffered)
 
-template <int BN, int KA, int SA, int SB>
+template <int BN, int KA, int SA, int SB, bool HAS_SF = false>
 struct SmemLayout {
   static constexpr int a_stage = BM * ATOM_BYTES;
   static constexpr int b_box = BN * ATOM_BYTES;       // one TMA box: BN rows x 128 bytes of K
   static constexpr int b_stage = b_box * KA;          // KA K-adjacent boxes per stage
   static constexpr int a_off = 0;
   static constexpr int b_off = a_off + SA * a_stage;
-  static constexpr int bar_off = b_off + SB * b_stage;
+  static constexpr int sfa_stage = HAS_SF ? SF_ATOM_BYTES : 0;
+  static constexpr int sfb_stage = HAS_SF ? SF_ATOM_BYTES * KA : 0;
+  static constexpr int sfa_off = b_off + SB * b_stage;
+  static constexpr int sfb2_off = sfa_off + SA * sfa_stage;
+  static constexpr int bar_off = sfb2_off + SB * sfb_stage;
   static constexpr int num_bars = 2 * SA + 2 * SB + 32 + 1;
   static constexpr int sfb_off = bar_off + num_bars * 8;          // 4 warps x BN floats (INT8 column scales)
   static constexpr int misc_off = sfb_off + 4 * BN * 4;           // tmem base, abort flag
@@ -210,19 +231,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
   using T = KindTraits<KIND>;
-  using L = SmemLayout<BN, KA, SA, SB>;
+  using L = SmemLayout<BN, KA, SA, SB, T::block_scaled>;
   static_assert(BN == 32 || BN == 64 || BN == 128, "BN must be 32, 64 or 128");
+  static_assert(!T::block_scaled || BN >= 64, "block-scaled kinds need BN >= 64");
   // TMEM plan: 512 / BN slots of BN columns. Hardware-accumulated kinds keep one output tile per slot; software-scaled
   // kinds keep scaled fp32 tiles in slots [0, CHUNK_TILES) and double-buffer the raw per-K-block product in the last two.
-  constexpr int NUM_SLOTS = TMEM_COLS / BN;
+  constexpr int NUM_SLOTS = (TMEM_COLS - (T::block_scaled ? SF_TMEM_COLS : 0)) / BN;
   constexpr int CHUNK_TILES = T::sw_scale ? NUM_SLOTS - 2 : NUM_SLOTS;
-  constexpr uint32_t IDESC = make_idesc(T::d_fmt, T::ab_fmt, BN);
+  constexpr uint32_t IDESC = T::block_scaled ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);
+  constexpr uint32_t SF_COL0 = NUM_SLOTS * BN;   // first TMEM column of the scale-factor area
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
 
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* smem_a = smem + L::a_off;
   uint8_t* smem_b = smem + L::b_off;
+  uint8_t* smem_sfa = smem + L::sfa_off;
+  uint8_t* smem_sfb = smem + L::sfb2_off;
+  const uint8_t* sfa_blocked = reinterpret_cast<const uint8_t*>(p.sfa);
+  const uint8_t* sfb_blocked = reinterpret_cast<const uint8_t*>(p.sfb);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
   uint64_t* a_full = bars;
   uint64_t* a_empty = a_full + SA;
@@ -300,7 +327,13 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             ok = wait_bar(&b_empty[s], ((jt / SB) & 1) ^ 1, wc, ST_TIMEOUT_B_EMPTY);
             if (!ok) break;
             if (spill && chunk == 0) bulk_wait_group_read0();  // earlier spill stores have finished reading their stages
-            mbar_arrive_expect_tx(&b_full[s], L::b_stage);
+            mbar_arrive_expect_tx(&b_full[s], L::b_stage + L::sfb_stage);
+            if constexpr (T::block_scaled) {
+              // scales of this stage: KA x 2 KB, contiguous in the blocked layout (the K direction is padded)
+              const long long tile128 = static_cast<long long>(it.expert) * p.sfb_rows + ((it.nt * BN) >> 7);
+              bulk_load_1d(smem_sfb + s * L::sfb_stage,
+                           sfb_blocked + (tile128 * p.sf_k + static_cast<long long>(ks) * KA * 4) * SF_BLOCK_BYTES, L::sfb_stage, &b_full[s]);
+            }
 #pragma unroll
             for (int bx = 0; bx < KA; ++bx) {
               // boxes past the end of K lie wholly outside the tensor and arrive as zeros
@@ -348,8 +381,14 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               const uint32_t s = it_a % SA;
               ok = wait_bar(&a_empty[s], ((it_a / SA) & 1) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
               if (!ok) break;
-              mbar_arrive_expect_tx(&a_full[s], L::a_stage);
-              tma_load_2d(smem_a + s * L::a_stage, &tmap_a, &a_full[s], kb * ATOM_BYTES, it.row0 + (m0 + mt) * BM);
+              mbar_arrive_expect_tx(&a_full[s], L::a_stage + L::sfa_stage);
+              const int a_row = it.row0 + (m0 + mt) * BM;
+              if constexpr (T::block_scaled) {
+                bulk_load_1d(smem_sfa + s * L::sfa_stage,
+                             sfa_blocked + (static_cast<long long>(a_row >> 7) * p.sf_k + static_cast<long long>(kb) * 4) * SF_BLOCK_BYTES,
+                             L::sfa_stage, &a_full[s]);
+              }
+              tma_load_2d(smem_a + s * L::a_stage, &tmap_a, &a_full[s], kb * ATOM_BYTES, a_row);
             }
           }
         }
@@ -393,12 +432,29 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               if (!ok) break;
               tc_fence_after_sync();
               const uint32_t a_addr = smem_u32(smem_a + sa * L::a_stage);
+              uint32_t sfa_col = 0, sfb_col = 0;
+              if constexpr (T::block_scaled) {
+                // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
+                sfa_col = SF_COL0 + (it_a & 1) * 16;
+                sfb_col = SF_COL0 + 32 + (kb & 1) * 16;
+                const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
+                if (mt == 0) {
+                  const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + bx * SF_ATOM_BYTES);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
+                }
+                // a 64-row weight tile uses half of its 128-row scale block: words 0-1 or 2-3 of each lane
+                if constexpr (BN == 64) sfb_col += ((it.nt & 1) ? 2 : 0);
+              }
 #pragma unroll
               for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
                 const uint64_t da = make_kmajor_sw128_desc(a_addr + j * MMA_K_BYTES);
                 const uint64_t db = make_kmajor_sw128_desc(b_addr + j * MMA_K_BYTES);
                 const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
-                umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+                if constexpr (T::block_scaled) umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
+                else umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
               }
               umma_commit(&a_empty[sa]);
               if constexpr (T::sw_scale) {
@@ -518,6 +574,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               uint32_t r[32];
               tmem_ld_32x32b_x32(lane_addr + mt * BN + cc * 32, r);
               tmem_wait_ld();
+              if constexpr (T::block_scaled) {
+                if (p.alpha != 1.f) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
+                }
+              }
               if (valid) store_row32(p, grow, n0 + cc * 32, r);
             }
             tc_fence_before_sync();

@@ -95,7 +95,10 @@ int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc);
  * (csrc/apis/gemm.hpp:569-630; kernel asym_gemm/include/asym_gemm/impls/sm90_int8_asym_gemm_1d1d.cuh:34-41). */
 int ag_m_grouped_int8_gemm_nt(const ag_gemm_desc_t* desc);
 
-/* NVFP4: packed E2M1 values, one UE4M3 scale per 16 elements of K. Replaces
+/* NVFP4: packed E2M1 values, one UE4M3 scale per 16 elements of K. For this entry point `sfa` and `sfb` are DEVICE
+ * buffers in the blocked layout produced by ag_fp4_sf_to_blocked (sfa: groups = 1, rows = all rows of A;
+ * sfb: groups = G, rows = N); k must be a multiple of 32, every segment must start on a multiple of 128 rows and,
+ * in the masked layout, M_max must be a multiple of 128. Replaces
  * m_grouped_fp4_asym_gemm_nt_contiguous / _masked (csrc/apis/gemm.hpp:237-300, 302-365; kernel
  * asym_gemm/include/asym_gemm/impls/sm100_fp4_asym_gemm_1d1d.cuh:44-51). */
 int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc);

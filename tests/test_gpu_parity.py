@@ -59,7 +59,12 @@ def _check(kind, d_rows: np.ndarray, ref: np.ndarray, segments, poison_rows_unto
     assert df <= TOL_DIFF[kind], f"{kind}: calc_diff {df:.3e} > {TOL_DIFF[kind]}"
 
 
-KINDS = ["bf16", "fp8", "int8"]
+KINDS = ["bf16", "fp8", "int8", "fp4"]
+
+
+def _skip_unsupported(kind, tile):
+    if kind == "fp4" and tile in (2, 3):
+        pytest.skip("NVFP4 has 64- and 128-column tile configurations only")
 
 
 @pytest.mark.parametrize("kind", KINDS)
@@ -87,6 +92,7 @@ def tile(request):
 def test_contiguous_ragged_multi_tile(kind, tile, b_on_host):
     """Ragged row counts, empty experts, segments longer than one accumulator chunk in every tile configuration
     (scratch replay), N and K tails; every tile configuration with B on the host and on the device."""
+    _skip_unsupported(kind, tile)
     rows = [300, 0, 1, 129, 0, 2300, 64, 513]
     n, k = 392, 640
     c = H.make_contiguous_case(kind, rows, n, k, seed=2, b_on_host=b_on_host)
@@ -100,6 +106,7 @@ def test_contiguous_ragged_multi_tile(kind, tile, b_on_host):
 @pytest.mark.parametrize("tile", [1, 2], indirect=True)
 def test_contiguous_no_scratch_matches(kind, tile):
     """Without scratch, long segments re-read B instead; the result must be bit-identical."""
+    _skip_unsupported(kind, tile)
     rows = [2500, 260]
     n, k = 256, 512
     c = H.make_contiguous_case(kind, rows, n, k, seed=3)
@@ -120,6 +127,7 @@ def test_contiguous_no_scratch_matches(kind, tile):
 @pytest.mark.parametrize("tile", [0, 1, 3], indirect=True)
 def test_masked(kind, tile):
     """Masked layout incl. an empty group and a full group (reference case: tests/m_grouped/...:320-342)."""
+    _skip_unsupported(kind, tile)
     masked_m = [64, 0, 96, 384, 1]
     m_max, n, k = 384, 256, 512
     c = H.make_masked_case(kind, masked_m, m_max, n, k, seed=4)

@@ -99,4 +99,4 @@ def test_c_abi_rejects_bad_descriptors_without_a_gpu():
     desc.layout = 0
     desc.n, desc.k, desc.num_groups, desc.m = 128, 512, 2, 0
     assert lib.ag_m_grouped_bf16_gemm_nt(desc) == _lib.AG_OK  # m == 0: nothing to do
-    assert lib.ag_fp4_sf_blocked_bytes(2, 130, 16) == 2 * 2 * 4 * 512
+    assert lib.ag_fp4_sf_blocked_bytes(2, 130, 16) == 2 * 2 * 32 * 512  # 2 groups x 2 row tiles x K runs padded to 32
