@@ -15,6 +15,7 @@ Differences from the reference, all on the permissive side:
 """
 from __future__ import annotations
 
+import weakref
 from typing import Optional, Tuple, Union
 
 import torch
@@ -102,18 +103,35 @@ def _scratch(kind: int, n: int, k: int, device: torch.device) -> Optional[torch.
     return t[off:off + need]
 
 
+def _cache_get(cache: dict, t: torch.Tensor, device: torch.device):
+    """Entries are tied to the identity of the source tensor object (a weak reference), its in-place version counter
+    and its address: a new tensor that happens to reuse a freed tensor's memory never hits."""
+    hit = cache.get((id(t), device.index))
+    if hit is not None and hit[0]() is t and hit[1] == t._version and hit[2] == t.data_ptr():
+        return hit[3]
+    return None
+
+
+def _cache_put(cache: dict, t: torch.Tensor, device: torch.device, value) -> None:
+    key = (id(t), device.index)
+    if len(cache) > 512:
+        for k in [k for k, v in cache.items() if v[0]() is None]:
+            del cache[k]
+        if len(cache) > 512:
+            cache.clear()
+    cache[key] = (weakref.ref(t), t._version, t.data_ptr(), value)
+
+
 def _device_copy(t: torch.Tensor, device: torch.device) -> torch.Tensor:
-    """Device-resident copy of a small host tensor (weight scales), cached until the source changes."""
+    """Device-resident copy of a small host tensor (weight scales), cached while the same tensor object is passed
+    again unmodified."""
     if t.is_cuda:
         return t
-    key = (t.data_ptr(), tuple(t.shape), t.dtype, device.index)
-    hit = _dev_copy_cache.get(key)
-    if hit is not None and hit[0] == t._version:
-        return hit[1]
+    hit = _cache_get(_dev_copy_cache, t, device)
+    if hit is not None:
+        return hit
     dev = t.to(device, non_blocking=t.is_pinned())
-    if len(_dev_copy_cache) > 256:
-        _dev_copy_cache.clear()
-    _dev_copy_cache[key] = (t._version, dev)
+    _cache_put(_dev_copy_cache, t, device, dev)
     return dev
 
 
@@ -323,20 +341,17 @@ def _fp4_blocked(sf: torch.Tensor, groups: int, rows: int, k16: int, device: tor
     (the reference re-lays both on every call, csrc/apis/gemm.hpp:271-290).
     """
     lib = _lib.load()
-    key = (sf.data_ptr(), tuple(sf.shape), device.index)
     if cache:
-        hit = _blocked_cache.get(key)
-        if hit is not None and hit[0] == sf._version:
-            return hit[1]
+        hit = _cache_get(_blocked_cache, sf, device)
+        if hit is not None:
+            return hit
     nbytes = int(lib.ag_fp4_sf_blocked_bytes(groups, rows, k16))
     out = torch.empty(nbytes, dtype=torch.uint8, device=device)
     with torch.cuda.device(device):
         _lib.check(lib.ag_fp4_sf_to_blocked(sf.data_ptr(), out.data_ptr(), groups, rows, k16,
                                             torch.cuda.current_stream(device).cuda_stream))
     if cache:
-        if len(_blocked_cache) > 256:
-            _blocked_cache.clear()
-        _blocked_cache[key] = (sf._version, out)
+        _cache_put(_blocked_cache, sf, device, out)
     return out
 
 

@@ -100,3 +100,25 @@ def test_c_abi_rejects_bad_descriptors_without_a_gpu():
     desc.n, desc.k, desc.num_groups, desc.m = 128, 512, 2, 0
     assert lib.ag_m_grouped_bf16_gemm_nt(desc) == _lib.AG_OK  # m == 0: nothing to do
     assert lib.ag_fp4_sf_blocked_bytes(2, 130, 16) == 2 * 2 * 32 * 512  # 2 groups x 2 row tiles x K runs padded to 32
+
+
+def test_weight_scale_cache_is_tied_to_the_tensor_object():
+    """A new tensor that reuses a freed tensor's address must not be served the old tensor's cached copy."""
+    from asymgemm_b200 import api
+
+    cache: dict = {}
+    dev = torch.device("cpu")
+    dev = type("D", (), {"index": 0})()
+    t1 = torch.zeros(8)
+    api._cache_put(cache, t1, dev, "copy-of-t1")
+    assert api._cache_get(cache, t1, dev) == "copy-of-t1"
+    t1.add_(1)                                   # in-place change bumps the version counter
+    assert api._cache_get(cache, t1, dev) is None
+    api._cache_put(cache, t1, dev, "copy-of-t1-v2")
+    t2 = torch.zeros(8)
+    assert api._cache_get(cache, t2, dev) is None
+    key = (id(t1), 0)
+    del t1                                       # entry stays but can never match another object
+    fake = torch.ones(8)
+    cache[(id(fake), 0)] = cache.pop(key)
+    assert api._cache_get(cache, fake, dev) is None
