@@ -1,0 +1,238 @@
+"""Expert-parallel FP8 MoE layer: experts sharded evenly over the ranks of one node, each rank's expert weights in
+pinned host memory on its own host link, tokens exchanged with all-to-all over NCCL.
+
+This is the multi-GPU form of the asymmetric grouped GEMM. The reference's own multi-GPU modes are 2-GPU training
+paths (asym_gemm/training/ep_vanilla.py:140-282 gathers every rank's tokens and reduce-scatters partial outputs);
+here tokens go only to the rank that owns their expert and weights never leave their rank:
+
+    route -> counts all-to-all -> token all-to-all(v) (fp8 rows + 1x128 scales) -> local contiguous layout
+          -> gate+up grouped GEMM -> SiLU(gate)*up -> 1x128 requantisation -> down grouped GEMM
+          -> all-to-all(v) back (bf16 rows) -> router-weighted sum over top-k
+
+`EPDispatcher` holds the routing arithmetic and the two exchanges; it is device-agnostic (CPU tensors + gloo in the
+tests, CUDA tensors + NCCL in production). `ExpertParallelMoE` adds the weights and the two grouped GEMMs.
+The activation between the GEMMs follows the reference's CPU MoE bucket: silu(gate) * up rounded to bf16
+(csrc/cpu/module.cpp:337-347), gate = first `inter` output columns, up = the second `inter`.
+"""
+from __future__ import annotations
+
+import ctypes
+import mmap
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+ALIGN = 128
+
+
+@dataclass
+class DispatchState:
+    """Everything `combine` needs to send results back and undo the permutations of `dispatch`."""
+    order: torch.Tensor          # [T*k] positions of the (token, slot) pairs sorted by expert
+    send_splits: List[int]       # rows sent to each rank
+    recv_splits: List[int]       # rows received from each rank
+    dest_rows: torch.Tensor      # [R] row of every received row in the padded contiguous layout
+    rows_per_expert: List[int]   # valid rows of every local expert
+    padded_rows: int             # rows of the contiguous layout (every expert padded to 128)
+    offsets: torch.Tensor        # int32 [2*S] (start, end) pairs, S = local experts with rows
+    experts: torch.Tensor        # int32 [S+1], ends in -1
+    tokens: int
+    top_k: int
+
+
+class EPDispatcher:
+    """Token routing for expert parallelism over one process group (expert e lives on rank e // experts_per_rank)."""
+
+    def __init__(self, num_experts: int, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if num_experts % self.world != 0:
+            raise RuntimeError(f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
+        self.num_experts = num_experts
+        self.experts_per_rank = num_experts // self.world
+
+    # ------------------------------------------------------------------ collectives (identity at world size 1)
+    def _all_to_all(self, out: torch.Tensor, inp: torch.Tensor, out_splits=None, in_splits=None) -> None:
+        if self.world == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
+
+    def plan(self, topk_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Sort the (token, slot) pairs by expert and exchange per-expert counts.
+
+        Returns (order [T*k], send_counts int32 [world, experts_per_rank], recv_counts int32 [world, experts_per_rank]),
+        recv_counts[s, j] = rows rank s sends to this rank's local expert j.
+        """
+        flat = topk_ids.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        send_counts = torch.bincount(flat, minlength=self.num_experts).to(torch.int32).view(self.world, self.experts_per_rank)
+        recv_counts = torch.empty_like(send_counts)
+        self._all_to_all(recv_counts, send_counts.contiguous())
+        return order, send_counts, recv_counts
+
+    def layout(self, recv_counts_host: torch.Tensor, device) -> Tuple[torch.Tensor, List[int], int, torch.Tensor, torch.Tensor]:
+        """Contiguous layout of the received rows: grouped by local expert, each expert padded to 128 rows.
+
+        Received rows arrive ordered by (source rank, expert). Returns (dest_rows [R], rows_per_expert, padded_rows,
+        offsets, experts) with dest_rows[i] = row of received row i in the padded layout.
+        """
+        rc = recv_counts_host.to(torch.int64)                      # [world, epr] on the host
+        per_expert = rc.sum(dim=0)                                  # [epr]
+        padded = (per_expert + ALIGN - 1) // ALIGN * ALIGN
+        expert_start = torch.cumsum(padded, 0) - padded             # [epr]
+        within = torch.cumsum(rc, 0) - rc                           # rows of expert j that come from lower ranks
+        block_dest = (expert_start.unsqueeze(0) + within).reshape(-1)   # [world*epr], source-major like the recv order
+        block_len = rc.reshape(-1)
+        block_recv = torch.cumsum(block_len, 0) - block_len
+        total = int(block_len.sum())
+        shift = torch.repeat_interleave(block_dest - block_recv, block_len, output_size=total)
+        dest_rows = (shift + torch.arange(total)).to(device)
+        offsets, experts = [], []
+        for j in range(self.experts_per_rank):
+            if per_expert[j] > 0:
+                offsets += [int(expert_start[j]), int(expert_start[j] + padded[j])]
+                experts.append(j)
+        experts.append(-1)
+        return (dest_rows, per_expert.tolist(), int(padded.sum()),
+                torch.tensor(offsets, dtype=torch.int32, device=device), torch.tensor(experts, dtype=torch.int32, device=device))
+
+    def dispatch(self, rows: torch.Tensor, topk_ids: torch.Tensor, extras: Tuple[torch.Tensor, ...] = ()):
+        """Send every (token, slot) pair's row to the rank that owns its expert.
+
+        rows [T, H] (any dtype; FP8 rows travel as bytes), extras: more per-token tensors [T, *] sent alongside (scales).
+        Returns (state, recv_rows [R, H], recv_extras). One host synchronisation (the split sizes).
+        """
+        tokens, top_k = topk_ids.shape
+        order, send_counts, recv_counts = self.plan(topk_ids)
+        counts_host = torch.stack([send_counts, recv_counts]).cpu()
+        send_splits = counts_host[0].sum(dim=1).tolist()
+        recv_splits = counts_host[1].sum(dim=1).tolist()
+        total_recv = int(sum(recv_splits))
+        src_token = torch.div(order, top_k, rounding_mode="floor")
+        outs = []
+        for t in (rows,) + tuple(extras):
+            as_bytes = t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+            send = as_bytes.index_select(0, src_token)
+            recv = torch.empty((total_recv,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+            self._all_to_all(recv, send, recv_splits, send_splits)
+            outs.append(recv.view(t.dtype) if t.dtype == torch.float8_e4m3fn else recv)
+        dest_rows, per_expert, padded_rows, offsets, experts = self.layout(counts_host[1], rows.device)
+        state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k)
+        return state, outs[0], tuple(outs[1:])
+
+    def combine(self, expert_out: torch.Tensor, state: DispatchState, topk_weights: torch.Tensor) -> torch.Tensor:
+        """expert_out [padded_rows, H] (contiguous layout) -> y [T, H] = sum_k w[t, k] * out(t, k), in fp32, as expert_out.dtype."""
+        back = expert_out.index_select(0, state.dest_rows)
+        ret = torch.empty((state.tokens * state.top_k, back.shape[1]), dtype=back.dtype, device=back.device)
+        self._all_to_all(ret, back, state.send_splits, state.recv_splits)
+        pairs = torch.empty_like(ret)
+        pairs.index_copy_(0, state.order, ret)
+        y = (pairs.view(state.tokens, state.top_k, -1).float() * topk_weights.unsqueeze(-1).float()).sum(dim=1)
+        return y.to(expert_out.dtype)
+
+
+def to_contiguous_layout(recv: torch.Tensor, state: DispatchState) -> torch.Tensor:
+    """Scatter received rows into the zero-padded contiguous layout the grouped GEMM consumes."""
+    as_bytes = recv.view(torch.uint8) if recv.dtype == torch.float8_e4m3fn else recv
+    out = torch.zeros((state.padded_rows,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=recv.device)
+    out.index_copy_(0, state.dest_rows, as_bytes)
+    return out.view(recv.dtype) if recv.dtype == torch.float8_e4m3fn else out
+
+
+# --------------------------------------------------------------------------------------------- pinned weights
+_keepalive: list = []
+
+
+def pinned_empty(shape, dtype: torch.dtype, numa_node: Optional[int] = None) -> torch.Tensor:
+    """Pinned host tensor for expert weights, optionally bound to one NUMA node.
+
+    With `numa_node`: anonymous mmap -> mbind(MPOL_BIND) -> cudaHostRegister, the recipe the reference uses for its
+    NUMA-bound slabs (asym_gemm/unified_moe/runtime.py:236-279); any failure falls back to torch's pinned allocator.
+    Pages are faulted in on first write, so fill the tensor from a thread running on that node.
+    """
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    if numa_node is not None and numa_node >= 0:
+        try:
+            nbytes = max(1, numel * torch.empty((), dtype=dtype).element_size())
+            mm = mmap.mmap(-1, nbytes)
+            addr = ctypes.addressof(ctypes.c_char.from_buffer(mm))
+            libc = ctypes.CDLL(None, use_errno=True)
+            mask = ctypes.c_ulong(1 << numa_node)
+            if libc.syscall(237, ctypes.c_void_p(addr), ctypes.c_size_t(nbytes), 2, ctypes.byref(mask), 65, 0) != 0:
+                raise OSError("mbind failed")
+            rc = torch.cuda.cudart().cudaHostRegister(addr, nbytes, 0)
+            if int(rc) != 0:
+                raise OSError(f"cudaHostRegister returned {rc}")
+            _keepalive.append(mm)
+            return torch.frombuffer(mm, dtype=dtype, count=numel).view(*shape)
+        except Exception:
+            pass
+    return torch.empty(*shape, dtype=dtype).pin_memory()
+
+
+def gpu_numa_node(device_index: int) -> int:
+    """NUMA node of the GPU's PCIe root, or -1 when the platform does not say (single-node VMs)."""
+    try:
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        devid = torch.cuda.get_device_properties(device_index).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{devid:02x}.0/numa_node"
+        with open(path) as f:
+            return int(f.read().strip())
+    except Exception:
+        return -1
+
+
+# --------------------------------------------------------------------------------------------- the layer
+def silu_mul_requant(d1: torch.Tensor, inter: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [M, 2*inter] -> (fp8 [M, inter], fp32 scales [M, inter/128]): silu(gate) * up, rounded to bf16, then 1x128 FP8."""
+    from .utils import per_token_cast_to_fp8
+    gate, up = d1[:, :inter].float(), d1[:, inter:].float()
+    act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+    return per_token_cast_to_fp8(act.float(), use_ue8m0=False)
+
+
+class ExpertParallelMoE:
+    """FP8 MoE layer (gate+up, SiLU*mul, down) with this rank's experts in pinned host memory.
+
+    w13: (fp8 [E_local, 2*inter, hidden] pinned, fp32 block scales [E_local, 2*inter/128, hidden/128])
+    w2:  (fp8 [E_local, hidden, inter] pinned,   fp32 block scales [E_local, hidden/128, inter/128])
+    """
+
+    def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None):
+        self.dispatcher = EPDispatcher(num_experts, group)
+        self.hidden, self.inter = hidden, inter
+        self.w13, self.w2 = w13, w2
+        epr = self.dispatcher.experts_per_rank
+        if tuple(w13[0].shape) != (epr, 2 * inter, hidden) or tuple(w2[0].shape) != (epr, hidden, inter):
+            raise RuntimeError("weight shapes do not match (experts_per_rank, 2*inter, hidden) / (experts_per_rank, hidden, inter)")
+
+    def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState) -> torch.Tensor:
+        """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]."""
+        from . import api
+        m = state.padded_rows
+        dev = a_q.device
+        d1 = torch.empty((m, 2 * self.inter), dtype=torch.bfloat16, device=dev)
+        d2 = torch.zeros((m, self.hidden), dtype=torch.bfloat16, device=dev)
+        if m == 0:
+            return d2
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), self.w13, d1, state.offsets, state.experts, None)
+        a2, s2 = silu_mul_requant(d1, self.inter)
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), self.w2, d2, state.offsets, state.experts, None)
+        return d2
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
+        from .utils import per_token_cast_to_fp8
+        x_q, sfx = per_token_cast_to_fp8(x.float(), use_ue8m0=False)
+        state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
+        a_q = to_contiguous_layout(recv_q, state)
+        sfa = to_contiguous_layout(recv_s, state)
+        out = self.experts_forward(a_q, sfa, state)
+        return self.dispatcher.combine(out, state, topk_weights)

@@ -34,6 +34,8 @@ WORKLOADS = {
     "c3_fp8": dict(kind="fp8", experts=256, k=7168, n=4096, tokens=16384, top_k=8, zipf=0.8),
     "c2_bf16": dict(kind="bf16", experts=128, k=2048, n=1536, tokens=8192, top_k=8, zipf=1.0),
     "c1_int8": dict(kind="int8", experts=16, k=2048, n=1536, tokens=2048, top_k=4, zipf=0.0),
+    # whole FP8 MoE layer, expert-parallel: gate+up (K=hidden, N=2*inter), SiLU*mul, down (K=inter, N=hidden)
+    "c5_moe_fp8": dict(kind="moe", experts=256, hidden=7168, inter=2048, tokens=65536, top_k=8),
 }
 ELEM_BYTES = {"fp8": 1.0, "bf16": 2.0, "int8": 1.0, "fp4": 0.5}
 
@@ -100,7 +102,42 @@ def build_workload(cfg, rank, world, device, seed=0):
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
 
 
+def build_moe(cfg, rank, world, device, group, seed=0):
+    """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
+    GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing."""
+    from asymgemm_b200 import ep
+    from asymgemm_b200.utils import per_block_cast_to_fp8
+    e_total, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
+    epr = e_total // world
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    node = ep.gpu_numa_node(device.index)
+    w13 = ep.pinned_empty((epr, 2 * i, h), torch.float8_e4m3fn, node)
+    w2 = ep.pinned_empty((epr, h, i), torch.float8_e4m3fn, node)
+    s13 = torch.empty((epr, 2 * i // 128, h // 128), dtype=torch.float32, device=device)
+    s2 = torch.empty((epr, h // 128, i // 128), dtype=torch.float32, device=device)
+    for e in range(epr):
+        q, s = per_block_cast_to_fp8(torch.randn((2 * i, h), device=device, generator=gen) * 0.02, use_ue8m0=False)
+        w13[e].copy_(q, non_blocking=True)
+        s13[e] = s
+        q, s = per_block_cast_to_fp8(torch.randn((h, i), device=device, generator=gen) * 0.02, use_ue8m0=False)
+        w2[e].copy_(q, non_blocking=True)
+        s2[e] = s
+    torch.cuda.synchronize(device)
+    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group)
+    t_local = cfg["tokens"] // world
+    x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
+    logits = torch.randn((t_local, e_total), device=device, generator=gen)
+    topk_w, topk_ids = torch.topk(torch.softmax(logits, dim=-1), cfg["top_k"], dim=-1)
+    topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
+    rows = t_local * cfg["top_k"]
+    return dict(kind="moe", layer=layer, x=x, ids=topk_ids, w=topk_w, numa_node=node,
+                flops=float(rows) * 2.0 * (2 * i * h + h * i), host_bytes=float(epr) * (2 * i * h + h * i),
+                nvlink_bytes=float(rows) * (h + h // 128 * 4 + 2 * h))
+
+
 def run_op(w, a=None, sfa=None, d=None):
+    if w["kind"] == "moe":
+        return w["layer"].forward(w["x"] if a is None else a, w["ids"], w["w"])
     import asymgemm_b200 as ag
     a = w["a"] if a is None else a
     sfa = w["sfa"] if sfa is None else sfa
@@ -225,9 +262,15 @@ def main():
     if args.experts and args.experts < cfg["experts"]:
         cfg["tokens"] = max(1, cfg["tokens"] * args.experts // cfg["experts"])
         cfg["experts"] = args.experts
-    config = {"workload": f"{args.workload}: m-grouped contiguous {cfg['kind']} GEMM, {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
-                          f"{cfg['tokens']} tokens x top-{cfg['top_k']}, Zipf({cfg['zipf']}), B in pinned host DRAM",
-              "experts_per_gpu": cfg["experts"] // world, "l2": "inputs larger than L2 (weights are re-read from host memory every step)"}
+    if cfg["kind"] == "moe":
+        desc = (f"{args.workload}: FP8 MoE layer (gate+up K={cfg['hidden']} N={2 * cfg['inter']}, SiLU*mul, down K={cfg['inter']} "
+                f"N={cfg['hidden']}), {cfg['experts']} experts sharded over the ranks, {cfg['tokens']} tokens x top-{cfg['top_k']} "
+                f"(softmax of N(0,1) logits), token all-to-all over NCCL, weights in pinned host DRAM per rank")
+    else:
+        desc = (f"{args.workload}: m-grouped contiguous {cfg['kind']} GEMM, {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
+                f"{cfg['tokens']} tokens x top-{cfg['top_k']}, Zipf({cfg['zipf']}), B in pinned host DRAM")
+    config = {"workload": desc, "experts_per_gpu": cfg["experts"] // world,
+              "l2": "inputs larger than L2 (weights are re-read from host memory every step)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -242,7 +285,8 @@ def main():
     import asymgemm_b200 as ag
     from asymgemm_b200 import _lib
 
-    w = build_workload(cfg, rank, world, device)
+    moe = cfg["kind"] == "moe"
+    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device)
     lib = _lib.load()
     ag.set_tile_config(args.tile)
     if args.sms:
@@ -280,18 +324,27 @@ def main():
     kernel_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
 
     # end to end through the operator with host buffers: pinned A (+scales) in, D out, every step
-    a_host = w["a"].cpu().pin_memory()
-    sfa_host = w["sfa"].cpu().pin_memory() if w["sfa"] is not None else None
-    d_host = torch.empty(w["d"].shape, dtype=w["d"].dtype).pin_memory()
-    a_dev, d_dev = torch.empty_like(w["a"]), torch.empty_like(w["d"])
-    sfa_dev = torch.empty_like(w["sfa"]) if w["sfa"] is not None else None
+    if moe:
+        a_host, sfa_host = w["x"].cpu().pin_memory(), None
+        d_host = torch.empty(w["x"].shape, dtype=torch.bfloat16).pin_memory()
+        a_dev = torch.empty_like(w["x"])
 
-    def e2e_step():
-        a_dev.copy_(a_host, non_blocking=True)
-        if sfa_dev is not None:
-            sfa_dev.copy_(sfa_host, non_blocking=True)
-        run_op(w, a_dev, sfa_dev, d_dev)
-        d_host.copy_(d_dev, non_blocking=True)
+        def e2e_step():
+            a_dev.copy_(a_host, non_blocking=True)
+            d_host.copy_(run_op(w, a_dev), non_blocking=True)
+    else:
+        a_host = w["a"].cpu().pin_memory()
+        sfa_host = w["sfa"].cpu().pin_memory() if w["sfa"] is not None else None
+        d_host = torch.empty(w["d"].shape, dtype=w["d"].dtype).pin_memory()
+        a_dev, d_dev = torch.empty_like(w["a"]), torch.empty_like(w["d"])
+        sfa_dev = torch.empty_like(w["sfa"]) if w["sfa"] is not None else None
+
+        def e2e_step():
+            a_dev.copy_(a_host, non_blocking=True)
+            if sfa_dev is not None:
+                sfa_dev.copy_(sfa_host, non_blocking=True)
+            run_op(w, a_dev, sfa_dev, d_dev)
+            d_host.copy_(d_dev, non_blocking=True)
 
     e2e_step()
     barrier()
@@ -330,12 +383,13 @@ def main():
             peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
         except Exception:
             pass
-        tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
+        tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0, "moe": 2.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
         line = {
             "metric": "grouped-GEMM TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)",
             "value": round(tflops, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": {"fp8": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)", "int8": "int8 (int32 accumulate)"}[cfg["kind"]],
+            "dtype": {"fp8": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)", "int8": "int8 (int32 accumulate)",
+                      "moe": "fp8_e4m3 (fp32 accumulate)"}[cfg["kind"]],
             "data": "synthetic (seeded; shapes of the named config, random weights)",
             "config": config,
             "host_link": {"weight_gbs": round(host_gbs, 2), "peak_gbs_sum": round(link_peak_sum, 2),
@@ -350,10 +404,14 @@ def main():
                     "h2d_bytes_per_step": int(a_host.numel() * a_host.element_size() + (sfa_host.numel() * 4 if sfa_host is not None else 0)),
                     "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
                     "note": "weights are read from pinned host memory inside the kernel in both timings"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (2 if moe else 1),
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if moe:
+            line["metric"] = "MoE-layer TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)"
+            line["config"]["numa_node_of_weights"] = w["numa_node"]
+            line["roofline"]["note"] += "; the step holds two grouped-GEMM launches plus torch glue kernels and two NCCL all-to-alls, achieved is over the whole step"
+        if world == 1 and not args.no_cpu_baseline and not moe:
             threads = os.cpu_count() or 1
             v, sample, kind, cores = cpu_reference_sample(cfg, w, threads, max_experts=8)
             line["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}

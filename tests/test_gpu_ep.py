@@ -1,0 +1,112 @@
+"""Expert-parallel FP8 MoE layer on the GPU: one rank against a dense fp32 reference, and 2 ranks over NCCL (when two
+GPUs are visible) where every rank checks its own tokens against the same dense reference."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _make_weights(num_experts, hidden, inter, device):
+    """All experts' FP8 weights from a fixed seed (every rank can rebuild them for the dense reference)."""
+    from asymgemm_b200.utils import per_block_cast_to_fp8
+    gen = torch.Generator(device="cpu").manual_seed(7)
+    w13, s13, w2, s2 = [], [], [], []
+    for _ in range(num_experts):
+        q, s = per_block_cast_to_fp8(torch.randn((2 * inter, hidden), generator=gen) * 0.05, use_ue8m0=False)
+        w13.append(q); s13.append(s)
+        q, s = per_block_cast_to_fp8(torch.randn((hidden, inter), generator=gen) * 0.05, use_ue8m0=False)
+        w2.append(q); s2.append(s)
+    return torch.stack(w13), torch.stack(s13), torch.stack(w2), torch.stack(s2)
+
+
+def _deq_block(q, s):
+    n, k = q.shape
+    return q.float() * s.repeat_interleave(128, 0).repeat_interleave(128, 1)[:n, :k]
+
+
+def _dense_reference(x, ids, wts, w13, s13, w2, s2, inter):
+    """Same arithmetic as the layer with fp32 matmuls on dequantised operands, token by expert."""
+    from asymgemm_b200.utils import per_token_cast_to_fp8
+    xq, sx = per_token_cast_to_fp8(x.float(), use_ue8m0=False)
+    xd = xq.float() * sx.repeat_interleave(128, 1)[:, : x.shape[1]]
+    y = torch.zeros_like(xd)
+    for e in ids.unique().tolist():
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        h = (xd[tok] @ _deq_block(w13[e], s13[e]).t()).to(torch.bfloat16).float()
+        act = (h[:, :inter] * torch.sigmoid(h[:, :inter]) * h[:, inter:]).to(torch.bfloat16).float()
+        aq, sa = per_token_cast_to_fp8(act, use_ue8m0=False)
+        ad = aq.float() * sa.repeat_interleave(128, 1)[:, :inter]
+        out = (ad @ _deq_block(w2[e], s2[e]).t()).to(torch.bfloat16).float()
+        y.index_add_(0, tok, out * wts[tok, slot].unsqueeze(1).float())
+    return y
+
+
+def _case(rank, world, device):
+    from asymgemm_b200 import ep
+    num_experts, hidden, inter, tokens, top_k = 8, 512, 256, 300 + 17 * rank, 2
+    w13, s13, w2, s2 = _make_weights(num_experts, hidden, inter, device)
+    epr = num_experts // world
+    lo = rank * epr
+    layer = ep.ExpertParallelMoE(num_experts, hidden, inter,
+                                 (w13[lo:lo + epr].contiguous().pin_memory(), s13[lo:lo + epr].contiguous().to(device)),
+                                 (w2[lo:lo + epr].contiguous().pin_memory(), s2[lo:lo + epr].contiguous().to(device)))
+    gen = torch.Generator().manual_seed(50 + rank)
+    x = torch.randn((tokens, hidden), generator=gen).to(torch.bfloat16).to(device)
+    logits = torch.randn((tokens, num_experts), generator=gen)
+    logits[:, 6] += 2.0    # a hot expert
+    logits[:, 1] -= 50.0   # an expert nobody picks
+    wts, ids = torch.topk(torch.softmax(logits, -1), top_k, dim=-1)
+    wts = (wts / wts.sum(-1, keepdim=True)).to(device)
+    ids = ids.to(device)
+    y = layer.forward(x, ids, wts)
+    ref = _dense_reference(x, ids, wts, w13.to(device), s13.to(device), w2.to(device), s2.to(device), inter)
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    return err
+
+
+def test_moe_layer_single_rank():
+    import asymgemm_b200 as ag
+    err = _case(0, 1, torch.device("cuda", 0))
+    ag.check_status()
+    assert err <= 2e-2, f"max-rel {err:.3e}"
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        device = torch.device("cuda", rank)
+        torch.cuda.set_device(device)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        import asymgemm_b200 as ag
+        err = _case(rank, world, device)
+        ag.check_status()
+        dist.barrier()
+        q.put((rank, err))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, f"error: {type(e).__name__}: {e}"))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_moe_layer_two_ranks_nccl():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    for r in range(2):
+        assert isinstance(res[r], float), res
+        assert res[r] <= 2e-2, res
