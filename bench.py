@@ -38,6 +38,9 @@ WORKLOADS = {
     "c5_moe_fp8": dict(kind="moe", experts=256, hidden=7168, inter=2048, tokens=65536, top_k=8),
 }
 ELEM_BYTES = {"fp8": 1.0, "bf16": 2.0, "int8": 1.0, "fp4": 0.5}
+# DRAM bytes (read + write) per padded row of A/D of the FP8 7168x4096 kernel, from one ncu capture of a 16-expert case
+# (profiles/mgrouped_fp8_host_streamed_16experts.md): traffic grows with the rows of the launch, not with the weights.
+NCU_DRAM_BYTES_PER_ROW = {"c3_fp8": 18.4e3}
 
 
 def rows_per_expert(cfg, seed=0):
@@ -396,7 +399,11 @@ def main():
                           "frac_of_measured_peak": round(host_gbs / link_peak_sum, 4), "per_gpu_peak_min_gbs": round(link_peak_min, 2),
                           "peak_how": "cudaMemcpyAsync pinned->device, 1 GiB, best of 3, measured in this run on each rank"},
             "roofline": {"bound": "host_link", "achieved": round(ach, 2), "peak": round(link_peak, 2), "unit": "GB/s",
-                         "frac": round(ach / link_peak, 4), "traffic": None,
+                         "frac": round(ach / link_peak, 4),
+                         "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload] * w["m_total"] / 1e9, 3)
+                                     if args.workload in NCU_DRAM_BYTES_PER_ROW and not moe else None),
+                         "traffic_unit": "GB of HBM traffic per launch, scaled by rows from an ncu capture of a smaller case",
+                         "algorithmic_gb": round(w["host_bytes"] / 1e9, 3),
                          "note": "algorithmic bytes = each active expert's weights once (N*K*bytes); the kernel is bound by the PCIe "
                                  "host link, not HBM or tensor throughput: peak is the copy-engine rate measured in this run",
                          "tensor_frac_of_measured": round(w["flops"] / (kernel_ms * 1e-3) / 1e12 / tensor_peak, 5)},
