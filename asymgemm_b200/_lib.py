@@ -61,6 +61,8 @@ EXPORTS = [
     "ag_m_grouped_fp8_gemm_nt",
     "ag_m_grouped_int8_gemm_nt",
     "ag_m_grouped_fp4_gemm_nt",
+    "ag_m_grouped_fp8_gemm_nt_static_scratch",
+    "ag_static_scratch_bytes",
     "ag_scratch_bytes",
     "ag_read_status",
     "ag_set_num_sms",
@@ -88,10 +90,12 @@ def load() -> ctypes.CDLL:
         )
     lib = ctypes.CDLL(str(LIB_PATH))
     for name in ("ag_m_grouped_bf16_gemm_nt", "ag_m_grouped_fp8_gemm_nt", "ag_m_grouped_int8_gemm_nt",
-                 "ag_m_grouped_fp4_gemm_nt"):
+                 "ag_m_grouped_fp4_gemm_nt", "ag_m_grouped_fp8_gemm_nt_static_scratch"):
         fn = getattr(lib, name)
         fn.argtypes = [POINTER(GemmDesc)]
         fn.restype = c_int32
+    lib.ag_static_scratch_bytes.argtypes = []
+    lib.ag_static_scratch_bytes.restype = c_uint64
     lib.ag_scratch_bytes.argtypes = [c_int32, c_int64, c_int64, c_int32]
     lib.ag_scratch_bytes.restype = c_uint64
     lib.ag_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]

@@ -239,6 +239,10 @@ const char* status_text(int code) {
 
 }  // namespace
 
+// Hooks for the other translation units of the library (not part of the public ABI).
+int agb_run_desc(int kind, const ag_gemm_desc_t* desc) { return run(kind, desc); }
+int agb_fail(int code, const char* message) { return fail(code, "%s", message); }
+
 extern "C" {
 
 int ag_m_grouped_bf16_gemm_nt(const ag_gemm_desc_t* desc) { return run(0, desc); }

@@ -103,6 +103,21 @@ int ag_m_grouped_int8_gemm_nt(const ag_gemm_desc_t* desc);
  * asym_gemm/include/asym_gemm/impls/sm100_fp4_asym_gemm_1d1d.cuh:44-51). */
 int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc);
 
+/* FP8 grouped GEMM (same arguments and results as ag_m_grouped_fp8_gemm_nt) for callers that cannot allocate device
+ * memory: processes whose HBM is handed out once at start-up, plugins loaded through FFI with no CUDA allocator of
+ * their own, loops that cannot afford a cudaMalloc (it synchronises the device and can fail when memory is nearly
+ * full). The scratch that long segments use comes from a fixed 80 MiB array inside the library's device image
+ * (ag_static_scratch_bytes); desc->scratch / scratch_bytes are ignored and desc->status MUST be given.
+ * Limits: returns AG_E_INVALID with a message when CTAs x tile rows x padded K bytes exceeds the array (for FP8 with
+ * weights on the host, tile_config 0 and all 148 SMs that is K <= 8704; tile_config 2 doubles it, a lower num_sms raises it);
+ * every GPU that loads the library holds the array until the process exits; all calls share it, so calls that can
+ * overlap on the GPU (other streams or threads) race -- serialise them. The array keeps the last call's contents and
+ * needs no clearing. The first call on each device looks up the array's address (cudaGetSymbolAddress): make that
+ * call with the device current and outside any stream capture. No cudaMalloc/cudaFree is called on any path.
+ * This entry point has no counterpart in the reference. */
+int ag_m_grouped_fp8_gemm_nt_static_scratch(const ag_gemm_desc_t* desc);
+uint64_t ag_static_scratch_bytes(void);
+
 /* Bytes of scratch that let every long segment replay its weight column from device memory
  * (kind: 0 bf16, 1 fp8, 2 int8, 3 nvfp4). Reference counterpart: none (the reference accumulates bf16
  * partial sums in D instead, impls/sm100_fp8_asym_gemm_1d1d.cuh:648-659). */

@@ -1,0 +1,81 @@
+"""The static-scratch FP8 entry point (for callers that cannot allocate device memory), called through the C ABI and
+compared with the ordinary entry point on the same inputs, twice in a row: the second call finds the first call's
+leftovers in the shared scratch array and must not be affected by them.
+
+Collected last on purpose (file name), so a run that stops at the first failure has already run every other test.
+The test itself allocates its tensors with torch before the calls; the entry point under test allocates nothing.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import asymgemm_b200 as ag
+from asymgemm_b200 import _lib
+from oracle import oracle
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _desc(c, d, status, tile=0, num_sms=0):
+    g = _lib.GemmDesc()
+    g.layout = _lib.LAYOUT_CONTIGUOUS
+    g.d_dtype = _lib.D_BF16
+    g.a, g.sfa = c["a"].data_ptr(), c["sfa"].data_ptr()
+    g.b, g.sfb = c["b"].data_ptr(), c["sfb_dev"].data_ptr()
+    g.d = d.data_ptr()
+    g.offsets, g.experts = c["offsets"].data_ptr(), c["experts"].data_ptr()
+    g.max_segments = c["list_size"]
+    g.m, g.n, g.k, g.num_groups = c["m_total"], c["n"], c["k"], c["g"]
+    g.status = status.data_ptr()
+    g.stream = torch.cuda.current_stream().cuda_stream
+    g.tile_config = tile
+    g.num_sms = num_sms
+    return g
+
+
+@pytest.mark.parametrize("tile", [0, 2])
+def test_static_scratch_matches_regular_entry_point_twice(tile):
+    lib = _lib.load()
+    # segments longer than one accumulator chunk, so that the scratch replay path runs
+    c = H.make_contiguous_case("fp8", [2100, 0, 130, 3000, 64], 384, 1024, seed=21)
+    c["sfb_dev"] = c["sfb"].cuda()
+    d_ref = torch.zeros((c["m_total"], c["n"]), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (c["b"], c["sfb"]), d_ref, c["offsets"], c["experts"], c["list_size"])
+    ag.check_status()
+    mask = H.valid_row_mask(c["segments"], c["m_total"])
+    assert oracle.max_rel(d_ref.float().cpu().numpy()[mask], c["ref"][mask]) <= 2e-2
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for call in range(2):
+        d = torch.full_like(d_ref, float("nan"))
+        rc = lib.ag_m_grouped_fp8_gemm_nt_static_scratch(_desc(c, d, status, tile=tile))
+        assert rc == _lib.AG_OK, _lib.last_error()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        got = d.float().cpu().numpy()[mask]
+        # tolerance of the FP8 parity tests; in practice the two entry points agree bit for bit
+        assert oracle.max_rel(got, d_ref.float().cpu().numpy()[mask]) <= 2e-2, f"call {call}"
+        assert oracle.max_rel(got, c["ref"][mask]) <= 2e-2, f"call {call}"
+
+
+def test_static_scratch_rejects_oversized_problems_and_missing_status():
+    lib = _lib.load()
+    c = H.make_contiguous_case("fp8", [128], 128, 512, seed=22)
+    c["sfb_dev"] = c["sfb"].cuda()
+    d = torch.zeros((c["m_total"], c["n"]), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    g = _desc(c, d, status)
+    g.status = None
+    assert lib.ag_m_grouped_fp8_gemm_nt_static_scratch(g) == _lib.AG_E_INVALID
+    assert "status" in _lib.last_error()
+    # claim a problem whose scratch need (CTAs x 64 rows x K bytes) exceeds the built-in array: rejected before any launch
+    g = _desc(c, d, status)
+    g.k, g.n, g.max_segments = 1 << 16, 1 << 14, 64
+    assert lib.ag_m_grouped_fp8_gemm_nt_static_scratch(g) == _lib.AG_E_INVALID
+    assert "built-in scratch" in _lib.last_error()
+    assert lib.ag_static_scratch_bytes() == 80 << 20
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
