@@ -21,6 +21,18 @@ from .api import (  # noqa: F401
     set_use_scratch,
     set_wait_limit_ms,
 )
+from .layout_api import (  # noqa: F401
+    get_arch_major,
+    get_arch_pair,
+    get_compile_mode,
+    get_mn_major_tma_aligned_packed_ue8m0_tensor,
+    get_mn_major_tma_aligned_tensor,
+    get_tc_util,
+    get_tma_aligned_size,
+    set_compile_mode,
+    set_tc_util,
+    transform_sf_into_required_layout,
+)
 from . import testing, utils  # noqa: F401
 
 __version__ = "0.1.0"

@@ -71,6 +71,7 @@ EXPORTS = [
     "ag_fp4_sf_blocked_bytes",
     "ag_fp4_sf_to_blocked",
     "ag_measure_host_link",
+    "ag_selftest_wait_limit",
     "ag_last_error",
     "ag_version",
 ]
@@ -110,6 +111,8 @@ def load() -> ctypes.CDLL:
     lib.ag_fp4_sf_blocked_bytes.restype = c_uint64
     lib.ag_fp4_sf_to_blocked.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]
     lib.ag_fp4_sf_to_blocked.restype = c_int32
+    lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
+    lib.ag_selftest_wait_limit.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]
     lib.ag_measure_host_link.restype = c_int32
     lib.ag_last_error.argtypes = []

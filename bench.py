@@ -51,7 +51,7 @@ def rows_per_expert(cfg, seed=0):
     return torch.bincount(picks.flatten(), minlength=e).tolist()
 
 
-def build_workload(cfg, rank, world, device, seed=0):
+def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False):
     """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
     from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
                                      per_token_cast_to_fp8, per_token_cast_to_int8)
@@ -98,6 +98,8 @@ def build_workload(cfg, rank, world, device, seed=0):
             q = w.to(torch.bfloat16)
         b_host[e].copy_(q, non_blocking=True)
     torch.cuda.synchronize(device)
+    if weights_on_device:
+        b_host = b_host.to(device)
     d = torch.empty((m_total, n), dtype=torch.bfloat16, device=device)
     active = sum(1 for c in counts if c > 0)
     return dict(kind=kind, a=a, sfa=sfa, b=b_host, sfb=sfb, d=d, offsets=offsets, experts=experts, list_size=list_size,
@@ -254,6 +256,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--experts", type=int, default=0, help="shrink the expert count (tokens shrink in proportion); 0 = full size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--weights", default="host", choices=["host", "device"],
+                    help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
     ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
     ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
     args = ap.parse_args()
@@ -289,7 +293,10 @@ def main():
     from asymgemm_b200 import _lib
 
     moe = cfg["kind"] == "moe"
-    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device)
+    on_dev = args.weights == "device"
+    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device, weights_on_device=on_dev)
+    if on_dev:
+        config["workload"] = config["workload"].replace("B in pinned host DRAM", "B resident in HBM")
     lib = _lib.load()
     ag.set_tile_config(args.tile)
     if args.sms:
@@ -414,6 +421,13 @@ def main():
             "gpu_launches": args.steps * (2 if moe else 1),
             "clocks": clocks,
         }
+        if on_dev and not moe:
+            tf = w["flops"] / (kernel_ms * 1e-3) / 1e12
+            line["roofline"] = {"bound": "tensor", "achieved": round(tf, 2), "peak": round(tensor_peak, 1), "unit": "TFLOP/s",
+                                "frac": round(tf / tensor_peak, 4), "traffic": None,
+                                "note": "weights resident in HBM: bound by the tensor pipe; peak = MEASURED_PEAKS.json bf16_tflops"
+                                        " (x2 for 8-bit operands), of measured"}
+            line.pop("host_link", None)
         if moe:
             line["metric"] = "MoE-layer TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)"
             line["config"]["numa_node_of_weights"] = w["numa_node"]

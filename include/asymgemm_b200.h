@@ -148,6 +148,12 @@ int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t row
  * ~50 GB/s for the same copy, asym_gemm/unified_moe/runtime.py:115-116). */
 int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out);
 
+/* Failure-detection self test: launches a one-CTA kernel whose only barrier wait can never be satisfied. After
+ * `timeout_ms` (1..2000) the wait gives up, the kernel stores (0 << 8) | 9 ("wait-limit self test expired") in *status
+ * and returns; the context stays usable. Replaces nothing in the reference, whose device waits are unbounded
+ * (csrc/ep_steal/ep_steal_sync.cu:63-64) and whose device asserts trap (asym_gemm/include/asym_gemm/common/utils.cuh:24-40). */
+int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
+
 const char* ag_last_error(void);
 const char* ag_version(void);
 

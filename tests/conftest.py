@@ -10,6 +10,7 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU")
+    config.addinivalue_line("markers", "expects_status: the test provokes a kernel status word on purpose")
 
 
 @pytest.fixture(autouse=True)

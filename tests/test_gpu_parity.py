@@ -197,3 +197,26 @@ def test_empty_problem_and_errors():
     ag.m_grouped_bf16_asym_gemm_nt_contiguous(a, b, d, off, exp, 3)
     torch.cuda.synchronize()
     assert (d == 7.0).all()
+
+
+@pytest.mark.expects_status
+def test_wait_limit_expires_with_status_and_context_stays_usable():
+    """Failure detection without faulting the GPU: a wait that nothing satisfies gives up after its limit, the kernel
+    reports a status word, the host raises, and the next GEMM on the same context is correct."""
+    import time
+    from asymgemm_b200 import _lib
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _lib.check(lib.ag_selftest_wait_limit(50, status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    out = _lib.c_int32(0)
+    rc = lib.ag_read_status(status.data_ptr(), torch.cuda.current_stream().cuda_stream, out)
+    dt = time.perf_counter() - t0
+    assert rc == _lib.AG_E_DEVICE and (out.value & 0xff) == 9 and "self test" in _lib.last_error()
+    assert 0.04 <= dt < 2.0, dt
+    c = H.make_contiguous_case("bf16", [128, 128], 128, 512, seed=9)
+    d = torch.zeros((c["m_total"], 128), dtype=torch.bfloat16, device="cuda")
+    _run_contiguous(c, d)
+    ag.check_status()
+    _check("bf16", d.float().cpu().numpy(), c["ref"], c["segments"])

@@ -122,3 +122,25 @@ def test_weight_scale_cache_is_tied_to_the_tensor_object():
     fake = torch.ones(8)
     cache[(id(fake), 0)] = cache.pop(key)
     assert api._cache_get(cache, fake, dev) is None
+
+
+def test_scale_layout_helpers_keep_the_reference_shapes_and_strides():
+    sf = torch.rand(2, 70, 6) + 0.5
+    out = ag.get_mn_major_tma_aligned_tensor(sf)
+    assert out.shape == sf.shape and out.stride() == (6 * 72, 1, 72) and torch.equal(out, sf)
+    pw = torch.exp2(torch.randint(-8, 8, (70, 6)).float())
+    packed = ag.get_mn_major_tma_aligned_packed_ue8m0_tensor(pw)
+    assert packed.shape == (70, 2) and packed.dtype == torch.int32 and packed.stride() == (1, 72)
+    # byte j of word w is the biased exponent of column 4*w + j; columns past k are zero
+    exp = (torch.log2(pw) + 127).to(torch.int32)
+    assert torch.equal(packed[:, 0] & 0xFF, exp[:, 0]) and torch.equal((packed[:, 1] >> 8) & 0xFF, exp[:, 5])
+    assert ((packed[:, 1] >> 16) == 0).all()
+    # weight scales: 128-row blocks are broadcast to rows first
+    sfb = torch.exp2(torch.randint(-4, 4, (3, 2, 4)).float())
+    t = ag.transform_sf_into_required_layout(sfb, 200, 512, (1, 128, 128), num_groups=3, is_sfa=False)
+    assert t.shape == (3, 200, 1)
+    assert torch.equal(t[1, 130, 0] & 0xFF, (torch.log2(sfb[1, 1, 0]) + 127).to(torch.int32))
+    with pytest.raises(RuntimeError):
+        ag.transform_sf_into_required_layout(sfb, 200, 512, (1, 64, 64))
+    ag.set_tc_util(80); ag.set_compile_mode(1)
+    assert ag.get_tc_util() == 80 and ag.get_compile_mode() == 1
