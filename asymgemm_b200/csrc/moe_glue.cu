@@ -1,0 +1,183 @@
+// Memory-bound helper kernels around the two grouped GEMMs of an expert-parallel FP8 MoE layer: 1x128 FP8 row
+// quantisation, SiLU(gate)*up fused with that quantisation, row gather/scatter between token order and the padded
+// contiguous layout, and the router-weighted top-k combine. Callers of the reference do these steps with separate torch
+// kernels (asym_gemm/unified_moe/runtime.py:1422-1476,1570,1620-1627; asym_gemm/training/frozen_linear.py:595-693);
+// each is one pass over its data here.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/asymgemm_b200.h"
+
+int agb_fail(int code, const char* message);
+
+namespace agb {
+
+constexpr float kFp8Max = 448.0f;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t quantise4(const float (&v)[4], float inv) {
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    out |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  return out;
+}
+
+// One warp per (row, 128-column block): scale = max(amax, 1e-4) / 448, q = e4m3(x * (1 / scale)).
+// MODE 0: x is bf16 [rows, cols]. MODE 1: x is bf16 [rows, 2*cols] holding gate | up; the value quantised is
+// bf16(silu(gate) * up), the activation the reference's CPU MoE bucket forms (csrc/cpu/module.cpp:337-347).
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                                         float* __restrict__ sf, long long rows, int cols, int blocks_per_row) {
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = rows * blocks_per_row;
+  if (warp_global >= total) return;
+  const long long row = warp_global / blocks_per_row;
+  const int blk = static_cast<int>(warp_global - row * blocks_per_row);
+  const int c0 = blk * 128 + lane * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  const int in_cols = MODE == 1 ? 2 * cols : cols;
+  const __nv_bfloat16* xr = x + row * in_cols;
+  if (c0 + 3 < cols) {
+    const uint2 g = *reinterpret_cast<const uint2*>(xr + c0);
+    const __nv_bfloat162 g0 = *reinterpret_cast<const __nv_bfloat162*>(&g.x), g1 = *reinterpret_cast<const __nv_bfloat162*>(&g.y);
+    v[0] = __low2float(g0); v[1] = __high2float(g0); v[2] = __low2float(g1); v[3] = __high2float(g1);
+    if (MODE == 1) {
+      const uint2 u = *reinterpret_cast<const uint2*>(xr + cols + c0);
+      const __nv_bfloat162 u0 = *reinterpret_cast<const __nv_bfloat162*>(&u.x), u1 = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+      const float uu[4] = {__low2float(u0), __high2float(u0), __low2float(u1), __high2float(u1)};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float s = v[i] / (1.0f + expf(-v[i]));
+        v[i] = __bfloat162float(__float2bfloat16_rn(s * uu[i]));
+      }
+    }
+  } else {
+    for (int i = 0; i < 4; ++i) {
+      if (c0 + i < cols) {
+        float g = __bfloat162float(xr[c0 + i]);
+        if (MODE == 1) {
+          const float s = g / (1.0f + expf(-g));
+          g = __bfloat162float(__float2bfloat16_rn(s * __bfloat162float(xr[cols + c0 + i])));
+        }
+        v[i] = g;
+      }
+    }
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = fmaxf(warp_max(amax), 1e-4f);
+  const float scale = amax * (1.0f / kFp8Max);  // torch's CUDA division by a scalar multiplies by its fp32 reciprocal
+  const float inv = 1.0f / scale;
+  const uint32_t packed = quantise4(v, inv);
+  uint8_t* qr = q + row * cols;
+  if (c0 + 3 < cols) {
+    *reinterpret_cast<uint32_t*>(qr + c0) = packed;
+  } else {
+    for (int i = 0; i < 4; ++i)
+      if (c0 + i < cols) qr[c0 + i] = static_cast<uint8_t>(packed >> (8 * i));
+  }
+  if (lane == 0) sf[row * blocks_per_row + blk] = scale;
+}
+
+// dst[dst_rows ? dst_rows[i] : i] = src[src_rows ? src_rows[i] : i] for i < rows; one warp per row, 16-byte vectors.
+__global__ void __launch_bounds__(256) move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                        const long long* __restrict__ src_rows, const long long* __restrict__ dst_rows,
+                                                        long long rows, int vec_per_row) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= rows) return;
+  const long long s = src_rows ? src_rows[w] : w;
+  const long long d = dst_rows ? dst_rows[w] : w;
+  const uint4* sp = src + s * vec_per_row;
+  uint4* dp = dst + d * vec_per_row;
+  for (int i = lane; i < vec_per_row; i += 32) dp[i] = sp[i];
+}
+
+// y[t] = sum_j w[t, j] * rows[pos[t * k + j]] in fp32, rounded once to bf16. One CTA per token, 8 columns per thread.
+__global__ void __launch_bounds__(256) combine_topk_kernel(const __nv_bfloat16* __restrict__ rows, const long long* __restrict__ pos,
+                                                           const float* __restrict__ w, __nv_bfloat16* __restrict__ y, int top_k, int cols) {
+  const long long t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const long long r = pos[t * top_k + j];
+      const float wt = w[t * top_k + j];
+      const uint4 v = *reinterpret_cast<const uint4*>(rows + r * cols + c);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] = fmaf(wt, __low2float(p[i]), acc[2 * i]);
+        acc[2 * i + 1] = fmaf(wt, __high2float(p[i]), acc[2 * i + 1]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) op[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(y + t * cols + c) = o;
+  }
+}
+
+}  // namespace agb
+
+namespace {
+int launch_check() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? AG_OK : agb_fail(AG_E_CUDA, cudaGetErrorString(e));
+}
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
+
+extern "C" {
+
+int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream) {
+  if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || cols % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
+  if (rows == 0) return AG_OK;
+  const int bpr = static_cast<int>((cols + 127) / 128);
+  const long long warps = rows * bpr;
+  agb::quant_rows_kernel<0><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr);
+  return launch_check();
+}
+
+int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, void* stream) {
+  if (!gate_up_bf16 || !q || !sf || rows < 0 || inter <= 0 || inter % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (inter must be a multiple of 4)");
+  if (rows == 0) return AG_OK;
+  const int bpr = static_cast<int>((inter + 127) / 128);
+  const long long warps = rows * bpr;
+  agb::quant_rows_kernel<1><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr);
+  return launch_check();
+}
+
+int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes, void* stream) {
+  if (!src || !dst || rows < 0 || row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(src) || !aligned16(dst))
+    return agb_fail(AG_E_INVALID, "bad arguments (rows must be 16-byte multiples and 16-byte aligned)");
+  if (rows == 0) return AG_OK;
+  agb::move_rows_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), reinterpret_cast<const long long*>(src_rows),
+      reinterpret_cast<const long long*>(dst_rows), rows, static_cast<int>(row_bytes / 16));
+  return launch_check();
+}
+
+int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
+                    int64_t cols, void* stream) {
+  if (!rows_bf16 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 8 != 0)
+    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 8)");
+  if (tokens == 0) return AG_OK;
+  agb::combine_topk_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(rows_bf16), reinterpret_cast<const long long*>(pos), weights, static_cast<__nv_bfloat16*>(y_bf16),
+      top_k, static_cast<int>(cols));
+  return launch_check();
+}
+
+}  // extern "C"

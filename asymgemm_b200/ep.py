@@ -24,6 +24,8 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from . import moe_ops
+
 ALIGN = 128
 
 
@@ -115,10 +117,13 @@ class EPDispatcher:
         src_token = torch.div(order, top_k, rounding_mode="floor")
         outs = []
         for t in (rows,) + tuple(extras):
-            as_bytes = t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
-            send = as_bytes.index_select(0, src_token)
-            recv = torch.empty((total_recv,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
-            self._all_to_all(recv, send, recv_splits, send_splits)
+            send = moe_ops.move_rows(t.contiguous(), src_token.numel(), src_rows=src_token)
+            if self.world == 1:
+                outs.append(send)      # nothing to exchange: the gathered rows are the received rows
+                continue
+            as_bytes = send.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else send
+            recv = torch.empty((total_recv,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=as_bytes.device)
+            self._all_to_all(recv, as_bytes, recv_splits, send_splits)
             outs.append(recv.view(t.dtype) if t.dtype == torch.float8_e4m3fn else recv)
         dest_rows, per_expert, padded_rows, offsets, experts = self.layout(counts_host[1], rows.device)
         state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k)
@@ -126,21 +131,21 @@ class EPDispatcher:
 
     def combine(self, expert_out: torch.Tensor, state: DispatchState, topk_weights: torch.Tensor) -> torch.Tensor:
         """expert_out [padded_rows, H] (contiguous layout) -> y [T, H] = sum_k w[t, k] * out(t, k), in fp32, as expert_out.dtype."""
-        back = expert_out.index_select(0, state.dest_rows)
+        # inverse of the sort: pair p (token p // k, slot p % k) was sent as sorted row inv[p]
+        inv = torch.empty_like(state.order)
+        inv[state.order] = torch.arange(state.order.numel(), device=state.order.device)
+        if self.world == 1:
+            # the sorted rows never left this rank: read them straight out of the padded layout
+            return moe_ops.combine_topk(expert_out, state.dest_rows.index_select(0, inv), topk_weights, state.tokens, state.top_k)
+        back = moe_ops.move_rows(expert_out, state.dest_rows.numel(), src_rows=state.dest_rows)
         ret = torch.empty((state.tokens * state.top_k, back.shape[1]), dtype=back.dtype, device=back.device)
         self._all_to_all(ret, back, state.send_splits, state.recv_splits)
-        pairs = torch.empty_like(ret)
-        pairs.index_copy_(0, state.order, ret)
-        y = (pairs.view(state.tokens, state.top_k, -1).float() * topk_weights.unsqueeze(-1).float()).sum(dim=1)
-        return y.to(expert_out.dtype)
+        return moe_ops.combine_topk(ret, inv, topk_weights, state.tokens, state.top_k)
 
 
 def to_contiguous_layout(recv: torch.Tensor, state: DispatchState) -> torch.Tensor:
     """Scatter received rows into the zero-padded contiguous layout the grouped GEMM consumes."""
-    as_bytes = recv.view(torch.uint8) if recv.dtype == torch.float8_e4m3fn else recv
-    out = torch.zeros((state.padded_rows,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=recv.device)
-    out.index_copy_(0, state.dest_rows, as_bytes)
-    return out.view(recv.dtype) if recv.dtype == torch.float8_e4m3fn else out
+    return moe_ops.move_rows(recv.contiguous(), state.padded_rows, dst_rows=state.dest_rows, zero=True)
 
 
 # --------------------------------------------------------------------------------------------- pinned weights
@@ -190,14 +195,6 @@ def gpu_numa_node(device_index: int) -> int:
 
 
 # --------------------------------------------------------------------------------------------- the layer
-def silu_mul_requant(d1: torch.Tensor, inter: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [M, 2*inter] -> (fp8 [M, inter], fp32 scales [M, inter/128]): silu(gate) * up, rounded to bf16, then 1x128 FP8."""
-    from .utils import per_token_cast_to_fp8
-    gate, up = d1[:, :inter].float(), d1[:, inter:].float()
-    act = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
-    return per_token_cast_to_fp8(act.float(), use_ue8m0=False)
-
-
 class ExpertParallelMoE:
     """FP8 MoE layer (gate+up, SiLU*mul, down) with this rank's experts in pinned host memory.
 
@@ -219,18 +216,17 @@ class ExpertParallelMoE:
         m = state.padded_rows
         dev = a_q.device
         d1 = torch.empty((m, 2 * self.inter), dtype=torch.bfloat16, device=dev)
-        d2 = torch.zeros((m, self.hidden), dtype=torch.bfloat16, device=dev)
+        d2 = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=dev)
         if m == 0:
             return d2
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), self.w13, d1, state.offsets, state.experts, None)
-        a2, s2 = silu_mul_requant(d1, self.inter)
+        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter)
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), self.w2, d2, state.offsets, state.experts, None)
         return d2
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
-        from .utils import per_token_cast_to_fp8
-        x_q, sfx = per_token_cast_to_fp8(x.float(), use_ue8m0=False)
+        x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous())
         state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)

@@ -148,6 +148,26 @@ int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t row
  * ~50 GB/s for the same copy, asym_gemm/unified_moe/runtime.py:115-116). */
 int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out);
 
+/* ---- helper kernels around the two GEMMs of an FP8 MoE layer (all device pointers, asynchronous on `stream`) ----
+ * The reference's callers do these steps with separate torch / Triton kernels
+ * (asym_gemm/unified_moe/runtime.py:1422-1476,1570,1620-1627; asym_gemm/unified_moe/_triton.py). */
+
+/* x bf16 [rows, cols] -> q e4m3 [rows, cols], sf fp32 [rows, ceil(cols/128)]; sf = max(amax, 1e-4) / 448 per 1x128 block,
+ * q = e4m3(x * (1 / sf)): the arithmetic of per_token_cast_to_fp8 (asym_gemm/utils/math.py:24-34). cols % 4 == 0. */
+int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream);
+
+/* gate_up bf16 [rows, 2*inter] (gate columns first) -> bf16(silu(gate) * up) quantised as above into q [rows, inter],
+ * sf [rows, ceil(inter/128)] (activation of csrc/cpu/module.cpp:337-347 followed by the 1x128 quantiser). */
+int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, void* stream);
+
+/* dst[dst_rows ? dst_rows[i] : i] = src[src_rows ? src_rows[i] : i], i < rows; rows of row_bytes (multiple of 16) bytes. */
+int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes,
+                 void* stream);
+
+/* y[t] = sum_j weights[t, j] * rows[pos[t * top_k + j]] accumulated in fp32, rounded once to bf16. cols % 8 == 0. */
+int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
+                    int64_t cols, void* stream);
+
 /* Failure-detection self test: launches a one-CTA kernel whose only barrier wait can never be satisfied. After
  * `timeout_ms` (1..2000) the wait gives up, the kernel stores (0 << 8) | 9 ("wait-limit self test expired") in *status
  * and returns; the context stays usable. Replaces nothing in the reference, whose device waits are unbounded

@@ -66,6 +66,9 @@ def _case(rank, world, device):
     y = layer.forward(x, ids, wts)
     ref = _dense_reference(x, ids, wts, w13.to(device), s13.to(device), w2.to(device), s2.to(device), inter)
     err = float((y.float() - ref).abs().max() / ref.abs().max())
+    yd, rd = y.double(), ref.double()
+    diff = float(1 - 2 * (yd * rd).sum() / ((yd * yd).sum() + (rd * rd).sum()))
+    assert diff < 1e-3, f"calc_diff {diff:.3e}"
     return err
 
 
@@ -73,7 +76,9 @@ def test_moe_layer_single_rank():
     import asymgemm_b200 as ag
     err = _case(0, 1, torch.device("cuda", 0))
     ag.check_status()
-    assert err <= 2e-2, f"max-rel {err:.3e}"
+    # two chained FP8 GEMMs with a requantisation in between: a one-ulp difference in the activation (expf vs torch's
+    # sigmoid) can move single FP8 codes, so the layer is held to 3e-2 max-rel and 1e-3 calc_diff
+    assert err <= 3e-2, f"max-rel {err:.3e}"
 
 
 def _worker(rank, world, port, q):
@@ -109,4 +114,43 @@ def test_moe_layer_two_ranks_nccl():
         p.join(timeout=60)
     for r in range(2):
         assert isinstance(res[r], float), res
-        assert res[r] <= 2e-2, res
+        assert res[r] <= 3e-2, res
+
+
+def test_helper_kernels_match_torch():
+    """The fused helper kernels against the torch formulation of the same steps."""
+    from asymgemm_b200 import moe_ops
+    from asymgemm_b200.utils import per_token_cast_to_fp8
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.randn((333, 640), device="cuda", generator=gen) * 3).to(torch.bfloat16)
+    x[5] = 0                                            # an all-zero row hits the 1e-4 clamp
+    q, sf = moe_ops.quant_rows_fp8(x)
+    q_ref, sf_ref = per_token_cast_to_fp8(x.float(), use_ue8m0=False)
+    assert torch.equal(sf, sf_ref) and torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+    inter = 384
+    gu = (torch.randn((257, 2 * inter), device="cuda", generator=gen) * 2).to(torch.bfloat16)
+    q, sf = moe_ops.silu_mul_quant_fp8(gu, inter)
+    g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    act = (g * torch.sigmoid(g) * u).to(torch.bfloat16).float()
+    got = q.float() * sf.repeat_interleave(128, 1)[:, :inter]
+    # 1x128 FP8 of the same activation: within half an e4m3 step (2^-4 relative) of the block maximum
+    amax = act.view(257, -1, 128).abs().amax(dim=2).repeat_interleave(128, 1)
+    assert ((got - act).abs() <= amax * 0.0625 + 1e-6).all()
+    q_ref, sf_ref = per_token_cast_to_fp8(act, use_ue8m0=False)
+    assert (sf - sf_ref).abs().max() <= 1e-2 * sf_ref.abs().max()
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-2   # expf vs torch.sigmoid: rare 1-ulp flips
+
+    rows = torch.randn((100, 256), device="cuda", generator=gen).to(torch.bfloat16)
+    idx = torch.randperm(100, device="cuda", generator=gen)[:60]
+    out = moe_ops.move_rows(rows, 300, src_rows=idx, dst_rows=idx * 3, zero=True)
+    ref = torch.zeros((300, 256), dtype=torch.bfloat16, device="cuda")
+    ref[idx * 3] = rows[idx]
+    assert torch.equal(out, ref)
+
+    tokens, k = 50, 3
+    pos = torch.randint(0, 100, (tokens * k,), device="cuda", generator=gen)
+    w = torch.rand((tokens, k), device="cuda", generator=gen)
+    y = moe_ops.combine_topk(rows, pos, w, tokens, k)
+    ref = (rows[pos].view(tokens, k, -1).float() * w.unsqueeze(-1)).sum(1)
+    assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
