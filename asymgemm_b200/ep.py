@@ -36,10 +36,10 @@ class DispatchState:
     send_splits: List[int]       # rows sent to each rank
     recv_splits: List[int]       # rows received from each rank
     dest_rows: torch.Tensor      # [R] row of every received row in the padded contiguous layout
-    rows_per_expert: List[int]   # valid rows of every local expert
-    padded_rows: int             # rows of the contiguous layout (every expert padded to 128)
-    offsets: torch.Tensor        # int32 [2*S] (start, end) pairs, S = local experts with rows
-    experts: torch.Tensor        # int32 [S+1], ends in -1
+    rows_per_expert: torch.Tensor  # [experts_per_rank] valid rows of every local expert (device tensor)
+    padded_rows: int             # rows allocated for the contiguous layout (upper bound; every expert padded to 128)
+    offsets: torch.Tensor        # int32 [2*experts_per_rank] (start, end) pairs; empty experts have start == end
+    experts: torch.Tensor        # int32 [experts_per_rank + 1] = 0 .. experts_per_rank-1, -1
     tokens: int
     top_k: int
 
@@ -76,44 +76,58 @@ class EPDispatcher:
         self._all_to_all(recv_counts, send_counts.contiguous())
         return order, send_counts, recv_counts
 
-    def layout(self, recv_counts_host: torch.Tensor, device) -> Tuple[torch.Tensor, List[int], int, torch.Tensor, torch.Tensor]:
+    def layout(self, recv_counts: torch.Tensor, total_recv: int):
         """Contiguous layout of the received rows: grouped by local expert, each expert padded to 128 rows.
 
-        Received rows arrive ordered by (source rank, expert). Returns (dest_rows [R], rows_per_expert, padded_rows,
-        offsets, experts) with dest_rows[i] = row of received row i in the padded layout.
+        Pure tensor arithmetic on the device of `recv_counts` [world, experts_per_rank] -- no host synchronisation.
+        Received rows arrive ordered by (source rank, expert). Returns (dest_rows [total_recv], rows_per_expert [epr],
+        padded_bound, offsets int32 [2*epr], experts int32 [epr+1]): dest_rows[i] = row of received row i in the padded
+        layout; every local expert gets a segment (an empty one if it received nothing, which the GEMM skips);
+        padded_bound = total_recv rounded up plus 127 rows per expert, an upper bound of the rows the layout can use.
         """
-        rc = recv_counts_host.to(torch.int64)                      # [world, epr] on the host
-        per_expert = rc.sum(dim=0)                                  # [epr]
+        dev = recv_counts.device
+        epr = self.experts_per_rank
+        rc = recv_counts.to(torch.int64)
+        per_expert = rc.sum(dim=0)                                   # [epr]
         padded = (per_expert + ALIGN - 1) // ALIGN * ALIGN
-        expert_start = torch.cumsum(padded, 0) - padded             # [epr]
-        within = torch.cumsum(rc, 0) - rc                           # rows of expert j that come from lower ranks
-        block_dest = (expert_start.unsqueeze(0) + within).reshape(-1)   # [world*epr], source-major like the recv order
+        expert_start = torch.cumsum(padded, 0) - padded              # [epr]
+        within = torch.cumsum(rc, 0) - rc                            # rows of expert j that come from lower ranks
+        block_dest = (expert_start.unsqueeze(0) + within).reshape(-1)    # [world*epr], source-major like the recv order
         block_len = rc.reshape(-1)
         block_recv = torch.cumsum(block_len, 0) - block_len
-        total = int(block_len.sum())
-        shift = torch.repeat_interleave(block_dest - block_recv, block_len, output_size=total)
-        dest_rows = (shift + torch.arange(total)).to(device)
-        offsets, experts = [], []
-        for j in range(self.experts_per_rank):
-            if per_expert[j] > 0:
-                offsets += [int(expert_start[j]), int(expert_start[j] + padded[j])]
-                experts.append(j)
-        experts.append(-1)
-        return (dest_rows, per_expert.tolist(), int(padded.sum()),
-                torch.tensor(offsets, dtype=torch.int32, device=device), torch.tensor(experts, dtype=torch.int32, device=device))
+        shift = torch.repeat_interleave(block_dest - block_recv, block_len, output_size=total_recv)
+        dest_rows = shift + torch.arange(total_recv, device=dev)
+        offsets = torch.stack([expert_start, expert_start + padded], dim=1).reshape(-1).to(torch.int32)
+        experts = torch.cat([torch.arange(epr, device=dev, dtype=torch.int32), torch.full((1,), -1, device=dev, dtype=torch.int32)])
+        padded_bound = (total_recv + ALIGN - 1) // ALIGN * ALIGN + epr * ALIGN if total_recv > 0 else 0
+        return dest_rows, per_expert, padded_bound, offsets, experts
 
     def dispatch(self, rows: torch.Tensor, topk_ids: torch.Tensor, extras: Tuple[torch.Tensor, ...] = ()):
         """Send every (token, slot) pair's row to the rank that owns its expert.
 
         rows [T, H] (any dtype; FP8 rows travel as bytes), extras: more per-token tensors [T, *] sent alongside (scales).
-        Returns (state, recv_rows [R, H], recv_extras). One host synchronisation (the split sizes).
+        Returns (state, recv_rows [R, H], recv_extras). With one rank nothing leaves the device and the host never
+        waits; with several ranks the split sizes of the exchange are read back once, on a side stream, so the host
+        does not wait for GEMMs still running on the compute stream.
         """
         tokens, top_k = topk_ids.shape
-        order, send_counts, recv_counts = self.plan(topk_ids)
-        counts_host = torch.stack([send_counts, recv_counts]).cpu()
-        send_splits = counts_host[0].sum(dim=1).tolist()
-        recv_splits = counts_host[1].sum(dim=1).tolist()
-        total_recv = int(sum(recv_splits))
+        if self.world == 1:
+            order, send_counts, recv_counts = self.plan(topk_ids)
+            send_splits = recv_splits = [tokens * top_k]
+            total_recv = tokens * top_k
+        else:
+            side = self._side_stream(topk_ids.device)
+            if side is not None:
+                side.wait_stream(torch.cuda.current_stream(topk_ids.device))
+                with torch.cuda.stream(side):
+                    order, send_counts, recv_counts = self.plan(topk_ids)
+                    counts_host = torch.stack([send_counts, recv_counts]).sum(dim=2).cpu()   # waits for the side stream only
+                torch.cuda.current_stream(topk_ids.device).wait_stream(side)
+            else:
+                order, send_counts, recv_counts = self.plan(topk_ids)
+                counts_host = torch.stack([send_counts, recv_counts]).sum(dim=2).cpu()
+            send_splits, recv_splits = counts_host[0].tolist(), counts_host[1].tolist()
+            total_recv = int(sum(recv_splits))
         src_token = torch.div(order, top_k, rounding_mode="floor")
         outs = []
         for t in (rows,) + tuple(extras):
@@ -125,9 +139,16 @@ class EPDispatcher:
             recv = torch.empty((total_recv,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=as_bytes.device)
             self._all_to_all(recv, as_bytes, recv_splits, send_splits)
             outs.append(recv.view(t.dtype) if t.dtype == torch.float8_e4m3fn else recv)
-        dest_rows, per_expert, padded_rows, offsets, experts = self.layout(counts_host[1], rows.device)
+        dest_rows, per_expert, padded_rows, offsets, experts = self.layout(recv_counts, total_recv)
         state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k)
         return state, outs[0], tuple(outs[1:])
+
+    def _side_stream(self, device):
+        if device.type != "cuda":
+            return None
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
 
     def combine(self, expert_out: torch.Tensor, state: DispatchState, topk_weights: torch.Tensor) -> torch.Tensor:
         """expert_out [padded_rows, H] (contiguous layout) -> y [T, H] = sum_k w[t, k] * out(t, k), in fp32, as expert_out.dtype."""

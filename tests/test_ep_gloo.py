@@ -49,7 +49,7 @@ def _roundtrip_worker(rank, world, port, q):
         state, recv, (recv_tag,) = disp.dispatch(x, ids, (torch.arange(tokens, dtype=torch.float32).unsqueeze(1),))
         a = to_contiguous_layout(recv, state)
         assert a.shape[0] == state.padded_rows and state.padded_rows % 128 == 0
-        assert sum(state.rows_per_expert) == recv.shape[0] == sum(state.recv_splits)
+        assert int(state.rows_per_expert.sum()) == recv.shape[0] == sum(state.recv_splits)
         # every segment is 128-aligned and holds exactly its expert's rows, padding rows are zero
         off = state.offsets.tolist()
         assert all(o % 128 == 0 for o in off)
@@ -99,8 +99,9 @@ def test_layout_arithmetic_single_rank():
     ids = torch.tensor([[0, 3], [3, 1], [3, 0]])
     x = torch.arange(3, dtype=torch.float32).unsqueeze(1) + 1
     state, recv, _ = disp.dispatch(x, ids)
-    assert state.rows_per_expert == [2, 1, 0, 3] and state.padded_rows == 384
-    assert state.offsets.tolist() == [0, 128, 128, 256, 256, 384] and state.experts.tolist() == [0, 1, 3, -1]
+    assert state.rows_per_expert.tolist() == [2, 1, 0, 3] and state.padded_rows == 128 + 4 * 128
+    # every local expert has a segment; the one without rows is empty (start == end)
+    assert state.offsets.tolist() == [0, 128, 128, 256, 256, 256, 256, 384] and state.experts.tolist() == [0, 1, 2, 3, -1]
     a = to_contiguous_layout(recv, state)
     assert a[:2, 0].tolist() == [1.0, 3.0] and a[128, 0] == 2.0 and a[256:259, 0].tolist() == [1.0, 2.0, 3.0]
     assert a.abs().sum() == 12.0
