@@ -71,6 +71,7 @@ EXPORTS = [
     "ag_fp4_sf_blocked_bytes",
     "ag_fp4_sf_to_blocked",
     "ag_measure_host_link",
+    "ag_measure_host_stream",
     "ag_selftest_wait_limit",
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
@@ -123,6 +124,8 @@ def load() -> ctypes.CDLL:
     lib.ag_move_rows.restype = c_int32
     lib.ag_combine_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p]
     lib.ag_combine_topk.restype = c_int32
+    lib.ag_measure_host_stream.argtypes = [c_uint64, c_int64, c_int32, c_int32, c_int32, c_int32, POINTER(c_double)]
+    lib.ag_measure_host_stream.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]

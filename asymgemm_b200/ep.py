@@ -173,30 +173,36 @@ def to_contiguous_layout(recv: torch.Tensor, state: DispatchState) -> torch.Tens
 _keepalive: list = []
 
 
-def pinned_empty(shape, dtype: torch.dtype, numa_node: Optional[int] = None) -> torch.Tensor:
-    """Pinned host tensor for expert weights, optionally bound to one NUMA node.
+def pinned_empty(shape, dtype: torch.dtype, numa_node: Optional[int] = None, huge_pages: bool = False) -> torch.Tensor:
+    """Pinned host tensor for expert weights, optionally bound to one NUMA node and/or backed by transparent huge pages.
 
-    With `numa_node`: anonymous mmap -> mbind(MPOL_BIND) -> cudaHostRegister, the recipe the reference uses for its
-    NUMA-bound slabs (asym_gemm/unified_moe/runtime.py:236-279); any failure falls back to torch's pinned allocator.
+    With `numa_node` or `huge_pages`: anonymous mmap -> [madvise(MADV_HUGEPAGE)] -> [mbind(MPOL_BIND)] ->
+    cudaHostRegister, the recipe the reference uses for its NUMA-bound slabs
+    (asym_gemm/unified_moe/runtime.py:236-279); any failure falls back to torch's pinned allocator.
     Pages are faulted in on first write, so fill the tensor from a thread running on that node.
     """
     numel = 1
     for s in shape:
         numel *= int(s)
-    if numa_node is not None and numa_node >= 0:
+    if (numa_node is not None and numa_node >= 0) or huge_pages:
         try:
             nbytes = max(1, numel * torch.empty((), dtype=dtype).element_size())
-            mm = mmap.mmap(-1, nbytes)
-            addr = ctypes.addressof(ctypes.c_char.from_buffer(mm))
+            two_mb = 2 << 20
+            mm = mmap.mmap(-1, (nbytes + two_mb - 1) // two_mb * two_mb + two_mb)
+            base = ctypes.addressof(ctypes.c_char.from_buffer(mm))
+            addr = (base + two_mb - 1) // two_mb * two_mb          # 2 MB aligned start inside the mapping
             libc = ctypes.CDLL(None, use_errno=True)
-            mask = ctypes.c_ulong(1 << numa_node)
-            if libc.syscall(237, ctypes.c_void_p(addr), ctypes.c_size_t(nbytes), 2, ctypes.byref(mask), 65, 0) != 0:
+            if huge_pages and libc.madvise(ctypes.c_void_p(addr), ctypes.c_size_t((nbytes + two_mb - 1) // two_mb * two_mb), 14) != 0:
+                raise OSError("madvise(MADV_HUGEPAGE) failed")
+            mask = ctypes.c_ulong(1 << max(numa_node or 0, 0))
+            if numa_node is not None and numa_node >= 0 and \
+                    libc.syscall(237, ctypes.c_void_p(addr), ctypes.c_size_t(nbytes), 2, ctypes.byref(mask), 65, 0) != 0:
                 raise OSError("mbind failed")
             rc = torch.cuda.cudart().cudaHostRegister(addr, nbytes, 0)
             if int(rc) != 0:
                 raise OSError(f"cudaHostRegister returned {rc}")
             _keepalive.append(mm)
-            return torch.frombuffer(mm, dtype=dtype, count=numel).view(*shape)
+            return torch.frombuffer(mm, dtype=dtype, count=numel, offset=addr - base).view(*shape)
         except Exception:
             pass
     return torch.empty(*shape, dtype=dtype).pin_memory()

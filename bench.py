@@ -51,7 +51,7 @@ def rows_per_expert(cfg, seed=0):
     return torch.bincount(picks.flatten(), minlength=e).tolist()
 
 
-def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False):
+def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False):
     """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
     from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
                                      per_token_cast_to_fp8, per_token_cast_to_int8)
@@ -80,7 +80,11 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False):
         else:
             a[start:start + rows] = x.to(torch.bfloat16)
 
-    b_host = torch.empty((g, n, k), dtype=a_dtype).pin_memory()
+    if huge_pages:
+        from asymgemm_b200 import ep
+        b_host = ep.pinned_empty((g, n, k), a_dtype, None, huge_pages=True)
+    else:
+        b_host = torch.empty((g, n, k), dtype=a_dtype).pin_memory()
     sfb = None
     if kind == "fp8":
         sfb = torch.empty((g, (n + 127) // 128, (k + 127) // 128), dtype=torch.float32, device=device)
@@ -258,6 +262,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weights", default="host", choices=["host", "device"],
                     help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
+    ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
     ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
     ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
     args = ap.parse_args()
@@ -294,7 +299,7 @@ def main():
 
     moe = cfg["kind"] == "moe"
     on_dev = args.weights == "device"
-    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device, weights_on_device=on_dev)
+    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages)
     if on_dev:
         config["workload"] = config["workload"].replace("B in pinned host DRAM", "B resident in HBM")
     lib = _lib.load()
@@ -307,10 +312,24 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    # measured host-link peak (copy engine, pinned -> device), rank by rank so links are measured alone
+    # measured host-link peak (copy engine, pinned -> device): each rank alone (the others idle), then all ranks at once
     peak = _lib.c_double(0.0)
+    link_peak = 0.0
+    for r in range(world):
+        barrier()
+        if r == rank:
+            _lib.check(lib.ag_measure_host_link(1 << 30, 3, peak))
+            link_peak = peak.value
+    barrier()
     _lib.check(lib.ag_measure_host_link(1 << 30, 3, peak))
-    link_peak = peak.value
+    link_peak_together = peak.value
+    barrier()
+    # copy-only TMA stream with the weight producer's access pattern, all ranks at once (reference for SM-issued reads)
+    row_bytes = int((cfg["hidden"] if moe else cfg["k"] * ELEM_BYTES[cfg["kind"]]))
+    row_bytes = max(128, row_bytes // 128 * 128)
+    _lib.check(lib.ag_measure_host_stream(1 << 30, row_bytes, 64, 2, 0, 2, peak))
+    stream_ceiling = peak.value
+    barrier()
 
     for _ in range(args.warmup):
         run_op(w)
@@ -368,7 +387,9 @@ def main():
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     ag.check_status()
 
-    stats = torch.tensor([total_ms / args.steps, e2e_ms, kernel_ms, w["flops"], w["host_bytes"], link_peak], dtype=torch.float64, device=device)
+    my_gbs = w["host_bytes"] / (total_ms / args.steps * 1e-3) / 1e9
+    stats = torch.tensor([total_ms / args.steps, e2e_ms, kernel_ms, w["flops"], w["host_bytes"], link_peak, link_peak_together,
+                          stream_ceiling, my_gbs], dtype=torch.float64, device=device)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -379,9 +400,15 @@ def main():
         ms_step, e2e_ms, kernel_ms = mx[0].item(), mx[1].item(), mx[2].item()
         flops, host_bytes = sm[3].item(), sm[4].item()
         link_peak_sum, link_peak_min = sm[5].item(), mn[5].item()
+        together_sum, together_min = sm[6].item(), mn[6].item()
+        ceil_sum, ceil_min = sm[7].item(), mn[7].item()
+        rank_gbs_min, rank_gbs_max = mn[8].item(), mx[8].item()
     else:
+        ceil_sum = ceil_min = stream_ceiling
+        rank_gbs_min = rank_gbs_max = my_gbs
         ms_step, flops, host_bytes = stats[0].item(), w["flops"], w["host_bytes"]
         link_peak_sum = link_peak_min = link_peak
+        together_sum = together_min = link_peak_together
 
     if rank == 0:
         tflops = flops / (ms_step * 1e-3) / 1e12
@@ -404,7 +431,15 @@ def main():
             "config": config,
             "host_link": {"weight_gbs": round(host_gbs, 2), "peak_gbs_sum": round(link_peak_sum, 2),
                           "frac_of_measured_peak": round(host_gbs / link_peak_sum, 4), "per_gpu_peak_min_gbs": round(link_peak_min, 2),
-                          "peak_how": "cudaMemcpyAsync pinned->device, 1 GiB, best of 3, measured in this run on each rank"},
+                          "peak_all_ranks_at_once_gbs_sum": round(together_sum, 2), "per_gpu_at_once_min_gbs": round(together_min, 2),
+                          "frac_of_peak_all_ranks_at_once": round(host_gbs / together_sum, 4),
+                          "tma_copy_only_all_ranks_at_once_gbs_sum": round(ceil_sum, 2), "tma_copy_only_per_gpu_min_gbs": round(ceil_min, 2),
+                          "per_rank_weight_gbs_min_max": [round(rank_gbs_min, 2), round(rank_gbs_max, 2)],
+                          "peak_how": "cudaMemcpyAsync pinned->device, 1 GiB, best of 3, measured in this run: peak_gbs_sum adds each "
+                                      "rank's rate measured while the others idle, peak_all_ranks_at_once adds the rates measured "
+                                      "with every rank copying at the same time; tma_copy_only is a copy-only TMA kernel with the weight "
+                                      "producer's access pattern on every SM, all ranks at once (a reference, not a bound). The step ends when the slowest rank ends, so "
+                                      "with even sharding weight_gbs <= n_gpus x the slowest rank's link rate"},
             "roofline": {"bound": "host_link", "achieved": round(ach, 2), "peak": round(link_peak, 2), "unit": "GB/s",
                          "frac": round(ach / link_peak, 4),
                          "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload] * w["m_total"] / 1e9, 3)

@@ -174,6 +174,13 @@ int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weig
  * (csrc/ep_steal/ep_steal_sync.cu:63-64) and whose device asserts trap (asym_gemm/include/asym_gemm/common/utils.cuh:24-40). */
 int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
 
+/* Copy-only ceiling for SM-issued reads of pinned memory: streams a `bytes` pinned buffer laid out as rows of `row_bytes`
+ * through shared memory with the weight producer's TMA pattern (each CTA owns columns of `box_rows` rows and walks K in
+ * 128-byte boxes, `boxes_per_stage` per stage) on `num_ctas` CTAs (0 = all SMs), best of `reps`. Reference counterpart:
+ * none (its authors report ~21.5 GB/s for in-kernel TMA reads, asym_gemm/unified_moe/runtime.py:113-116). */
+int ag_measure_host_stream(uint64_t bytes, int64_t row_bytes, int32_t box_rows, int32_t boxes_per_stage, int32_t num_ctas,
+                           int32_t reps, double* gbps_out);
+
 const char* ag_last_error(void);
 const char* ag_version(void);
 
