@@ -17,6 +17,7 @@ from .api import (  # noqa: F401
     m_grouped_int8_asym_gemm_nt_contiguous,
     m_grouped_int8_asym_gemm_nt_masked,
     set_num_sms,
+    set_split_segments,
     set_tile_config,
     set_use_scratch,
     set_wait_limit_ms,

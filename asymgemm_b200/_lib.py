@@ -53,6 +53,7 @@ class GemmDesc(Structure):
         ("raw_dump", c_void_p),
         ("alpha", c_float),
         ("tile_config", c_int32),
+        ("no_split", c_int32),
     ]
 
 

@@ -24,7 +24,7 @@ from . import _lib
 from ._lib import GemmDesc
 
 _MK_ALIGNMENT = 128
-_state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0}
+_state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0}
 _scratch_cache: dict = {}
 _status_cache: dict = {}
 _dev_copy_cache: dict = {}
@@ -57,6 +57,11 @@ def set_wait_limit_ms(ms: int) -> None:
 def set_tile_config(tile: int) -> None:
     """Force a tile configuration (see ``ag_gemm_desc_t.tile_config``); 0 = choose from where B lives."""
     _state["tile_config"] = int(tile)
+
+
+def set_split_segments(flag: bool) -> None:
+    """Device-resident B only: whether long segments are split into row chunks across CTAs (default) or kept whole."""
+    _state["no_split"] = 0 if flag else 1
 
 
 def set_use_scratch(flag: bool) -> None:
@@ -164,7 +169,8 @@ def _common_checks(a, b, d, masked: bool, k_div: int = 1):
         m_, n_ = d.shape
         _require(m == m_ and n == n_ and k == k_, "shape mismatch between a, b and d")
     _require(n > 0 and k > 0 and g > 0, "n, k and num_groups must be positive")
-    _require(a.is_cuda and d.is_cuda, "a and d must be CUDA tensors")
+    _require(a.is_cuda, "a must be a CUDA tensor")
+    _require(d.is_cuda or d.is_pinned(), "d must be a CUDA tensor (or, as an extension, pinned host memory the kernel writes directly)")
     _require(a.is_contiguous(), "a must be K-major (contiguous)")
     _require(b.is_contiguous(), "b must be K-major [G, N, K] (contiguous)")
     _require(d.is_contiguous(), "d must be row-major (contiguous)")
@@ -202,6 +208,7 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
         desc.raw_dump = raw_dump.data_ptr() if raw_dump is not None else None
         desc.alpha = alpha
         desc.tile_config = _state["tile_config"]
+        desc.no_split = _state["no_split"]
         _lib.check(getattr(lib, fn_name)(desc))
 
 

@@ -197,7 +197,14 @@ int run(int kind, const ag_gemm_desc_t* g) {
   p.b_streaming = res == RES_HOST_MAPPED;
   p.alpha = g->alpha == 0.f ? 1.f : g->alpha;
 
-  const long long items = static_cast<long long>(p.max_segments) * p.n_tiles;
+  // Device-resident weights: split long segments into accumulator-sized row chunks so that work spreads evenly.
+  // Host-resident weights keep whole segments per item: the weight column must cross the host link only once.
+  if (res != RES_HOST_MAPPED && !g->no_split) {
+    const int slots = (512 - (kind == 3 ? 64 : 0)) / bn;
+    p.split_rows = 128 * ((kind == 1 || kind == 2) ? slots - 2 : slots);
+  }
+  const long long seg_items = p.split_rows > 0 ? rows_total / p.split_rows + p.max_segments : p.max_segments;
+  const long long items = seg_items * p.n_tiles;
   const int grid = static_cast<int>(items < grid_cap ? items : grid_cap);
   if (grid <= 0) return AG_OK;
 

@@ -70,6 +70,7 @@ struct GemmParams {
   int d_fp32;
   int use_scratch;         // 1 = replay long segments from the scratch copy, 0 = re-read B from its source
   int b_streaming;         // 1 = B is host memory: mark its lines evict-first in L2
+  int split_rows;          // > 0: split segments into chunks of this many rows (one accumulator chunk) per item
   float alpha;             // NVFP4 global scale (product of the two tensor-level scales), 1.0 otherwise
 };
 
@@ -80,31 +81,64 @@ struct Item {
   int nt;
 };
 
-// Returns 0 when the CTA has run out of work, 1 otherwise (rows may still be 0: skip).
-__device__ __forceinline__ int fetch_item(const GemmParams& p, long long item, Item& it) {
-  const int seg = static_cast<int>(item / p.n_tiles);
-  it.nt = static_cast<int>(item - static_cast<long long>(seg) * p.n_tiles);
+// Row range and weight index of segment `seg`. Returns 0 past the end of the segment list.
+__device__ __forceinline__ int read_segment(const GemmParams& p, int seg, int& expert, int& row0, int& rows) {
   if (seg >= p.max_segments) return 0;
   if (p.layout == LAYOUT_MASKED) {
-    it.expert = seg;
-    it.row0 = seg * p.m_max;
-    int r = __ldg(p.masked_m + seg);
-    it.rows = r < 0 ? 0 : (r > p.m_max ? p.m_max : r);
+    expert = seg;
+    row0 = seg * p.m_max;
+    const int r = __ldg(p.masked_m + seg);
+    rows = r < 0 ? 0 : (r > p.m_max ? p.m_max : r);
   } else {
     const int e = __ldg(p.experts + seg);
     if (e < 0) return 0;
-    it.expert = e;
+    expert = e;
     int r0 = __ldg(p.offsets + 2 * seg), r1 = __ldg(p.offsets + 2 * seg + 1);
     if (r0 < 0) r0 = 0;
     if (r1 > p.rows_total) r1 = static_cast<int>(p.rows_total);
-    it.row0 = r0;
-    it.rows = r1 > r0 ? r1 - r0 : 0;
+    row0 = r0;
+    rows = r1 > r0 ? r1 - r0 : 0;
     if (e >= p.num_groups) {  // would read outside B: flag it and skip
       atomicCAS(p.status, 0, ST_BAD_EXPERT | (static_cast<int>(blockIdx.x) << 8));
-      it.rows = 0;
+      rows = 0;
     }
   }
   return 1;
+}
+
+// Position of a role's walk through the item list when segments are split into row chunks (p.split_rows > 0).
+struct ItemCursor {
+  int seg = 0;
+  long long first = 0;  // index of the first item of segment `seg`
+};
+
+// Maps item index -> work. Returns 0 when the CTA has run out of work, 1 otherwise (rows may still be 0: skip).
+// Whole-segment mode (weights streamed from the host): item = (segment, n-tile), the segment's column is fetched once.
+// Split mode (weights in device memory, p.split_rows = rows of one accumulator chunk): item = (segment, row chunk, n-tile)
+// with the n-tile fastest, so that long segments spread over many CTAs and CTAs running together share A rows in L2.
+// Item indices seen by one role only grow, so the cursor advances monotonically: O(segments) reads per CTA in total.
+__device__ __forceinline__ int fetch_item(const GemmParams& p, long long item, ItemCursor& cur, Item& it) {
+  if (p.split_rows <= 0) {
+    const int seg = static_cast<int>(item / p.n_tiles);
+    it.nt = static_cast<int>(item - static_cast<long long>(seg) * p.n_tiles);
+    return read_segment(p, seg, it.expert, it.row0, it.rows);
+  }
+  while (true) {
+    int expert, row0, rows;
+    if (!read_segment(p, cur.seg, expert, row0, rows)) return 0;
+    const long long chunks = (rows + p.split_rows - 1) / p.split_rows;
+    const long long local = item - cur.first;
+    if (local < chunks * p.n_tiles) {
+      const int chunk = static_cast<int>(local / p.n_tiles);
+      it.nt = static_cast<int>(local - static_cast<long long>(chunk) * p.n_tiles);
+      it.expert = expert;
+      it.row0 = row0 + chunk * p.split_rows;
+      it.rows = min(p.split_rows, rows - chunk * p.split_rows);
+      return 1;
+    }
+    cur.first += chunks * p.n_tiles;
+    ++cur.seg;
+  }
 }
 
 struct WaitCtx {
@@ -293,10 +327,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t jt = 0;  // stage uses so far
       bool ok = true;
+      ItemCursor cursor;
       const uint64_t pol_stream = l2_policy_evict_first();
       for (long long item = blockIdx.x; ok; item += gridDim.x) {
         Item it;
-        if (!fetch_item(p, item, it)) break;
+        if (!fetch_item(p, item, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         const int chunks = (mtiles + CHUNK_TILES - 1) / CHUNK_TILES;
@@ -369,9 +404,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t it_a = 0;
       bool ok = true;
+      ItemCursor cursor;
       for (long long item = blockIdx.x; ok; item += gridDim.x) {
         Item it;
-        if (!fetch_item(p, item, it)) break;
+        if (!fetch_item(p, item, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
@@ -403,9 +439,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t it_a = 0, jt = 0, rt = 0, slot_phase = 0;
       bool ok = true;
+      ItemCursor cursor;
       for (long long item = blockIdx.x; ok; item += gridDim.x) {
         Item it;
-        if (!fetch_item(p, item, it)) break;
+        if (!fetch_item(p, item, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
@@ -484,9 +521,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t rt = 0, slot_phase = 0;
     bool ok = true;
+    ItemCursor cursor;
     for (long long item = blockIdx.x; ok; item += gridDim.x) {
       Item it;
-      if (!fetch_item(p, item, it)) break;
+      if (!fetch_item(p, item, cursor, it)) break;
       if (it.rows <= 0) continue;
       const int mtiles = (it.rows + BM - 1) / BM;
       const int n0 = it.nt * BN;

@@ -34,6 +34,9 @@ WORKLOADS = {
     "c3_fp8": dict(kind="fp8", experts=256, k=7168, n=4096, tokens=16384, top_k=8, zipf=0.8),
     "c2_bf16": dict(kind="bf16", experts=128, k=2048, n=1536, tokens=8192, top_k=8, zipf=1.0),
     "c1_int8": dict(kind="int8", experts=16, k=2048, n=1536, tokens=2048, top_k=4, zipf=0.0),
+    "c2b_bf16": dict(kind="bf16", experts=128, k=768, n=2048, tokens=8192, top_k=8, zipf=1.0),
+    # NVFP4, masked layout: 1024 rows per expert, valid counts from the routing, capped at the stride
+    "c4_fp4": dict(kind="fp4", experts=128, k=4096, n=3072, tokens=16384, top_k=8, zipf=1.0, masked_stride=1024),
     # whole FP8 MoE layer, expert-parallel: gate+up (K=hidden, N=2*inter), SiLU*mul, down (K=inter, N=hidden)
     "c5_moe_fp8": dict(kind="moe", experts=256, hidden=7168, inter=2048, tokens=65536, top_k=8),
 }
@@ -144,9 +147,42 @@ def build_moe(cfg, rank, world, device, group, seed=0):
                 nvlink_bytes=float(rows) * (h + h // 128 * 4 + 2 * h))
 
 
+def build_masked_fp4(cfg, rank, world, device, seed=0):
+    """NVFP4 masked-layout operands: A [G, stride, K/2] + e4m3 scales on the device, B and its scales in pinned host memory."""
+    from asymgemm_b200.utils import per_token_cast_to_nvfp4_e4m3
+    k, n, stride = cfg["k"], cfg["n"], cfg["masked_stride"]
+    counts = rows_per_expert(cfg, seed)
+    per = cfg["experts"] // world
+    counts = [min(c, stride) for c in counts[rank * per:(rank + 1) * per]]
+    g = len(counts)
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    a = torch.zeros((g, stride, k // 2), dtype=torch.uint8, device=device)
+    sfa = torch.zeros((g, stride, k // 16), dtype=torch.float8_e4m3fn, device=device)
+    b = torch.empty((g, n, k // 2), dtype=torch.uint8).pin_memory()
+    sfb = torch.empty((g, n, k // 16), dtype=torch.float8_e4m3fn).pin_memory()
+    for e in range(g):
+        if counts[e]:
+            q, s = per_token_cast_to_nvfp4_e4m3(torch.randn((counts[e], k), device=device, generator=gen))
+            a[e, :counts[e]], sfa[e, :counts[e]] = q, s
+        q, s = per_token_cast_to_nvfp4_e4m3(torch.randn((n, k), device=device, generator=gen) * 0.02)
+        b[e].copy_(q, non_blocking=True)
+        sfb[e].copy_(s, non_blocking=True)
+    torch.cuda.synchronize(device)
+    valid = sum(counts)
+    active = sum(1 for c in counts if c > 0)
+    return dict(kind="fp4", a=a, sfa=sfa, b=b, sfb=sfb, d=torch.empty((g, stride, n), dtype=torch.bfloat16, device=device),
+                masked_m=torch.tensor(counts, dtype=torch.int32, device=device), counts=counts, g=g, n=n, k=k, m_total=g * stride,
+                # the weight scales are re-laid out once and then stay on the device, so only the packed values stream per call
+                flops=2.0 * n * k * valid, host_bytes=active * n * k * 0.5, segs=None)
+
+
 def run_op(w, a=None, sfa=None, d=None):
     if w["kind"] == "moe":
         return w["layer"].forward(w["x"] if a is None else a, w["ids"], w["w"])
+    if w["kind"] == "fp4":
+        import asymgemm_b200 as ag
+        return ag.m_grouped_fp4_asym_gemm_nt_masked((w["a"] if a is None else a, w["sfa"] if sfa is None else sfa), (w["b"], w["sfb"]),
+                                                    w["d"] if d is None else d, w["masked_m"], max(1, sum(w["counts"]) // w["g"]))
     import asymgemm_b200 as ag
     a = w["a"] if a is None else a
     sfa = w["sfa"] if sfa is None else sfa
@@ -209,6 +245,8 @@ def cpu_reference_sample(cfg, w, threads, max_experts):
     import numpy as np
     from oracle import oracle as O
     kind, n, k = w["kind"], w["n"], w["k"]
+    if kind == "fp4":
+        return _cpu_reference_fp4(w, threads, max_experts)
     segs = [s for s in w["segs"] if s[2] > 0][:max_experts]
     torch.set_num_threads(threads)
     flops = 0.0
@@ -251,6 +289,30 @@ def cpu_reference_sample(cfg, w, threads, max_experts):
     return flops / dt / 1e12, f"{len(segs)} experts of this workload, torch CPU bf16 `a[s:e] @ w.t()` per expert", "port", threads
 
 
+def _dequant_fp4(packed, sf):
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=torch.float32, device=packed.device)
+    vals = torch.stack([lut[(packed & 0xF).long()], lut[(packed >> 4).long()]], dim=-1).flatten(-2)
+    return vals * sf.float().repeat_interleave(16, dim=-1)
+
+
+def _cpu_reference_fp4(w, threads, max_experts):
+    """torch CPU bf16 loop over the first experts of the masked NVFP4 workload (operands dequantised beforehand)."""
+    torch.set_num_threads(threads)
+    ops, flops = [], 0.0
+    for e in [i for i, c in enumerate(w["counts"]) if c > 0][:max_experts]:
+        rows = w["counts"][e]
+        a = _dequant_fp4(w["a"][e, :rows], w["sfa"][e, :rows]).to(torch.bfloat16).cpu()
+        b = _dequant_fp4(w["b"][e].to(w["a"].device), w["sfb"][e].to(w["a"].device)).to(torch.bfloat16).cpu()
+        ops.append((a, b))
+        flops += 2.0 * rows * w["n"] * w["k"]
+    ops[0][0] @ ops[0][1].t()
+    t0 = time.perf_counter()
+    for a, b in ops:
+        a @ b.t()
+    dt = time.perf_counter() - t0
+    return flops / dt / 1e12, f"{len(ops)} experts of this workload, torch CPU bf16 `a[:m] @ w.t()` per expert", "port", threads
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -262,6 +324,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weights", default="host", choices=["host", "device"],
                     help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
+    ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
     ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
     ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
     ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
@@ -279,7 +342,8 @@ def main():
                 f"N={cfg['hidden']}), {cfg['experts']} experts sharded over the ranks, {cfg['tokens']} tokens x top-{cfg['top_k']} "
                 f"(softmax of N(0,1) logits), token all-to-all over NCCL, weights in pinned host DRAM per rank")
     else:
-        desc = (f"{args.workload}: m-grouped contiguous {cfg['kind']} GEMM, {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
+        layout = f"masked (stride {cfg['masked_stride']})" if "masked_stride" in cfg else "contiguous"
+        desc = (f"{args.workload}: m-grouped {layout} {cfg['kind']} GEMM, {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
                 f"{cfg['tokens']} tokens x top-{cfg['top_k']}, Zipf({cfg['zipf']}), B in pinned host DRAM")
     config = {"workload": desc, "experts_per_gpu": cfg["experts"] // world,
               "l2": "inputs larger than L2 (weights are re-read from host memory every step)"}
@@ -299,7 +363,12 @@ def main():
 
     moe = cfg["kind"] == "moe"
     on_dev = args.weights == "device"
-    w = build_moe(cfg, rank, world, device, None) if moe else build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages)
+    if moe:
+        w = build_moe(cfg, rank, world, device, None)
+    elif cfg["kind"] == "fp4":
+        w = build_masked_fp4(cfg, rank, world, device)
+    else:
+        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages)
     if on_dev:
         config["workload"] = config["workload"].replace("B in pinned host DRAM", "B resident in HBM")
     lib = _lib.load()
@@ -368,20 +437,41 @@ def main():
         a_dev, d_dev = torch.empty_like(w["a"]), torch.empty_like(w["d"])
         sfa_dev = torch.empty_like(w["sfa"]) if w["sfa"] is not None else None
 
+        # Results leave through a second stream and two device buffers, so the device->host read of step i (the idle
+        # direction of the link) overlaps the kernel of step i+1; uploads share the weights' direction and stay in order.
+        out_stream = torch.cuda.Stream(device=device)
+        d_bufs = [d_dev, torch.empty_like(d_dev)]
+        done = [torch.cuda.Event(), torch.cuda.Event()]
+        copied = [torch.cuda.Event(), torch.cuda.Event()]
+        e2e_count = [0]
+
         def e2e_step():
+            j = e2e_count[0] & 1
+            e2e_count[0] += 1
+            main = torch.cuda.current_stream(device)
+            main.wait_event(copied[j])
             a_dev.copy_(a_host, non_blocking=True)
             if sfa_dev is not None:
                 sfa_dev.copy_(sfa_host, non_blocking=True)
-            run_op(w, a_dev, sfa_dev, d_dev)
-            d_host.copy_(d_dev, non_blocking=True)
+            if args.d_host:
+                run_op(w, a_dev, sfa_dev, d_host)
+                return
+            run_op(w, a_dev, sfa_dev, d_bufs[j])
+            done[j].record(main)
+            with torch.cuda.stream(out_stream):
+                out_stream.wait_event(done[j])
+                d_host.copy_(d_bufs[j], non_blocking=True)
+                copied[j].record(out_stream)
 
     e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_steps = max(2, min(args.steps, 4))
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    if not moe:
+        torch.cuda.current_stream(device).wait_stream(out_stream)   # the last result has reached the host
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
@@ -420,13 +510,13 @@ def main():
             peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
         except Exception:
             pass
-        tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0, "moe": 2.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
+        tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0, "moe": 2.0, "fp4": 4.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
         line = {
             "metric": "grouped-GEMM TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)",
             "value": round(tflops, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"fp8": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)", "int8": "int8 (int32 accumulate)",
-                      "moe": "fp8_e4m3 (fp32 accumulate)"}[cfg["kind"]],
+                      "moe": "fp8_e4m3 (fp32 accumulate)", "fp4": "nvfp4 e2m1 + ue4m3 block scales (fp32 accumulate)"}[cfg["kind"]],
             "data": "synthetic (seeded; shapes of the named config, random weights)",
             "config": config,
             "host_link": {"weight_gbs": round(host_gbs, 2), "peak_gbs_sum": round(link_peak_sum, 2),
@@ -450,7 +540,8 @@ def main():
                                  "host link, not HBM or tensor throughput: peak is the copy-engine rate measured in this run",
                          "tensor_frac_of_measured": round(w["flops"] / (kernel_ms * 1e-3) / 1e12 / tensor_peak, 5)},
             "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
-                    "h2d_bytes_per_step": int(a_host.numel() * a_host.element_size() + (sfa_host.numel() * 4 if sfa_host is not None else 0)),
+                    "h2d_bytes_per_step": int(a_host.numel() * a_host.element_size()
+                                              + (sfa_host.numel() * sfa_host.element_size() if sfa_host is not None else 0)),
                     "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
                     "note": "weights are read from pinned host memory inside the kernel in both timings"},
             "gpu_launches": args.steps * (2 if moe else 1),

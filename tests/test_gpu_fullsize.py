@@ -60,3 +60,31 @@ def test_full_size_properties(name, experts):
         worst = max(worst, float(err))
     tol = 1e-2 if w["kind"] == "bf16" else 2e-2
     assert worst <= tol, f"max-rel {worst:.3e} > {tol}"
+
+
+def test_full_size_nvfp4_masked_properties():
+    """C4: NVFP4 masked layout, 128 experts x 1024-row stride, K=4096, N=3072, weights and their scales in pinned host
+    memory: sampled blocks against a torch fp32 product of the dequantised operands, untouched rows, run-to-run identity."""
+    cfg = dict(bench.WORKLOADS["c4_fp4"])
+    w = bench.build_masked_fp4(cfg, 0, 1, torch.device("cuda", 0))
+    w["d"].fill_(float("nan"))
+    bench.run_op(w)
+    ag.check_status()
+    d1 = w["d"].clone()
+    bench.run_op(w)
+    ag.check_status()
+    assert torch.equal(d1.view(torch.int16), w["d"].view(torch.int16))
+    gen = torch.Generator().manual_seed(1)
+    worst = 0.0
+    assert max(w["counts"]) == 1024 and min(w["counts"]) < 1024   # the routing law caps some experts and not others
+    for e, rows in enumerate(w["counts"]):
+        assert torch.isnan(w["d"][e, rows:]).all()
+        if rows == 0 or e % 8:
+            continue
+        n0 = int(torch.randint(0, w["n"] // 128, (1,), generator=gen)) * 128
+        a = bench._dequant_fp4(w["a"][e, :rows], w["sfa"][e, :rows])
+        b = bench._dequant_fp4(w["b"][e, n0:n0 + 128].cuda(), w["sfb"][e, n0:n0 + 128].cuda())
+        ref = a @ b.t()
+        err = (w["d"][e, :rows, n0:n0 + 128].float() - ref).abs().max() / ref.abs().max().clamp_min(1e-9)
+        worst = max(worst, float(err))
+    assert worst <= 2e-2, f"max-rel {worst:.3e}"

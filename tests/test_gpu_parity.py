@@ -220,3 +220,94 @@ def test_wait_limit_expires_with_status_and_context_stays_usable():
     _run_contiguous(c, d)
     ag.check_status()
     _check("bf16", d.float().cpu().numpy(), c["ref"], c["segments"])
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_same_expert_in_two_segments_and_unsorted_experts(kind):
+    """Segments need not be sorted by expert and one expert may own two segments (each re-reads its weights)."""
+    c = H.make_contiguous_case(kind, [128, 256, 128], 256, 512, seed=31)
+    # rewrite the table: expert 2 first, then expert 0 twice (rows of old expert 1 are given to expert 0's weights)
+    offsets = torch.tensor([384, 512, 0, 128, 128, 384], dtype=torch.int32, device="cuda")
+    experts = torch.tensor([2, 0, 0, -1], dtype=torch.int32, device="cuda")
+    segments = [(2, 384, 512), (0, 0, 128), (0, 128, 384)]
+    if kind == "bf16":
+        ref = oracle.gemm_bf16(H.np_bits(c["a"]), H.np_bits(c["b"]), segments)
+        d = torch.zeros((512, 256), dtype=torch.bfloat16, device="cuda")
+        ag.m_grouped_bf16_asym_gemm_nt_contiguous(c["a"], c["b"], d, offsets, experts, 4)
+    else:
+        ref = oracle.gemm_fp8(H.np_bits(c["a"]), c["sfa"].cpu().numpy(), H.np_bits(c["b"]), c["sfb"].cpu().numpy(), segments)
+        d = torch.zeros((512, 256), dtype=torch.bfloat16, device="cuda")
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (c["b"], c["sfb"]), d, offsets, experts, 4)
+    torch.cuda.synchronize()
+    _check(kind, d.float().cpu().numpy(), ref, segments)
+
+
+@pytest.mark.expects_status
+def test_list_size_limits_the_segments_visited_and_bad_expert_is_reported():
+    c = H.make_contiguous_case("bf16", [128, 128, 128], 128, 256, seed=32)
+    d = torch.zeros((384, 128), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_bf16_asym_gemm_nt_contiguous(c["a"], c["b"], d, c["offsets"], c["experts"], 2)   # visit 2 entries only
+    torch.cuda.synchronize()
+    assert (d[256:] == 0).all() and d[:256].abs().sum() > 0
+    # an expert id beyond the weight tensor is skipped and reported through the status word, nothing is read out of bounds
+    experts = torch.tensor([0, 7, 2, -1], dtype=torch.int32, device="cuda")
+    d.zero_()
+    ag.m_grouped_bf16_asym_gemm_nt_contiguous(c["a"], c["b"], d, c["offsets"], experts, 4)
+    with pytest.raises(RuntimeError, match="expert id"):
+        ag.check_status()
+    assert (d[128:256] == 0).all() and d[:128].abs().sum() > 0 and d[256:].abs().sum() > 0
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "int8"])
+def test_masked_stride_not_a_multiple_of_128(kind):
+    """M_max = 200: the last tile of a group overlaps the next group's rows in A but only valid rows are written."""
+    masked_m = [200, 7, 0, 150]
+    c = H.make_masked_case(kind, masked_m, 200, 128, 256, seed=33)
+    d = torch.full((4, 200, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _run_masked(c, d)
+    torch.cuda.synchronize()
+    d_np = d.float().cpu().numpy().reshape(-1, 128)
+    _check(kind, d_np, c["ref"], c["segments"])
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], 800)]).all()
+
+
+def test_masked_call_is_capturable_in_a_cuda_graph():
+    """The masked layout has a grid that does not depend on routing: capture once, replay with new row counts
+    (the property the reference calls CUDA-graph safe, csrc/jit_kernels/impls/sm100_fp8_asym_gemm_1d1d.hpp:284-292)."""
+    c = H.make_masked_case("bf16", [128, 128, 128], 128, 128, 256, seed=34)
+    d = torch.zeros((3, 128, 128), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_bf16_asym_gemm_nt_masked(c["a"], c["b"], d, c["masked_m"], 128)   # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ag.m_grouped_bf16_asym_gemm_nt_masked(c["a"], c["b"], d, c["masked_m"], 128)
+    full = c["ref"].reshape(3, 128, 128)
+    for counts in ([128, 0, 5], [1, 128, 64]):
+        c["masked_m"].copy_(torch.tensor(counts, dtype=torch.int32))
+        d.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = d.float().cpu().numpy()
+        for g, r in enumerate(counts):
+            if r:
+                assert oracle.max_rel(got[g, :r], full[g, :r]) <= 1e-2
+            assert np.isnan(got[g, r:]).all()
+    ag.check_status()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_device_resident_split_matches_whole_segments(kind):
+    """With B in device memory long segments are split into row chunks across CTAs; the result must not change."""
+    rows = [1500, 0, 700, 40, 2600]
+    c = H.make_contiguous_case(kind, rows, 384, 512, seed=41, b_on_host=False)
+    d1 = torch.zeros((c["m_total"], 384), dtype=torch.bfloat16, device="cuda")
+    d2 = torch.zeros_like(d1)
+    _run_contiguous(c, d1)
+    ag.set_split_segments(False)
+    try:
+        _run_contiguous(c, d2)
+    finally:
+        ag.set_split_segments(True)
+    torch.cuda.synchronize()
+    assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
+    _check(kind, d1.float().cpu().numpy(), c["ref"], c["segments"])
