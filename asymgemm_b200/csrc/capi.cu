@@ -181,7 +181,11 @@ int run(int kind, const ag_gemm_desc_t* g) {
   p.m_max = masked ? static_cast<int>(g->m) : 0;
   p.num_groups = g->num_groups;
   p.n = static_cast<int>(g->n);
-  int tile = g->tile_config > 0 ? g->tile_config - 1 : (res == RES_HOST_MAPPED ? agb::kTileHost : agb::kTileDevice);
+  int tile = g->tile_config > 0 ? g->tile_config - 1
+                                : (res == RES_HOST_MAPPED ? agb::kTileHost
+                                                          : ((kind == 1 || kind == 2) ? agb::kTileDeviceRegAcc : agb::kTileDevice));
+  if (tile == agb::kTileDeviceRegAcc)
+    AG_REQUIRE(kind == 1 || kind == 2, "tile_config 5 (register accumulators) exists for fp8 and int8 only");
   AG_REQUIRE(tile >= 0 && tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
   if (kind == 3) {
     AG_REQUIRE(agb::kTileConfigs[tile].bn >= 64, "nvfp4 supports tile_config 1 and 4 only (64 or 128 columns per item)");
@@ -200,8 +204,7 @@ int run(int kind, const ag_gemm_desc_t* g) {
   // Device-resident weights: split long segments into accumulator-sized row chunks so that work spreads evenly.
   // Host-resident weights keep whole segments per item: the weight column must cross the host link only once.
   if (res != RES_HOST_MAPPED && !g->no_split) {
-    const int slots = (512 - (kind == 3 ? 64 : 0)) / bn;
-    p.split_rows = 128 * ((kind == 1 || kind == 2) ? slots - 2 : slots);
+    p.split_rows = 128 * agb::chunk_tiles_of(kind, tile, bn);
   }
   const long long seg_items = p.split_rows > 0 ? rows_total / p.split_rows + p.max_segments : p.max_segments;
   const long long items = seg_items * p.n_tiles;

@@ -12,13 +12,19 @@ namespace agb {
 struct TileConfig {
   int bn, ka, sb;
 };
-constexpr int kNumTileConfigs = 4;
+constexpr int kNumTileConfigs = 5;
 constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
     {128, 1, 8},  // 0: B resident in device memory (tensor-core efficiency)
     {32, 4, 8},   // 1: B streamed from host memory, fewest host pages in flight per CTA
     {32, 8, 4},   // 2: as 1 with longer contiguous runs per row
     {64, 2, 8},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
+    {128, 1, 8},  // 4: FP8 / INT8 with B resident in device memory: scaled accumulators in registers, one tile per item
 };
+constexpr int kTileDeviceRegAcc = 4;
+// rows of one accumulator chunk (what one item covers when long segments are split)
+constexpr int chunk_tiles_of(int kind, int tile, int bn) {
+  return kind == 3 ? (512 - 64) / bn : ((kind == 1 || kind == 2) ? (tile == kTileDeviceRegAcc ? 1 : 512 / bn - 2) : 512 / bn);
+}
 // NVFP4 also stages 2 KB of scale factors per K atom and operand, so its host-streaming configuration uses
 // single-atom stages in a deeper ring to stay inside the 227 KB of shared memory.
 constexpr TileConfig kTileFp4Host = {64, 1, 12};
@@ -36,12 +42,12 @@ cudaError_t launch_fp4(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
 cudaError_t fp4_sf_to_blocked(const void* src, void* dst, long long groups, long long rows, long long k16, cudaStream_t stream);
 long long fp4_sf_k4_padded_host(long long k16);
 
-template <Kind KIND, int BN, int KA, int SB>
+template <Kind KIND, int BN, int KA, int SB, bool REG_ACC = false>
 cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ms,
                        const GemmParams& p) {
   using L = SmemLayout<BN, KA, kStagesA, SB, KindTraits<KIND>::block_scaled>;
   static_assert(L::dyn_bytes <= 232448, "tile configuration does not fit in shared memory");
-  auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB>;
+  auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB, REG_ACC>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -51,7 +57,7 @@ cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, con
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kernel<<<grid, NUM_THREADS, L::dyn_bytes, stream>>>(ma, mb, ms, p);
+  kernel<<<grid, num_threads_of<KIND, REG_ACC>(), L::dyn_bytes, stream>>>(ma, mb, ms, p);
   return cudaGetLastError();
 }
 
@@ -62,6 +68,9 @@ cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
     case 1: return launch_one<KIND, 32, 4, 8>(grid, stream, ma, mb, ms, p);
     case 2: return launch_one<KIND, 32, 8, 4>(grid, stream, ma, mb, ms, p);
     case 3: return launch_one<KIND, 64, 2, 8>(grid, stream, ma, mb, ms, p);
+    case 4:
+      if constexpr (KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 8, true>(grid, stream, ma, mb, ms, p);
+      else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }
 }

@@ -260,8 +260,20 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
   }
 }
 
-template <Kind KIND, int BN, int KA, int SA, int SB>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// REG_ACC (software-scaled kinds only): the scaled fp32 accumulators of ONE 128-row tile live in the drain warps'
+// registers instead of TMEM, all TMEM slots hold raw per-K-block products (a 512/BN-deep MMA pipeline) and the drain
+// does one tcgen05.ld + fma per block instead of ld + ld + st. Used when the weights are device-resident, where items are
+// one tile tall anyway and the drain, not the host link, sets the pace.
+// Drain warpgroups. INT8 with REG_ACC uses two (384 threads): warps 4-7 own the low half of the tile's columns, warps 8-11
+// the high half, so each thread keeps BN/2 accumulators and the per-column scaling is shared out (measured: 272 -> 383
+// TFLOP/s on the 16-expert INT8 case). FP8, whose block scale is one scalar per tile, is not drain-bound and keeps one.
+template <Kind KIND, bool REG_ACC>
+__host__ __device__ constexpr int drain_wgs_of() { return (REG_ACC && KIND == Kind::INT8) ? 2 : 1; }
+template <Kind KIND, bool REG_ACC>
+__host__ __device__ constexpr int num_threads_of() { return 128 + 128 * drain_wgs_of<KIND, REG_ACC>(); }
+
+template <Kind KIND, int BN, int KA, int SA, int SB, bool REG_ACC = false>
+__global__ void __launch_bounds__(num_threads_of<KIND, REG_ACC>(), 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
   using T = KindTraits<KIND>;
@@ -271,8 +283,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // TMEM plan: 512 / BN slots of BN columns. Hardware-accumulated kinds keep one output tile per slot; software-scaled
   // kinds keep scaled fp32 tiles in slots [0, CHUNK_TILES) and double-buffer the raw per-K-block product in the last two.
   constexpr int NUM_SLOTS = (TMEM_COLS - (T::block_scaled ? SF_TMEM_COLS : 0)) / BN;
-  constexpr int CHUNK_TILES = T::sw_scale ? NUM_SLOTS - 2 : NUM_SLOTS;
+  static_assert(!REG_ACC || T::sw_scale, "REG_ACC applies to the software-scaled kinds");
+  constexpr int RAW_SLOTS = REG_ACC ? NUM_SLOTS : 2;                 // raw product slots (software-scaled kinds)
+  constexpr int CHUNK_TILES = T::sw_scale ? (REG_ACC ? 1 : NUM_SLOTS - 2) : NUM_SLOTS;
+  constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
   constexpr uint32_t IDESC = T::block_scaled ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);
+  constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, REG_ACC>();   // one arrival per drain warp
   constexpr uint32_t SF_COL0 = NUM_SLOTS * BN;   // first TMEM column of the scale-factor area
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
 
@@ -302,7 +318,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (threadIdx.x == 0) {
     for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-    for (int i = 0; i < 16; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], 4); }
+    for (int i = 0; i < 16; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], DRAIN_ARRIVALS); }
     mbar_init(done_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -459,9 +475,9 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               if (!ok) break;
               uint32_t d_col;
               if constexpr (T::sw_scale) {
-                const uint32_t rs = rt & 1;
-                ok = wait_bar(&tm_empty[rs], ((rt >> 1) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
-                d_col = (CHUNK_TILES + rs) * BN;
+                const uint32_t rs = rt % RAW_SLOTS;
+                ok = wait_bar(&tm_empty[rs], ((rt / RAW_SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                d_col = (RAW_SLOT0 + rs) * BN;
               } else {
                 if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
                 d_col = mt * BN;
@@ -495,7 +511,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               }
               umma_commit(&a_empty[sa]);
               if constexpr (T::sw_scale) {
-                umma_commit(&tm_full[rt & 1]);
+                umma_commit(&tm_full[rt % RAW_SLOTS]);
                 ++rt;
               } else {
                 if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
@@ -531,7 +547,77 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const long long row_end = static_cast<long long>(it.row0) + it.rows;
       for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
         const int mc = min(CHUNK_TILES, mtiles - m0);
-        if constexpr (T::sw_scale) {
+        if constexpr (T::sw_scale && REG_ACC) {
+          // one 128-row tile per chunk; its scaled accumulators stay in registers across the whole K loop
+          constexpr int COLS = BN / drain_wgs_of<KIND, REG_ACC>();   // columns owned by this drain warpgroup
+          const int col_base = ((warp - 4) >> 2) * COLS;
+          const long long grow = static_cast<long long>(it.row0) + m0 * BM + row_in_tile;
+          const bool valid = grow < row_end;
+          float acc[COLS];
+          float* sfb_buf = sfb_smem + (warp - 4) * COLS;     // private to this warp
+          for (int kb = 0; kb < kb_count && ok; ++kb, ++rt) {
+            float sb_scalar = 0.f;
+            if constexpr (KIND == Kind::FP8) {
+              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + (n0 >> 7)) * p.sf_k + kb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < COLS / 32; ++j) {
+                const int col = n0 + col_base + j * 32 + lane;
+                sfb_buf[j * 32 + lane] =
+                    col < p.n ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + col) * p.sf_k + kb) : 0.f;
+              }
+              __syncwarp();
+            }
+            const float sa = valid ? __ldg(p.sfa + grow * p.sf_k + kb) : 0.f;
+            const uint32_t rs = rt % RAW_SLOTS;
+            ok = wait_bar(&tm_full[rs], (rt / RAW_SLOTS) & 1, wc, ST_TIMEOUT_TM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t raw_addr = lane_addr + (RAW_SLOT0 + rs) * BN + col_base;
+#pragma unroll
+            for (int cc = 0; cc < COLS / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(raw_addr + cc * 32, r);
+              tmem_wait_ld();
+              if (cc == COLS / 32 - 1) {  // this warp has read its part of the raw slot: hand it back before the arithmetic
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tm_empty[rs]);
+              }
+              if constexpr (KIND == Kind::INT8) {
+                if (p.raw_dump != nullptr && valid) {
+                  int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + cc * 32;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (n0 + col_base + cc * 32 + j < p.n) dst[j] = static_cast<int>(r[j]);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float prod, scale;
+                if constexpr (KIND == Kind::INT8) {
+                  prod = static_cast<float>(static_cast<int>(r[j]));
+                  scale = sa * sfb_buf[cc * 32 + j];
+                } else {
+                  prod = __uint_as_float(r[j]);
+                  scale = sa * sb_scalar;
+                }
+                acc[cc * 32 + j] = fmaf(prod, scale, kb > 0 ? acc[cc * 32 + j] : 0.f);
+              }
+            }
+            if constexpr (KIND == Kind::INT8) __syncwarp();  // everyone is done with sfb_buf before the next block refills it
+          }
+          if (ok && valid) {
+#pragma unroll
+            for (int cc = 0; cc < COLS / 32; ++cc) {
+              uint32_t v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[cc * 32 + j]);
+              store_row32(p, grow, n0 + col_base + cc * 32, v);
+            }
+          }
+        } else if constexpr (T::sw_scale) {
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             // column scales of this K block
             float sb_scalar = 0.f;

@@ -84,7 +84,7 @@ int ag_m_grouped_fp8_gemm_nt_static_scratch(const ag_gemm_desc_t* desc) {
   bool host_b = false;
   if (cudaPointerGetAttributes(&at, desc->b) == cudaSuccess) host_b = at.type == cudaMemoryTypeHost;
   else cudaGetLastError();
-  int tile = desc->tile_config > 0 ? desc->tile_config - 1 : (host_b ? agb::kTileHost : agb::kTileDevice);
+  int tile = desc->tile_config > 0 ? desc->tile_config - 1 : (host_b ? agb::kTileHost : agb::kTileDeviceRegAcc);
   if (tile < 0 || tile >= agb::kNumTileConfigs) return agb_fail(AG_E_INVALID, "tile_config out of range");
   const agb::TileConfig tc = agb::tile_config_of(1, tile);
   const uint64_t atoms = (static_cast<uint64_t>(desc->k) + 127) / 128;

@@ -76,7 +76,8 @@ typedef struct ag_gemm_desc {
   float alpha;         /* nvfp4 only: product of the two tensor-level scales; 0 is read as 1 */
   int32_t tile_config; /* 0 = choose from where b lives; 1.. = force tile configuration (tuning / tests):
                           1 = 128 columns per item (device-resident b), 2 = 32 columns x 512 B of K per stage
-                          (host-resident b), 3 = 32 x 1024 B, 4 = 64 x 256 B */
+                          (host-resident b), 3 = 32 x 1024 B, 4 = 64 x 256 B, 5 = 128 columns with the scaled accumulators in registers
+                          (fp8 / int8 with device-resident b) */
   int32_t no_split;    /* device-resident b only: 1 = keep one item per (segment, n-tile) instead of splitting long segments into
                           accumulator-sized row chunks across CTAs (tests / tuning); ignored for host-resident b */
 } ag_gemm_desc_t;
