@@ -42,6 +42,7 @@ class DispatchState:
     experts: torch.Tensor        # int32 [experts_per_rank + 1] = 0 .. experts_per_rank-1, -1
     tokens: int
     top_k: int
+    src_token: Optional[torch.Tensor] = None   # one rank only: rows were not gathered yet; received row i is token src_token[i]
 
 
 class EPDispatcher:
@@ -131,16 +132,17 @@ class EPDispatcher:
         src_token = torch.div(order, top_k, rounding_mode="floor")
         outs = []
         for t in (rows,) + tuple(extras):
-            send = moe_ops.move_rows(t.contiguous(), src_token.numel(), src_rows=src_token)
             if self.world == 1:
-                outs.append(send)      # nothing to exchange: the gathered rows are the received rows
+                outs.append(t)         # nothing to exchange: the gather is folded into the scatter to the padded layout
                 continue
+            send = moe_ops.move_rows(t.contiguous(), src_token.numel(), src_rows=src_token)
             as_bytes = send.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else send
             recv = torch.empty((total_recv,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=as_bytes.device)
             self._all_to_all(recv, as_bytes, recv_splits, send_splits)
             outs.append(recv.view(t.dtype) if t.dtype == torch.float8_e4m3fn else recv)
         dest_rows, per_expert, padded_rows, offsets, experts = self.layout(recv_counts, total_recv)
-        state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k)
+        state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k,
+                              src_token if self.world == 1 else None)
         return state, outs[0], tuple(outs[1:])
 
     def _side_stream(self, device):
@@ -166,7 +168,7 @@ class EPDispatcher:
 
 def to_contiguous_layout(recv: torch.Tensor, state: DispatchState) -> torch.Tensor:
     """Scatter received rows into the zero-padded contiguous layout the grouped GEMM consumes."""
-    return moe_ops.move_rows(recv.contiguous(), state.padded_rows, dst_rows=state.dest_rows, zero=True)
+    return moe_ops.move_rows(recv.contiguous(), state.padded_rows, src_rows=state.src_token, dst_rows=state.dest_rows, zero=True)
 
 
 # --------------------------------------------------------------------------------------------- pinned weights

@@ -102,6 +102,7 @@ def test_layout_arithmetic_single_rank():
     assert state.rows_per_expert.tolist() == [2, 1, 0, 3] and state.padded_rows == 128 + 4 * 128
     # every local expert has a segment; the one without rows is empty (start == end)
     assert state.offsets.tolist() == [0, 128, 128, 256, 256, 256, 256, 384] and state.experts.tolist() == [0, 1, 2, 3, -1]
+    assert recv is x and state.src_token.tolist() == [0, 2, 1, 0, 1, 2]   # one rank: rows are gathered by the scatter itself
     a = to_contiguous_layout(recv, state)
     assert a[:2, 0].tolist() == [1.0, 3.0] and a[128, 0] == 2.0 and a[256:259, 0].tolist() == [1.0, 2.0, 3.0]
     assert a.abs().sum() == 12.0

@@ -1,0 +1,70 @@
+"""Seeded random sweep: dtype x layout x weight residency x tile configuration x ragged shapes, each case checked
+against the CPU oracle with the tolerances of tests/test_gpu_parity.py."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import asymgemm_b200 as ag
+from tests import helpers as H
+from tests.test_gpu_parity import _check, _run_contiguous, _run_masked
+
+pytestmark = pytest.mark.gpu
+
+K_STEP = {"bf16": 8, "fp8": 16, "int8": 128, "fp4": 32}
+TILES = {"bf16": [0, 1, 2, 3, 4], "fp8": [0, 1, 2, 3, 4, 5], "int8": [0, 1, 2, 3, 4, 5], "fp4": [0, 1, 4]}
+
+
+def _random_case(rng: random.Random):
+    kind = rng.choice(["bf16", "fp8", "int8", "fp4"])
+    masked = rng.random() < 0.4
+    groups = rng.randint(1, 6)
+    n = 8 * rng.randint(1, 60)
+    k = K_STEP[kind] * rng.randint(1, 1024 // K_STEP[kind])
+    if kind == "fp8":
+        k = max(k, 16)
+    tile = rng.choice(TILES[kind])
+    host = rng.random() < 0.6
+
+    def rows():
+        r = rng.random()
+        if r < 0.15:
+            return 0
+        if r < 0.25:
+            return rng.randint(1800, 2600)      # longer than one accumulator chunk in every configuration
+        return rng.randint(1, 400)
+    counts = [rows() for _ in range(groups)]
+    if sum(counts) == 0:
+        counts[0] = 5
+    return kind, masked, counts, n, k, tile, host
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_random_case(seed):
+    rng = random.Random(1000 + seed)
+    kind, masked, counts, n, k, tile, host = _random_case(rng)
+    ag.set_tile_config(tile)
+    try:
+        if masked:
+            m_max = max(counts)
+            m_max = -(-m_max // 128) * 128 if kind == "fp4" or rng.random() < 0.5 else m_max + rng.randint(0, 40)
+            c = H.make_masked_case(kind, counts, m_max, n, k, seed=seed, b_on_host=host)
+            d = torch.full((len(counts), m_max, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            _run_masked(c, d)
+            rows_total = len(counts) * m_max
+        else:
+            c = H.make_contiguous_case(kind, counts, n, k, seed=seed, b_on_host=host)
+            d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            _run_contiguous(c, d)
+            rows_total = c["m_total"]
+        ag.check_status()
+    finally:
+        ag.set_tile_config(0)
+    d_np = d.float().cpu().numpy().reshape(rows_total, n)
+    info = f"kind={kind} masked={masked} counts={counts} n={n} k={k} tile={tile} host={host}"
+    try:
+        _check(kind, d_np, c["ref"], c["segments"])
+    except AssertionError as e:
+        raise AssertionError(f"{e} [{info}]")
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], rows_total)]).all(), info
