@@ -78,6 +78,9 @@ EXPORTS = [
     "ag_silu_mul_quant_fp8",
     "ag_move_rows",
     "ag_combine_topk",
+    "ag_quant_rows_int8",
+    "ag_silu_mul_quant_int8",
+    "ag_combine_topk_f32",
     "ag_last_error",
     "ag_version",
 ]
@@ -127,6 +130,12 @@ def load() -> ctypes.CDLL:
     lib.ag_combine_topk.restype = c_int32
     lib.ag_measure_host_stream.argtypes = [c_uint64, c_int64, c_int32, c_int32, c_int32, c_int32, POINTER(c_double)]
     lib.ag_measure_host_stream.restype = c_int32
+    lib.ag_quant_rows_int8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
+    lib.ag_quant_rows_int8.restype = c_int32
+    lib.ag_silu_mul_quant_int8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
+    lib.ag_silu_mul_quant_int8.restype = c_int32
+    lib.ag_combine_topk_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p]
+    lib.ag_combine_topk_f32.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]

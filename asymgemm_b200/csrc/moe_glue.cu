@@ -127,6 +127,55 @@ __global__ void __launch_bounds__(256) combine_topk_kernel(const __nv_bfloat16* 
   }
 }
 
+// One warp per row: scale = max(amax(row) * (1/127), 1e-12), q = clamp(rint(x * (1 / scale)), -127, 127); the scale is written
+// to every one of the row's `kb` K-block slots, which is how the reference feeds its per-token INT8 scales to the grouped
+// GEMM (quantize_per_token_int8_gpu + expand, asym_gemm/unified_moe/runtime.py:573-583,1558-1562).
+// MODE 0: x is bf16 [rows, cols]. MODE 1: x is fp32 [rows, 2*cols] = gate | up and the value quantised is
+// bf16(silu(gate) * up) (runtime.py:1570,1620-1627).
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_rows_int8_kernel(const void* __restrict__ xin, int8_t* __restrict__ q, float* __restrict__ sf,
+                                                              long long rows, int cols, int kb) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  auto value = [&](int c) -> float {
+    if (MODE == 0) return __bfloat162float(static_cast<const __nv_bfloat16*>(xin)[row * cols + c]);
+    const float* g = static_cast<const float*>(xin) + row * 2 * cols;
+    const float gate = g[c];
+    return __bfloat162float(__float2bfloat16_rn((gate / (1.0f + expf(-gate))) * g[cols + c]));
+  };
+  float amax = 0.f;
+  for (int c = lane; c < cols; c += 32) amax = fmaxf(amax, fabsf(value(c)));
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax * (1.0f / 127.0f), 1e-12f);
+  const float inv = 1.0f / scale;
+  for (int c = lane; c < cols; c += 32) {
+    const float r = fminf(fmaxf(rintf(value(c) * inv), -127.f), 127.f);
+    q[row * cols + c] = static_cast<int8_t>(r);
+  }
+  for (int i = lane; i < kb; i += 32) sf[row * kb + i] = scale;
+}
+
+// fp32-row variant of combine_topk_kernel (the reference keeps the INT8 layer's down-projection output in fp32).
+__global__ void __launch_bounds__(256) combine_topk_f32_kernel(const float* __restrict__ rows, const long long* __restrict__ pos,
+                                                               const float* __restrict__ w, __nv_bfloat16* __restrict__ y, int top_k, int cols) {
+  const long long t = blockIdx.x;
+  for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const long long r = pos[t * top_k + j];
+      const float wt = w[t * top_k + j];
+      const float4 v = *reinterpret_cast<const float4*>(rows + r * cols + c);
+      acc[0] = fmaf(wt, v.x, acc[0]); acc[1] = fmaf(wt, v.y, acc[1]); acc[2] = fmaf(wt, v.z, acc[2]); acc[3] = fmaf(wt, v.w, acc[3]);
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(y + t * cols + c) = o;
+  }
+}
+
 }  // namespace agb
 
 namespace {
@@ -177,6 +226,33 @@ int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weig
   agb::combine_topk_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(rows_bf16), reinterpret_cast<const long long*>(pos), weights, static_cast<__nv_bfloat16*>(y_bf16),
       top_k, static_cast<int>(cols));
+  return launch_check();
+}
+
+int ag_quant_rows_int8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream) {
+  if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0) return agb_fail(AG_E_INVALID, "bad arguments");
+  if (rows == 0) return AG_OK;
+  agb::quant_rows_int8_kernel<0><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      x_bf16, static_cast<int8_t*>(q), sf, rows, static_cast<int>(cols), static_cast<int>((cols + 127) / 128));
+  return launch_check();
+}
+
+int ag_silu_mul_quant_int8(const void* gate_up_f32, void* q, float* sf, int64_t rows, int64_t inter, void* stream) {
+  if (!gate_up_f32 || !q || !sf || rows < 0 || inter <= 0) return agb_fail(AG_E_INVALID, "bad arguments");
+  if (rows == 0) return AG_OK;
+  agb::quant_rows_int8_kernel<1><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      gate_up_f32, static_cast<int8_t*>(q), sf, rows, static_cast<int>(inter), static_cast<int>((inter + 127) / 128));
+  return launch_check();
+}
+
+int ag_combine_topk_f32(const void* rows_f32, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
+                        int64_t cols, void* stream) {
+  if (!rows_f32 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 4 != 0)
+    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
+  if (tokens == 0) return AG_OK;
+  agb::combine_topk_f32_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(rows_f32), reinterpret_cast<const long long*>(pos), weights, static_cast<__nv_bfloat16*>(y_bf16), top_k,
+      static_cast<int>(cols));
   return launch_check();
 }
 

@@ -42,6 +42,31 @@ def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int) -> Tuple[torch.Tensor,
     return q, sf
 
 
+def quant_rows_int8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, cols] -> (int8 [rows, cols], fp32 [rows, ceil(cols/128)] holding the row's scale in every K-block slot)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
+        raise RuntimeError("quant_rows_int8 wants a contiguous 2-D bf16 CUDA tensor")
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    sf = torch.empty((rows, (cols + 127) // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().ag_quant_rows_int8(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, cols, _stream(x)))
+    return q, sf
+
+
+def silu_mul_quant_int8(gate_up: torch.Tensor, inter: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 [rows, 2*inter] -> bf16(silu(gate) * up) quantised per row to (int8 [rows, inter], fp32 [rows, ceil(inter/128)])."""
+    if not (gate_up.is_cuda and gate_up.dtype == torch.float32 and gate_up.dim() == 2 and gate_up.is_contiguous()
+            and gate_up.shape[1] == 2 * inter):
+        raise RuntimeError("silu_mul_quant_int8 wants a contiguous fp32 CUDA tensor [rows, 2*inter]")
+    rows = gate_up.shape[0]
+    q = torch.empty((rows, inter), dtype=torch.int8, device=gate_up.device)
+    sf = torch.empty((rows, (inter + 127) // 128), dtype=torch.float32, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        _lib.check(_lib.load().ag_silu_mul_quant_int8(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, inter, _stream(gate_up)))
+    return q, sf
+
+
 def _row_bytes(t: torch.Tensor) -> int:
     n = t.element_size()
     for s in t.shape[1:]:
@@ -83,6 +108,13 @@ def combine_topk(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, t
         with torch.cuda.device(rows.device):
             _lib.check(_lib.load().ag_combine_topk(rows.data_ptr(), pos.data_ptr(), w.data_ptr(), y.data_ptr(), tokens, top_k, cols,
                                                    _stream(rows)))
+        return y
+    if rows.is_cuda and rows.dtype == torch.float32 and cols % 4 == 0 and rows.is_contiguous():
+        y = torch.empty((tokens, cols), dtype=torch.bfloat16, device=rows.device)
+        w = weights.to(torch.float32).contiguous()
+        with torch.cuda.device(rows.device):
+            _lib.check(_lib.load().ag_combine_topk_f32(rows.data_ptr(), pos.data_ptr(), w.data_ptr(), y.data_ptr(), tokens, top_k, cols,
+                                                       _stream(rows)))
         return y
     picked = rows.index_select(0, pos).view(tokens, top_k, cols).float()
     return (picked * weights.unsqueeze(-1).float()).sum(dim=1).to(rows.dtype)

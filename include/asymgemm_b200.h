@@ -171,6 +171,16 @@ int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int6
 int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                     int64_t cols, void* stream);
 
+/* INT8 counterparts for the reference's INT8 MoE layer (asym_gemm/unified_moe/runtime.py:573-583,1558-1627): one scale per
+ * row = max(amax * (1/127), 1e-12), written to each of the row's ceil(cols/128) K-block slots so that the tensors can be
+ * passed to ag_m_grouped_int8_gemm_nt as they are; q = clamp(rint(x / scale), -127, 127).
+ * ag_silu_mul_quant_int8 takes the fp32 gate | up output [rows, 2*inter] and quantises bf16(silu(gate) * up). */
+int ag_quant_rows_int8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream);
+int ag_silu_mul_quant_int8(const void* gate_up_f32, void* q, float* sf, int64_t rows, int64_t inter, void* stream);
+/* ag_combine_topk for fp32 rows (cols % 4 == 0); the result is rounded once to bf16. */
+int ag_combine_topk_f32(const void* rows_f32, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
+                        int64_t cols, void* stream);
+
 /* Failure-detection self test: launches a one-CTA kernel whose only barrier wait can never be satisfied. After
  * `timeout_ms` (1..2000) the wait gives up, the kernel stores (0 << 8) | 9 ("wait-limit self test expired") in *status
  * and returns; the context stays usable. Replaces nothing in the reference, whose device waits are unbounded
