@@ -48,14 +48,32 @@ class DispatchState:
 class EPDispatcher:
     """Token routing for expert parallelism over one process group (expert e lives on rank e // experts_per_rank)."""
 
-    def __init__(self, num_experts: int, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, num_experts: int, group: Optional[dist.ProcessGroup] = None,
+                 expert_ranges: Optional[List[Tuple[int, int]]] = None):
+        """`expert_ranges[r] = (lo, hi)`: the contiguous experts rank r owns (default: equal shares, expert e on rank
+        e // (num_experts / world)); unequal shares let faster host links carry more experts (proportional_expert_ranges)."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        if num_experts % self.world != 0:
-            raise RuntimeError(f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
+        if expert_ranges is None:
+            if num_experts % self.world != 0:
+                raise RuntimeError(f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
+            per = num_experts // self.world
+            expert_ranges = [(r * per, (r + 1) * per) for r in range(self.world)]
+        if len(expert_ranges) != self.world or expert_ranges[0][0] != 0 or expert_ranges[-1][1] != num_experts or \
+                any(expert_ranges[i][1] != expert_ranges[i + 1][0] for i in range(self.world - 1)) or \
+                any(hi <= lo for lo, hi in expert_ranges):
+            raise RuntimeError(f"expert_ranges must tile [0, {num_experts}) with one non-empty range per rank: {expert_ranges}")
         self.num_experts = num_experts
-        self.experts_per_rank = num_experts // self.world
+        self.expert_ranges = [(int(lo), int(hi)) for lo, hi in expert_ranges]
+        self.experts_per_rank = self.expert_ranges[self.rank][1] - self.expert_ranges[self.rank][0]   # this rank's experts
+        self.max_experts_per_rank = max(hi - lo for lo, hi in self.expert_ranges)
+        # slot (r, j) of the [world, max_experts_per_rank] count matrix holds expert lo[r] + j (or nothing when j >= n_r)
+        idx = torch.full((self.world, self.max_experts_per_rank), num_experts, dtype=torch.int64)
+        for r, (lo, hi) in enumerate(self.expert_ranges):
+            idx[r, : hi - lo] = torch.arange(lo, hi)
+        self._slot_expert = idx
+        self._slot_cache: dict = {}
 
     # ------------------------------------------------------------------ collectives (identity at world size 1)
     def _all_to_all(self, out: torch.Tensor, inp: torch.Tensor, out_splits=None, in_splits=None) -> None:
@@ -67,15 +85,21 @@ class EPDispatcher:
     def plan(self, topk_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Sort the (token, slot) pairs by expert and exchange per-expert counts.
 
-        Returns (order [T*k], send_counts int32 [world, experts_per_rank], recv_counts int32 [world, experts_per_rank]),
+        Returns (order [T*k], send_counts int32 [world, max_experts_per_rank], recv_counts int32 [world, experts_per_rank]),
         recv_counts[s, j] = rows rank s sends to this rank's local expert j.
         """
         flat = topk_ids.reshape(-1)
         order = torch.argsort(flat, stable=True)
-        send_counts = torch.bincount(flat, minlength=self.num_experts).to(torch.int32).view(self.world, self.experts_per_rank)
+        per_expert = torch.bincount(flat, minlength=self.num_experts)
+        slot = self._slot_cache.get(flat.device)
+        if slot is None:
+            slot = self._slot_expert.to(flat.device)
+            self._slot_cache[flat.device] = slot
+        padded = torch.cat([per_expert, per_expert.new_zeros(1)])          # index num_experts = "no expert in this slot"
+        send_counts = padded[slot].to(torch.int32).contiguous()
         recv_counts = torch.empty_like(send_counts)
-        self._all_to_all(recv_counts, send_counts.contiguous())
-        return order, send_counts, recv_counts
+        self._all_to_all(recv_counts, send_counts)
+        return order, send_counts, recv_counts[:, : self.experts_per_rank].contiguous()
 
     def layout(self, recv_counts: torch.Tensor, total_recv: int):
         """Contiguous layout of the received rows: grouped by local expert, each expert padded to 128 rows.
@@ -122,11 +146,11 @@ class EPDispatcher:
                 side.wait_stream(torch.cuda.current_stream(topk_ids.device))
                 with torch.cuda.stream(side):
                     order, send_counts, recv_counts = self.plan(topk_ids)
-                    counts_host = torch.stack([send_counts, recv_counts]).sum(dim=2).cpu()   # waits for the side stream only
+                    counts_host = torch.stack([send_counts.sum(dim=1), recv_counts.sum(dim=1)]).cpu()   # waits for the side stream only
                 torch.cuda.current_stream(topk_ids.device).wait_stream(side)
             else:
                 order, send_counts, recv_counts = self.plan(topk_ids)
-                counts_host = torch.stack([send_counts, recv_counts]).sum(dim=2).cpu()
+                counts_host = torch.stack([send_counts.sum(dim=1), recv_counts.sum(dim=1)]).cpu()
             send_splits, recv_splits = counts_host[0].tolist(), counts_host[1].tolist()
             total_recv = int(sum(recv_splits))
         src_token = torch.div(order, top_k, rounding_mode="floor")
@@ -210,6 +234,36 @@ def pinned_empty(shape, dtype: torch.dtype, numa_node: Optional[int] = None, hug
     return torch.empty(*shape, dtype=dtype).pin_memory()
 
 
+def proportional_expert_ranges(rates: List[float], num_experts: int, tolerance: float = 0.1) -> List[Tuple[int, int]]:
+    """Contiguous expert ranges [lo, hi) per rank, sized in proportion to each rank's measured host-link rate.
+
+    Every rank streams its own experts' weights over its own host link and a step ends with the slowest rank, so when the
+    links of one machine are not equally fast (on an 8-GPU host four links were measured at 23 GB/s and four at 35 GB/s
+    with all eight busy) equal shards leave the fast links idle. Rates within `tolerance` of each other give the even
+    split. Every rank keeps at least one expert.
+    """
+    world = len(rates)
+    if world <= 0 or num_experts < world:
+        raise RuntimeError("need at least one expert per rank")
+    even = [(r * num_experts // world, (r + 1) * num_experts // world) for r in range(world)]
+    if min(rates) <= 0 or max(rates) / min(rates) <= 1.0 + tolerance:
+        return even
+    total = float(sum(rates))
+    counts = [max(1, int(num_experts * r / total)) for r in rates]
+    # hand out what rounding left over (or take back any excess) where it changes the finishing time least
+    while sum(counts) < num_experts:
+        i = min(range(world), key=lambda j: (counts[j] + 1) / rates[j])
+        counts[i] += 1
+    while sum(counts) > num_experts:
+        i = max((j for j in range(world) if counts[j] > 1), key=lambda j: counts[j] / rates[j])
+        counts[i] -= 1
+    out, lo = [], 0
+    for c in counts:
+        out.append((lo, lo + c))
+        lo += c
+    return out
+
+
 def gpu_numa_node(device_index: int) -> int:
     """NUMA node of the GPU's PCIe root, or -1 when the platform does not say (single-node VMs)."""
     try:
@@ -231,8 +285,9 @@ class ExpertParallelMoE:
     w2:  (fp8 [E_local, hidden, inter] pinned,   fp32 block scales [E_local, hidden/128, inter/128])
     """
 
-    def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None):
-        self.dispatcher = EPDispatcher(num_experts, group)
+    def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
+                 expert_ranges: Optional[List[Tuple[int, int]]] = None):
+        self.dispatcher = EPDispatcher(num_experts, group, expert_ranges)
         self.hidden, self.inter = hidden, inter
         self.w13, self.w2 = w13, w2
         epr = self.dispatcher.experts_per_rank

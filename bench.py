@@ -7,8 +7,10 @@ host-link peak.
 One step = one grouped GEMM over one batch of synthetic, seeded input (the shapes of BASELINE.json's configs; no
 dataset or checkpoint is involved). The default workload is the DeepSeek-V3-shaped FP8 gate+up GEMM: 256 experts,
 K=7168, N=4096, 16384 tokens x top-8 with Zipf(0.8) expert popularity, B (7.5 GB) in pinned host memory.
-With N > 1 ranks the experts (and the rows routed to them) are split evenly across ranks; every rank streams its own
-shard over its own host link and there is no collective on the data path, so total work is fixed ("strong").
+With N > 1 ranks the experts (and the rows routed to them) are split across ranks in contiguous ranges -- evenly when the
+ranks' host links measure within 10 % of each other with all of them streaming at once, otherwise in proportion to those
+rates (--even-shards forces the even split); every rank streams its own shard over its own host link and there is no
+collective on the data path, so total work is fixed ("strong").
 
 Prints ONE JSON line on rank 0. `value` times the kernel with activations already in HBM; `e2e` times the public
 operator call with host buffers (pinned A in, D out) inside the timed region.
@@ -54,7 +56,7 @@ def rows_per_expert(cfg, seed=0):
     return torch.bincount(picks.flatten(), minlength=e).tolist()
 
 
-def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False):
+def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False, expert_range=None):
     """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
     from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
                                      per_token_cast_to_fp8, per_token_cast_to_int8)
@@ -62,7 +64,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     counts = rows_per_expert(cfg, seed)
     e_total = cfg["experts"]
     per = e_total // world
-    lo, hi = rank * per, (rank + 1) * per if rank < world - 1 else e_total
+    lo, hi = expert_range if expert_range is not None else (rank * per, (rank + 1) * per if rank < world - 1 else e_total)
     counts = counts[lo:hi]
     g = len(counts)
     offsets, experts, list_size, m_total, segs = build_contiguous_layout(counts, device=device)
@@ -114,13 +116,13 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
 
 
-def build_moe(cfg, rank, world, device, group, seed=0):
+def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None):
     """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
     GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing."""
     from asymgemm_b200 import ep
     from asymgemm_b200.utils import per_block_cast_to_fp8
     e_total, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
-    epr = e_total // world
+    epr = e_total // world if expert_ranges is None else expert_ranges[rank][1] - expert_ranges[rank][0]
     gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
     node = ep.gpu_numa_node(device.index)
     w13 = ep.pinned_empty((epr, 2 * i, h), torch.float8_e4m3fn, node)
@@ -135,7 +137,7 @@ def build_moe(cfg, rank, world, device, group, seed=0):
         w2[e].copy_(q, non_blocking=True)
         s2[e] = s
     torch.cuda.synchronize(device)
-    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group)
+    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges)
     t_local = cfg["tokens"] // world
     x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
     logits = torch.randn((t_local, e_total), device=device, generator=gen)
@@ -325,6 +327,8 @@ def main():
     ap.add_argument("--weights", default="host", choices=["host", "device"],
                     help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
     ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
+    ap.add_argument("--even-shards", action="store_true",
+                    help="N > 1: give every rank the same number of experts even when the host links are measured unequal")
     ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
     ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
     ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
@@ -363,15 +367,32 @@ def main():
 
     moe = cfg["kind"] == "moe"
     on_dev = args.weights == "device"
+    lib = _lib.load()
+    expert_range = None
+    ranges = None
+    if world > 1 and cfg["kind"] != "fp4" and not on_dev and not args.even_shards:
+        # Shard sizes follow each rank's host-link rate measured with every rank streaming at once (copy-only TMA kernel).
+        from asymgemm_b200.ep import proportional_expert_ranges
+        rate = _lib.c_double(0.0)
+        row_b = max(128, int(cfg["hidden"] if moe else cfg["k"] * ELEM_BYTES[cfg["kind"]]) // 128 * 128)
+        dist.barrier()
+        _lib.check(lib.ag_measure_host_stream(1 << 30, row_b, 64, 2, 0, 2, rate))
+        rates = torch.zeros(world, dtype=torch.float64, device=device)
+        rates[rank] = rate.value
+        dist.all_reduce(rates)
+        ranges = proportional_expert_ranges(rates.tolist(), cfg["experts"])
+        expert_range = ranges[rank]
+        config["experts_per_rank"] = [hi - lo for lo, hi in ranges]
+        config["sharding"] = ("contiguous expert ranges sized by each rank's host-link rate measured with all ranks streaming at once "
+                              f"({[round(x, 1) for x in rates.tolist()]} GB/s); equal when the rates are within 10 %")
     if moe:
-        w = build_moe(cfg, rank, world, device, None)
+        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges)
     elif cfg["kind"] == "fp4":
         w = build_masked_fp4(cfg, rank, world, device)
     else:
-        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages)
+        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages, expert_range=expert_range)
     if on_dev:
         config["workload"] = config["workload"].replace("B in pinned host DRAM", "B resident in HBM")
-    lib = _lib.load()
     ag.set_tile_config(args.tile)
     if args.sms:
         ag.set_num_sms(args.sms)

@@ -35,7 +35,7 @@ def _fake_experts(a, state, first_expert):
     return out
 
 
-def _roundtrip_worker(rank, world, port, q):
+def _roundtrip_worker(rank, world, port, q, ranges=None):
     try:
         _init(rank, world, port)
         torch.manual_seed(100 + rank)
@@ -45,7 +45,8 @@ def _roundtrip_worker(rank, world, port, q):
         if rank == 0:
             ids[:, 0] = 5            # a hot expert on the other rank; expert 2 may get no rows at all
         w = torch.rand(tokens, top_k)
-        disp = EPDispatcher(num_experts)
+        disp = EPDispatcher(num_experts, expert_ranges=ranges)
+        first_expert = disp.expert_ranges[rank][0]
         state, recv, (recv_tag,) = disp.dispatch(x, ids, (torch.arange(tokens, dtype=torch.float32).unsqueeze(1),))
         a = to_contiguous_layout(recv, state)
         assert a.shape[0] == state.padded_rows and state.padded_rows % 128 == 0
@@ -53,7 +54,8 @@ def _roundtrip_worker(rank, world, port, q):
         # every segment is 128-aligned and holds exactly its expert's rows, padding rows are zero
         off = state.offsets.tolist()
         assert all(o % 128 == 0 for o in off)
-        y = disp.combine(_fake_experts(a, state, rank * disp.experts_per_rank), state, w)
+        assert state.experts.tolist() == list(range(disp.experts_per_rank)) + [-1]
+        y = disp.combine(_fake_experts(a, state, first_expert), state, w)
         want = ((ids + 1).float() * w).sum(dim=1, keepdim=True) * x
         assert torch.allclose(y, want, rtol=1e-5, atol=1e-5), (y - want).abs().max()
         dist.barrier()
@@ -65,11 +67,11 @@ def _roundtrip_worker(rank, world, port, q):
             dist.destroy_process_group()
 
 
-def _run(worker, world=2, timeout=120):
+def _run(worker, world=2, timeout=120, extra=()):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, q) + tuple(extra)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
@@ -88,10 +90,21 @@ def test_dispatch_combine_roundtrip_two_ranks():
     assert results == {0: "ok", 1: "ok"}, results
 
 
+def test_dispatch_combine_roundtrip_unequal_expert_ranges():
+    """Rank 0 owns experts 0-2, rank 1 owns experts 3-7 (shares sized by link rate in production)."""
+    results = _run(_roundtrip_worker, extra=([(0, 3), (3, 8)],))
+    assert results == {0: "ok", 1: "ok"}, results
+
+
+def test_expert_ranges_are_validated():
+    with pytest.raises(RuntimeError):
+        EPDispatcher(4, expert_ranges=[(0, 3)])          # does not cover all experts
+    with pytest.raises(RuntimeError):
+        EPDispatcher(4, expert_ranges=[(1, 4)])
+
+
 def _single_rank_layout():
-    disp = EPDispatcher.__new__(EPDispatcher)
-    disp.group, disp.world, disp.rank, disp.num_experts, disp.experts_per_rank = None, 1, 0, 4, 4
-    return disp
+    return EPDispatcher(4)     # no process group: one rank owning all four experts
 
 
 def test_layout_arithmetic_single_rank():

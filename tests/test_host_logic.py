@@ -144,3 +144,18 @@ def test_scale_layout_helpers_keep_the_reference_shapes_and_strides():
         ag.transform_sf_into_required_layout(sfb, 200, 512, (1, 64, 64))
     ag.set_tc_util(80); ag.set_compile_mode(1)
     assert ag.get_tc_util() == 80 and ag.get_compile_mode() == 1
+
+
+def test_proportional_expert_ranges():
+    from asymgemm_b200.ep import proportional_expert_ranges as pr
+    assert pr([50.0, 51.0, 49.5, 50.2], 256) == [(0, 64), (64, 128), (128, 192), (192, 256)]      # within tolerance: even
+    r = pr([23.0] * 4 + [35.0] * 4, 256)
+    sizes = [hi - lo for lo, hi in r]
+    assert sum(sizes) == 256 and r[0][0] == 0 and r[-1][1] == 256 and all(r[i][1] == r[i + 1][0] for i in range(7))
+    assert all(25 <= n <= 26 for n in sizes[:4]) and all(38 <= n <= 39 for n in sizes[4:])
+    # finishing time (experts / rate) is balanced to within one expert
+    t = [n / rate for n, rate in zip(sizes, [23.0] * 4 + [35.0] * 4)]
+    assert max(t) - min(t) <= 1 / 23.0 + 1e-9
+    assert [hi - lo for lo, hi in pr([1.0, 100.0], 4)] == [1, 3]
+    with pytest.raises(RuntimeError):
+        pr([1.0, 1.0, 1.0], 2)
