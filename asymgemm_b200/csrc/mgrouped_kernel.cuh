@@ -12,15 +12,21 @@
 //     TMEM across the whole K loop (K outer, M inner inside a chunk). Segments longer than one chunk
 //     replay the column from a per-CTA scratch copy in device memory that the first pass writes with a
 //     TMA store of the very shared-memory stage the MMA consumes (no second trip over the host link);
-//   * no atomics, no partial sums in D: every output element is written once, from fp32.
+//   * no atomics, no partial sums in D: every output element is written once, from fp32;
+//   * when B is device-resident there is no link to spare, so long segments are split into accumulator-sized row
+//     chunks that become items of their own (fetch_item, split mode) and spread over all CTAs.
 //
 // Tile shape is chosen by where B lives. Streaming from the host, throughput drops once the rows being streamed at
 // the same time (CTAs x BN) spread over more than a few thousand 4 KB host pages (measured: 148 CTAs x 128 rows ->
-// 44.5 GB/s, 148 x 32 rows -> 51.4 GB/s of a 55.6 GB/s copy-engine peak), so host-resident B uses BN = 32 with
+// 44.5 GB/s, 148 x 32 rows -> 51.4 GB/s of a 55.6 GB/s copy-engine peak), so host-resident B uses BN = 64 or 32 with
 // KA = several 128-byte K atoms per stage; device-resident B uses BN = 128, KA = 1 for tensor-core efficiency.
 //
-// Warp roles (256 threads): warp 0 = B producer (+ scratch spill), warp 1 = A producer,
-// warp 2 = TMEM allocator + single-thread tcgen05.mma issuer, warp 3 idle, warps 4-7 = TMEM drain.
+// Four operand kinds share the body: BF16 and NVFP4 accumulate in TMEM in hardware (NVFP4 with its UE4M3 scale
+// factors copied into TMEM by tcgen05.cp); FP8 and INT8 produce one raw product per 128-wide K block that the drain warps
+// scale in fp32 (block scales are arbitrary fp32 numbers) and add to accumulators kept in TMEM, or in registers (REG_ACC).
+//
+// Warp roles: warp 0 = B producer (+ scratch spill), warp 1 = A producer, warp 2 = TMEM allocator + single-thread
+// tcgen05.mma issuer, warp 3 idle, warps 4-7 (and 8-11 for INT8 with REG_ACC) = TMEM drain.
 //
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
 // shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
