@@ -57,7 +57,7 @@ cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, con
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kernel<<<grid, num_threads_of<KIND, REG_ACC>(), L::dyn_bytes, stream>>>(ma, mb, ms, p);
+  kernel<<<grid, num_threads_of<KIND, BN, REG_ACC>(), L::dyn_bytes, stream>>>(ma, mb, ms, p);
   return cudaGetLastError();
 }
 

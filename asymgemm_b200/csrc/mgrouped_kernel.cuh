@@ -270,16 +270,19 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
 // registers instead of TMEM, all TMEM slots hold raw per-K-block products (a 512/BN-deep MMA pipeline) and the drain
 // does one tcgen05.ld + fma per block instead of ld + ld + st. Used when the weights are device-resident, where items are
 // one tile tall anyway and the drain, not the host link, sets the pace.
-// Drain warpgroups. INT8 with REG_ACC uses two (384 threads): warps 4-7 own the low half of the tile's columns, warps 8-11
-// the high half, so each thread keeps BN/2 accumulators and the per-column scaling is shared out (measured: 272 -> 383
-// TFLOP/s on the 16-expert INT8 case). FP8, whose block scale is one scalar per tile, is not drain-bound and keeps one.
-template <Kind KIND, bool REG_ACC>
-__host__ __device__ constexpr int drain_wgs_of() { return (REG_ACC && KIND == Kind::INT8) ? 2 : 1; }
-template <Kind KIND, bool REG_ACC>
-__host__ __device__ constexpr int num_threads_of() { return 128 + 128 * drain_wgs_of<KIND, REG_ACC>(); }
+// Drain warpgroups. The software-scaled kinds use two (384 threads) wherever a tile is at least 64 columns wide: warps
+// 4-7 own the low half of the tile's columns, warps 8-11 the high half, and the two groups drain a raw slot side by
+// side (INT8 with REG_ACC: 272 -> 383 TFLOP/s on the 16-expert case). The exception is FP8 with REG_ACC, whose block
+// scale is one scalar per tile: it is bound by operand traffic, not by the drain, and measured slightly faster with one.
+template <Kind KIND, int BN, bool REG_ACC>
+__host__ __device__ constexpr int drain_wgs_of() {
+  return (KIND != Kind::FP8 && KIND != Kind::INT8) ? 1 : (REG_ACC ? (KIND == Kind::INT8 ? 2 : 1) : (BN >= 64 ? 2 : 1));
+}
+template <Kind KIND, int BN, bool REG_ACC>
+__host__ __device__ constexpr int num_threads_of() { return 128 + 128 * drain_wgs_of<KIND, BN, REG_ACC>(); }
 
 template <Kind KIND, int BN, int KA, int SA, int SB, bool REG_ACC = false>
-__global__ void __launch_bounds__(num_threads_of<KIND, REG_ACC>(), 1)
+__global__ void __launch_bounds__(num_threads_of<KIND, BN, REG_ACC>(), 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
   using T = KindTraits<KIND>;
@@ -294,7 +297,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int CHUNK_TILES = T::sw_scale ? (REG_ACC ? 1 : NUM_SLOTS - 2) : NUM_SLOTS;
   constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
   constexpr uint32_t IDESC = T::block_scaled ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);
-  constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, REG_ACC>();   // one arrival per drain warp
+  constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, BN, REG_ACC>();   // one arrival per drain warp
   constexpr uint32_t SF_COL0 = NUM_SLOTS * BN;   // first TMEM column of the scale-factor area
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
 
@@ -555,7 +558,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mc = min(CHUNK_TILES, mtiles - m0);
         if constexpr (T::sw_scale && REG_ACC) {
           // one 128-row tile per chunk; its scaled accumulators stay in registers across the whole K loop
-          constexpr int COLS = BN / drain_wgs_of<KIND, REG_ACC>();   // columns owned by this drain warpgroup
+          constexpr int COLS = BN / drain_wgs_of<KIND, BN, REG_ACC>();   // columns owned by this drain warpgroup
           const int col_base = ((warp - 4) >> 2) * COLS;
           const long long grow = static_cast<long long>(it.row0) + m0 * BM + row_in_tile;
           const bool valid = grow < row_end;
@@ -624,6 +627,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
           }
         } else if constexpr (T::sw_scale) {
+          constexpr int COLS = BN / drain_wgs_of<KIND, BN, REG_ACC>();   // columns owned by this drain warpgroup
+          const int col_base = ((warp - 4) >> 2) * COLS;
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             // column scales of this K block
             float sb_scalar = 0.f;
@@ -634,11 +639,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
               const bool valid = grow < row_end;
               const float sa = valid ? __ldg(p.sfa + grow * p.sf_k + kb) : 0.f;
-              float* sfb_buf = sfb_smem + q * BN;  // private to this warp: no cross-warp barrier on any path
+              float* sfb_buf = sfb_smem + (warp - 4) * COLS;  // private to this warp: no cross-warp barrier on any path
               if constexpr (KIND == Kind::INT8) {
 #pragma unroll
-                for (int j = 0; j < BN / 32; ++j) {
-                  const int col = n0 + j * 32 + lane;
+                for (int j = 0; j < COLS / 32; ++j) {
+                  const int col = n0 + col_base + j * 32 + lane;
                   sfb_buf[j * 32 + lane] =
                       col < p.n ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + col) * p.sf_k + kb) : 0.f;
                 }
@@ -649,21 +654,21 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) break;
               tc_fence_after_sync();
-              const uint32_t raw_addr = lane_addr + (CHUNK_TILES + rs) * BN;
-              const uint32_t acc_addr = lane_addr + mt * BN;
+              const uint32_t raw_addr = lane_addr + (CHUNK_TILES + rs) * BN + col_base;
+              const uint32_t acc_addr = lane_addr + mt * BN + col_base;
               const bool last = kb == kb_count - 1;
 #pragma unroll 1
-              for (int cc = 0; cc < BN / 32; ++cc) {
+              for (int cc = 0; cc < COLS / 32; ++cc) {
                 uint32_t r[32], a[32];
                 tmem_ld_32x32b_x32(raw_addr + cc * 32, r);
                 if (kb > 0) tmem_ld_32x32b_x32(acc_addr + cc * 32, a);
                 tmem_wait_ld();
                 if constexpr (KIND == Kind::INT8) {
                   if (p.raw_dump != nullptr && valid) {
-                    int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + cc * 32;
+                    int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + cc * 32;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                      if (n0 + cc * 32 + j < p.n) dst[j] = static_cast<int>(r[j]);
+                      if (n0 + col_base + cc * 32 + j < p.n) dst[j] = static_cast<int>(r[j]);
                   }
                 }
 #pragma unroll
@@ -680,7 +685,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   a[j] = __float_as_uint(fmaf(prod, scale, prev));
                 }
                 if (last) {
-                  if (valid) store_row32(p, grow, n0 + cc * 32, a);
+                  if (valid) store_row32(p, grow, n0 + col_base + cc * 32, a);
                 } else {
                   tmem_st_32x32b_x32(acc_addr + cc * 32, a);
                 }
