@@ -6,7 +6,7 @@ checkout is not needed to run the tests. What is imported from bytedance-iaas/As
   * asym_gemm/utils/math.py          -- the quantisers that define the FP8 / INT8 / NVFP4 formats
   * tests/test_fp4_asym_gemm.py      -- _quantize_nvfp4_e4m3, _manual_dequant_reference (NVFP4 dequantised reference)
   * tests/test_sm90_int8.py          -- ref_2d / dequant (INT8 float reference)
-  * tests/generators.py              -- build_offsets_experts_from_m_indices (offsets / experts tables)
+  * tests/m_grouped/test_sm100_bf16_fp8_fp4_m_grouped.py -- _fp4_masked_reference (masked NVFP4 reference)
   * oracle/_ref (csrc/cpu/cpu_gemm)  -- exact int32 block sums through the reference's cg_gemm
 The compiled extension `asym_gemm._C` cannot be built here; a stub package stands in for it so that the pure-Python
 helpers import. The reference's GPU kernels themselves are never run.
@@ -60,6 +60,11 @@ def _install_reference(ref: Path):
     sys.modules.update({"asym_gemm": pkg, "asym_gemm.utils": utils, "asym_gemm.testing": testing})
     fp4 = _load(ref / "tests" / "test_fp4_asym_gemm.py", "ref_test_fp4")
     int8 = _load(ref / "tests" / "test_sm90_int8.py", "ref_test_int8")
+    # tests/m_grouped/... imports its NVFP4 helpers from a module name that does not exist in the repository
+    # (`test_nvfp4`); they live in tests/test_fp4_asym_gemm.py, so that module stands in under the missing name.
+    sys.modules["test_nvfp4"] = fp4
+    global MG
+    MG = _load(ref / "tests" / "m_grouped" / "test_sm100_bf16_fp8_fp4_m_grouped.py", "ref_test_m_grouped")
     return math_mod, numeric, fp4, int8
 
 
@@ -175,6 +180,22 @@ def main():
     refm = torch.einsum("gmk,gnk->gmn", a_deq, b_deq)
     np.savez_compressed(HERE / "fp8_masked.npz", a=bits(aq), sfa=sfa.numpy(), b=bits(bq), sfb=sfb.numpy(), masked_m=masked_m,
                         ref_f32=refm.numpy(), xm=xm.numpy().astype(np.float16))
+    # ---- masked layout, the other dtypes, on the same activations xm and weights w
+    a16m, b16m = xm.to(torch.bfloat16), w.to(torch.bfloat16)
+    ref16m = torch.einsum("gmk,gnk->gmn", a16m.float(), b16m.float())          # tests/m_grouped/...: _bf16_masked_case
+    np.savez_compressed(HERE / "bf16_masked.npz", a=bits(a16m), b=bits(b16m), masked_m=masked_m, ref_f32=ref16m.numpy(),
+                        ref_bf16=bits(ref16m.to(torch.bfloat16)))
+    aq, sfa = zip(*[M.per_token_cast_to_int8(xm[i]) for i in range(g)])
+    aq, sfa = torch.stack(aq), torch.stack(sfa)
+    bq, sfb = zip(*[M.per_channel_cast_to_int8(w[i]) for i in range(g)])
+    bq, sfb = torch.stack(bq), torch.stack(sfb)
+    ref8m = torch.stack([int8.ref_2d(aq[i], sfa[i], bq[i], sfb[i], k) for i in range(g)])   # tests/test_sm90_int8.py:51-54
+    np.savez_compressed(HERE / "int8_masked.npz", a=aq.numpy(), sfa=sfa.numpy(), b=bq.numpy(), sfb=sfb.numpy(), masked_m=masked_m,
+                        ref_f32=ref8m.numpy())
+    a_ps = [fp4._quantize_a_nvfp4_e4m3(xm[i].numpy(), 16) for i in range(g)]
+    a_p4, a_s4 = np.stack([p for p, _ in a_ps]), np.stack([s_ for _, s_ in a_ps])
+    ref4m = MG._fp4_masked_reference(a_p4, a_s4, b_p, b_s, torch.from_numpy(masked_m), 16)
+    np.savez_compressed(HERE / "fp4_masked.npz", a=a_p4, sfa=a_s4, b=b_p, sfb=b_s, masked_m=masked_m, ref_f32=ref4m.numpy())
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)
 
