@@ -95,13 +95,17 @@ def check_status(device: Union[torch.device, int, None] = None, reset: bool = Tr
 
 
 def _scratch(kind: int, n: int, k: int, device: torch.device) -> Optional[torch.Tensor]:
+    """Replay scratch for the launch about to be made: one buffer per (device, stream), because launches on different
+    streams may overlap on the GPU and each CTA keeps its current weight column there."""
     if not _state["use_scratch"]:
         return None
     lib = _lib.load()
     need = int(lib.ag_scratch_bytes(kind, n, k, 0))
-    key = device.index
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     t = _scratch_cache.get(key)
     if t is None or t.numel() < need + 1024:
+        if len(_scratch_cache) >= 8:
+            _scratch_cache.clear()
         t = torch.empty(need + 1024, dtype=torch.uint8, device=device)
         _scratch_cache[key] = t
     off = (-t.data_ptr()) % 1024

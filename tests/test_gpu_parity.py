@@ -313,3 +313,18 @@ def test_device_resident_split_matches_whole_segments(kind):
     torch.cuda.synchronize()
     assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
     _check(kind, d1.float().cpu().numpy(), c["ref"], c["segments"])
+
+
+def test_two_streams_do_not_share_replay_scratch():
+    """Two long-segment GEMMs issued back to back on different streams may overlap; each must get its own scratch."""
+    cases = [H.make_contiguous_case("fp8", [2600, 1900], 256, 1024, seed=51 + i) for i in range(2)]
+    outs = [torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda") for c in cases]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for _ in range(3):
+        for c, d, st in zip(cases, outs, streams):
+            with torch.cuda.stream(st):
+                _run_contiguous(c, d)
+    torch.cuda.synchronize()
+    for c, d in zip(cases, outs):
+        _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
