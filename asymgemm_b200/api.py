@@ -139,7 +139,7 @@ def _device_copy(t: torch.Tensor, device: torch.device) -> torch.Tensor:
     hit = _cache_get(_dev_copy_cache, t, device)
     if hit is not None:
         return hit
-    dev = t.to(device, non_blocking=t.is_pinned())
+    dev = t.to(device)   # blocking, once per weight tensor: the cached copy may be used from any stream afterwards
     _cache_put(_dev_copy_cache, t, device, dev)
     return dev
 
@@ -362,6 +362,7 @@ def _fp4_blocked(sf: torch.Tensor, groups: int, rows: int, k16: int, device: tor
         _lib.check(lib.ag_fp4_sf_to_blocked(sf.data_ptr(), out.data_ptr(), groups, rows, k16,
                                             torch.cuda.current_stream(device).cuda_stream))
     if cache:
+        torch.cuda.current_stream(device).synchronize()   # once per weight tensor: safe to reuse from any stream
         _cache_put(_blocked_cache, sf, device, out)
     return out
 
