@@ -16,6 +16,7 @@ from .api import (  # noqa: F401
     m_grouped_fp8_asym_gemm_nt_masked,
     m_grouped_int8_asym_gemm_nt_contiguous,
     m_grouped_int8_asym_gemm_nt_masked,
+    set_fp8_scale_mode,
     set_num_sms,
     set_split_segments,
     set_tile_config,

@@ -22,7 +22,7 @@ LAYOUT_MASKED = 1
 D_BF16 = 0
 D_FP32 = 1
 
-KIND_BF16, KIND_FP8, KIND_INT8, KIND_NVFP4 = 0, 1, 2, 3
+KIND_BF16, KIND_FP8, KIND_INT8, KIND_NVFP4, KIND_FP8_UE8M0 = 0, 1, 2, 3, 4
 
 
 class GemmDesc(Structure):
@@ -63,6 +63,9 @@ EXPORTS = [
     "ag_m_grouped_int8_gemm_nt",
     "ag_m_grouped_fp4_gemm_nt",
     "ag_m_grouped_fp8_gemm_nt_static_scratch",
+    "ag_m_grouped_fp8_ue8m0_gemm_nt",
+    "ag_fp8_sf_blocked_bytes",
+    "ag_fp8_sf_to_blocked_ue8m0",
     "ag_static_scratch_bytes",
     "ag_scratch_bytes",
     "ag_read_status",
@@ -100,7 +103,7 @@ def load() -> ctypes.CDLL:
         )
     lib = ctypes.CDLL(str(LIB_PATH))
     for name in ("ag_m_grouped_bf16_gemm_nt", "ag_m_grouped_fp8_gemm_nt", "ag_m_grouped_int8_gemm_nt",
-                 "ag_m_grouped_fp4_gemm_nt", "ag_m_grouped_fp8_gemm_nt_static_scratch"):
+                 "ag_m_grouped_fp4_gemm_nt", "ag_m_grouped_fp8_gemm_nt_static_scratch", "ag_m_grouped_fp8_ue8m0_gemm_nt"):
         fn = getattr(lib, name)
         fn.argtypes = [POINTER(GemmDesc)]
         fn.restype = c_int32
@@ -116,13 +119,17 @@ def load() -> ctypes.CDLL:
     lib.ag_get_num_sms.restype = c_int32
     lib.ag_get_mk_alignment_for_contiguous_layout.argtypes = []
     lib.ag_get_mk_alignment_for_contiguous_layout.restype = c_int32
+    lib.ag_fp8_sf_blocked_bytes.argtypes = [c_int64, c_int64, c_int64]
+    lib.ag_fp8_sf_blocked_bytes.restype = c_uint64
+    lib.ag_fp8_sf_to_blocked_ue8m0.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p]
+    lib.ag_fp8_sf_to_blocked_ue8m0.restype = c_int32
     lib.ag_fp4_sf_blocked_bytes.argtypes = [c_int64, c_int64, c_int64]
     lib.ag_fp4_sf_blocked_bytes.restype = c_uint64
     lib.ag_fp4_sf_to_blocked.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]
     lib.ag_fp4_sf_to_blocked.restype = c_int32
-    lib.ag_quant_rows_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
+    lib.ag_quant_rows_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     lib.ag_quant_rows_fp8.restype = c_int32
-    lib.ag_silu_mul_quant_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
+    lib.ag_silu_mul_quant_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     lib.ag_silu_mul_quant_fp8.restype = c_int32
     lib.ag_move_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
     lib.ag_move_rows.restype = c_int32

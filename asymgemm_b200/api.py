@@ -24,7 +24,7 @@ from . import _lib
 from ._lib import GemmDesc
 
 _MK_ALIGNMENT = 128
-_state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0}
+_state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0, "fp8_ue8m0": False}
 _scratch_cache: dict = {}
 _status_cache: dict = {}
 _dev_copy_cache: dict = {}
@@ -57,6 +57,16 @@ def set_wait_limit_ms(ms: int) -> None:
 def set_tile_config(tile: int) -> None:
     """Force a tile configuration (see ``ag_gemm_desc_t.tile_config``); 0 = choose from where B lives."""
     _state["tile_config"] = int(tile)
+
+
+def set_fp8_scale_mode(mode: str) -> None:
+    """How the FP8 entry points apply their fp32 block scales when the call does not say (`ue8m0_scales=None`):
+    "fp32" (default) multiplies by the exact fp32 scales in the TMEM drain; "ue8m0" lets the tensor core apply them as
+    power-of-two factors like the reference's SM100 kernel (mantissas are dropped: use it with scales produced by
+    `use_ue8m0=True` quantisers). The hardware path needs 128-row aligned segments / M_max."""
+    if mode not in ("fp32", "ue8m0"):
+        raise RuntimeError("mode must be 'fp32' or 'ue8m0'")
+    _state["fp8_ue8m0"] = mode == "ue8m0"
 
 
 def set_split_segments(flag: bool) -> None:
@@ -264,29 +274,71 @@ def _fp8_scales(a, b, g, rows_shape, n, k, recipe):
     return sfa.contiguous(), _device_copy(sfb.contiguous(), a_q.device)
 
 
+def _fp8_blocked_ue8m0(sf: torch.Tensor, groups: int, rows: int, kb: int, rows_per_scale: int, device, cache: bool) -> torch.Tensor:
+    """fp32 scales -> blocked UE8M0 device buffer for the hardware-scaled FP8 kernel (weights: once, cached)."""
+    lib = _lib.load()
+    if cache:
+        hit = _cache_get(_blocked_cache, sf, device)
+        if hit is not None:
+            return hit
+    out = torch.empty(int(lib.ag_fp8_sf_blocked_bytes(groups, rows, kb)), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _lib.check(lib.ag_fp8_sf_to_blocked_ue8m0(sf.data_ptr(), out.data_ptr(), groups, rows, kb, rows_per_scale,
+                                                  torch.cuda.current_stream(device).cuda_stream))
+    if cache:
+        torch.cuda.current_stream(device).synchronize()
+        _cache_put(_blocked_cache, sf, device, out)
+    return out
+
+
+def _fp8_use_hw(ue8m0_scales: Optional[bool]) -> bool:
+    return _state["fp8_ue8m0"] if ue8m0_scales is None else bool(ue8m0_scales)
+
+
 def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor], d,
                                           offsets, experts, list_size=None,
                                           recipe: Optional[Tuple[int, int, int]] = None, compiled_dims: str = "nk",
-                                          disable_ue8m0_cast: bool = False) -> None:
-    """FP8 E4M3 with 1x128 (A) and 128x128 (B) fp32 scales, bf16 out (csrc/apis/gemm.hpp:81-157)."""
+                                          disable_ue8m0_cast: bool = False, *, ue8m0_scales: Optional[bool] = None) -> None:
+    """FP8 E4M3 with 1x128 (A) and 128x128 (B) fp32 scales, bf16 out (csrc/apis/gemm.hpp:81-157).
+
+    ``ue8m0_scales`` (extension): True = apply the scales in the tensor core as power-of-two factors (the reference's
+    SM100 numerics; segments must be 128-row aligned), False = exact fp32 in the drain, None = `set_fp8_scale_mode`.
+    """
     g, m, n, k = _common_checks(a[0], b[0], d, masked=False)
     _check_index_tensors(offsets, experts, g)
     sfa, sfb = _fp8_scales(a, b, g, (m,), n, k, recipe)
     if m == 0:
         return
     segs = _list_size_to_segments(list_size, offsets, experts)
+    if _fp8_use_hw(ue8m0_scales):
+        kb, dev = (k + 127) // 128, a[0].device
+        sfa_b = _fp8_blocked_ue8m0(sfa, 1, m, kb, 1, dev, cache=False)
+        cacheable = b[1].is_contiguous() and (b[1].is_cuda or b[1].is_pinned())
+        sfb_b = _fp8_blocked_ue8m0(b[1] if cacheable else sfb, g, n, kb, 128, dev, cache=cacheable)
+        _launch(_lib.KIND_FP8_UE8M0, "ag_m_grouped_fp8_ue8m0_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b,
+                d=d, offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
+        return
     _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
             offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
 
 
 def m_grouped_fp8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk",
-                                      disable_ue8m0_cast: bool = False) -> None:
-    """Masked FP8 (csrc/apis/gemm.hpp:159-235)."""
+                                      disable_ue8m0_cast: bool = False, *, ue8m0_scales: Optional[bool] = None) -> None:
+    """Masked FP8 (csrc/apis/gemm.hpp:159-235). ``ue8m0_scales``: see the contiguous entry point (needs M_max % 128 == 0)."""
     g, m, n, k = _common_checks(a[0], b[0], d, masked=True)
     sfa, sfb = _fp8_scales(a, b, g, (g, m), n, k, recipe)
     _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
              "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
     if m == 0 or expected_m == 0:
+        return
+    if _fp8_use_hw(ue8m0_scales):
+        _require(m % 128 == 0, "the hardware-scaled FP8 path needs M_max to be a multiple of 128")
+        kb, dev = (k + 127) // 128, a[0].device
+        sfa_b = _fp8_blocked_ue8m0(sfa, 1, g * m, kb, 1, dev, cache=False)
+        cacheable = b[1].is_contiguous() and (b[1].is_cuda or b[1].is_pinned())
+        sfb_b = _fp8_blocked_ue8m0(b[1] if cacheable else sfb, g, n, kb, 128, dev, cache=cacheable)
+        _launch(_lib.KIND_FP8_UE8M0, "ag_m_grouped_fp8_ue8m0_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
+                masked_m=masked_m, m=m, n=n, k=k, g=g)
         return
     _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
             masked_m=masked_m, m=m, n=n, k=k, g=g)

@@ -118,7 +118,7 @@ int device_sm_count(int* out) {
 uint64_t k_bytes_of(int kind, int64_t k) {
   switch (kind) {
     case 0: return static_cast<uint64_t>(k) * 2;
-    case 3: return static_cast<uint64_t>(k) / 2;
+    case 3: return static_cast<uint64_t>(k) / 2;   // kind 4 (fp8 with UE8M0 scales): one byte per element, like fp8
     default: return static_cast<uint64_t>(k);
   }
 }
@@ -139,7 +139,7 @@ int run(int kind, const ag_gemm_desc_t* g) {
   AG_REQUIRE(g->n % 8 == 0, "n must be a multiple of 8 (got %lld)", static_cast<long long>(g->n));
   if (masked) AG_REQUIRE(g->masked_m != nullptr, "masked layout needs masked_m");
   else AG_REQUIRE(g->offsets != nullptr && g->experts != nullptr, "contiguous layout needs offsets and experts");
-  if (kind == 1 || kind == 2 || kind == 3) AG_REQUIRE(g->sfa != nullptr && g->sfb != nullptr, "quantised kinds need sfa and sfb");
+  if (kind >= 1) AG_REQUIRE(g->sfa != nullptr && g->sfb != nullptr, "quantised kinds need sfa and sfb");
 
   const uint64_t kbytes = k_bytes_of(kind, g->k);
   AG_REQUIRE(kbytes % 16 == 0, "K must make rows a multiple of 16 bytes (row bytes %llu)", static_cast<unsigned long long>(kbytes));
@@ -187,15 +187,16 @@ int run(int kind, const ag_gemm_desc_t* g) {
   if (tile == agb::kTileDeviceRegAcc)
     AG_REQUIRE(kind == 1 || kind == 2, "tile_config 5 (register accumulators) exists for fp8 and int8 only");
   AG_REQUIRE(tile >= 0 && tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
-  if (kind == 3) {
-    AG_REQUIRE(agb::kTileConfigs[tile].bn >= 64, "nvfp4 supports tile_config 1 and 4 only (64 or 128 columns per item)");
-    AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
-    if (masked) AG_REQUIRE(g->m % 128 == 0, "nvfp4 masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
+  if (kind == 3 || kind == 4) {
+    AG_REQUIRE(tile == 0 || tile == 3, "hardware block-scaled kinds support tile_config 1 and 4 only (128 or 64 columns per item)");
+    if (kind == 3) AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
+    if (masked) AG_REQUIRE(g->m % 128 == 0, "block-scaled masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
   }
   const int bn = agb::tile_config_of(kind, tile).bn, ka = agb::tile_config_of(kind, tile).ka;
   p.n_tiles = static_cast<int>((g->n + bn - 1) / bn);
   p.kb_count = static_cast<int>((kbytes + 127) / 128);
-  p.sf_k = kind == 3 ? static_cast<int>(agb::fp4_sf_k4_padded_host((g->k + 15) / 16)) : static_cast<int>((g->k + 127) / 128);
+  p.sf_k = kind == 3 ? static_cast<int>(agb::fp4_sf_k4_padded_host((g->k + 15) / 16))
+           : kind == 4 ? static_cast<int>(agb::fp8_sf_k4_padded_host((g->k + 127) / 128)) : static_cast<int>((g->k + 127) / 128);
   p.sfb_rows = kind == 2 ? static_cast<int>(g->n) : static_cast<int>((g->n + 127) / 128);
   p.d_fp32 = g->d_dtype == AG_D_FP32;
   p.b_streaming = res == RES_HOST_MAPPED;
@@ -259,6 +260,23 @@ int ag_m_grouped_bf16_gemm_nt(const ag_gemm_desc_t* desc) { return run(0, desc);
 int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc) { return run(1, desc); }
 int ag_m_grouped_int8_gemm_nt(const ag_gemm_desc_t* desc) { return run(2, desc); }
 int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc) { return run(3, desc); }
+int ag_m_grouped_fp8_ue8m0_gemm_nt(const ag_gemm_desc_t* desc) { return run(4, desc); }
+
+uint64_t ag_fp8_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t kb) {
+  return static_cast<uint64_t>(groups) * static_cast<uint64_t>((rows + 127) / 128) * static_cast<uint64_t>(agb::fp8_sf_k4_padded_host(kb)) * 512;
+}
+
+int ag_fp8_sf_to_blocked_ue8m0(const float* src, void* dst, int64_t groups, int64_t rows, int64_t kb, int32_t rows_per_scale, void* stream) {
+  AG_REQUIRE(src != nullptr && dst != nullptr && groups > 0 && rows > 0 && kb > 0 && (rows_per_scale == 1 || rows_per_scale == 128),
+             "bad arguments (rows_per_scale must be 1 or 128)");
+  const void* src_dev = src;
+  if (classify(src, &src_dev) == RES_UNREACHABLE)
+    return fail(AG_E_NOT_MAPPED, "scale tensor (%p) is neither device memory nor pinned/registered host memory", static_cast<const void*>(src));
+  cudaError_t e = agb::fp8_sf_to_blocked_ue8m0(static_cast<const float*>(src_dev), dst, groups, rows, kb, rows_per_scale,
+                                               static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(AG_E_CUDA, "scale re-layout launch failed: %s", cudaGetErrorString(e));
+  return AG_OK;
+}
 
 uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms) {
   (void)n;

@@ -9,6 +9,8 @@ namespace agb {
 // Tile configurations. BN = output columns (= weight rows) per item, KA = 128-byte K atoms per weight stage,
 // SB = weight ring depth. Every configuration keeps 128 KB of weight reads in flight per CTA and a 64 KB
 // activation ring (SA = 4 stages of 128 rows x 128 B).
+constexpr bool kind_is_block_scaled(int kind) { return kind == 3 || kind == 4; }
+
 struct TileConfig {
   int bn, ka, sb;
 };
@@ -23,7 +25,7 @@ constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
 constexpr int kTileDeviceRegAcc = 4;
 // rows of one accumulator chunk (what one item covers when long segments are split)
 constexpr int chunk_tiles_of(int kind, int tile, int bn) {
-  return kind == 3 ? (512 - 64) / bn : ((kind == 1 || kind == 2) ? (tile == kTileDeviceRegAcc ? 1 : 512 / bn - 2) : 512 / bn);
+  return kind_is_block_scaled(kind) ? (512 - 64) / bn : ((kind == 1 || kind == 2) ? (tile == kTileDeviceRegAcc ? 1 : 512 / bn - 2) : 512 / bn);
 }
 // NVFP4 also stages 2 KB of scale factors per K atom and operand, so its host-streaming configuration uses
 // single-atom stages in a deeper ring to stay inside the 227 KB of shared memory.
@@ -39,13 +41,17 @@ cudaError_t launch_bf16(AGB_LAUNCH_ARGS);
 cudaError_t launch_fp8(AGB_LAUNCH_ARGS);
 cudaError_t launch_int8(AGB_LAUNCH_ARGS);
 cudaError_t launch_fp4(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
+cudaError_t launch_fp8_ue8m0(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
+cudaError_t fp8_sf_to_blocked_ue8m0(const float* src, void* dst, long long groups, long long rows, long long kb, int rows_per_scale,
+                                    cudaStream_t stream);
 cudaError_t fp4_sf_to_blocked(const void* src, void* dst, long long groups, long long rows, long long k16, cudaStream_t stream);
 long long fp4_sf_k4_padded_host(long long k16);
+long long fp8_sf_k4_padded_host(long long kb);
 
 template <Kind KIND, int BN, int KA, int SB, bool REG_ACC = false>
 cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ms,
                        const GemmParams& p) {
-  using L = SmemLayout<BN, KA, kStagesA, SB, KindTraits<KIND>::block_scaled>;
+  using L = SmemLayout<BN, KA, kStagesA, SB, SfStage<KIND, KA>::a, SfStage<KIND, KA>::b>;
   static_assert(L::dyn_bytes <= 232448, "tile configuration does not fit in shared memory");
   auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB, REG_ACC>;
   static bool configured[64] = {};
@@ -81,6 +87,7 @@ inline cudaError_t launch_mgrouped(int kind, AGB_LAUNCH_ARGS) {
     case 1: return launch_fp8(tile, grid, stream, ma, mb, ms, p);
     case 2: return launch_int8(tile, grid, stream, ma, mb, ms, p);
     case 3: return launch_fp4(tile, grid, stream, ma, mb, ms, p);
+    case 4: return launch_fp8_ue8m0(tile, grid, stream, ma, mb, ms, p);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -36,7 +36,7 @@
 
 namespace agb {
 
-enum class Kind : int { BF16 = 0, FP8 = 1, INT8 = 2, NVFP4 = 3 };
+enum class Kind : int { BF16 = 0, FP8 = 1, INT8 = 2, NVFP4 = 3, FP8_UE8M0 = 4 };
 enum : int { LAYOUT_CONTIGUOUS = 0, LAYOUT_MASKED = 1 };
 
 // status codes written to GemmParams::status (low byte = code, upper bits = CTA index)
@@ -202,6 +202,16 @@ struct KindTraits<Kind::NVFP4> {
   static constexpr bool block_scaled = true;
   static constexpr uint32_t d_fmt = 1, ab_fmt = 1;
 };
+// FP8 with power-of-two block scales applied by the tensor core (what the reference's SM100 FP8 kernel does,
+// asym_gemm/include/asym_gemm/impls/sm100_fp8_asym_gemm_1d1d.cuh:433-462): one UE8M0 byte per row and 128-wide K block,
+// four K blocks per 32-bit TMEM word, the byte picked by the descriptor's sf-id. No drain-side arithmetic.
+template <>
+struct KindTraits<Kind::FP8_UE8M0> {
+  static constexpr MmaKind mma = MmaKind::F8F6F4;  // unused: issued through umma_mxfp8
+  static constexpr bool sw_scale = false;
+  static constexpr bool block_scaled = true;
+  static constexpr uint32_t d_fmt = 1, ab_fmt = 0;
+};
 
 constexpr int BM = 128;            // rows per MMA tile
 constexpr int ATOM_BYTES = 128;    // bytes of K per pipeline stage row (one 128-byte swizzle atom)
@@ -215,15 +225,23 @@ constexpr int SF_BLOCK_BYTES = 512;
 constexpr int SF_ATOM_BYTES = 4 * SF_BLOCK_BYTES;
 constexpr int SF_TMEM_COLS = 64;   // A: 2 x 16 columns, B: 2 x 16 columns (double-buffered)
 
-template <int BN, int KA, int SA, int SB, bool HAS_SF = false>
+// Scale-factor bytes staged with every A stage / B stage (0 for kinds without hardware block scaling).
+// NVFP4: 2 KB per 128-byte K atom. FP8_UE8M0: one 512-byte block covers four K atoms; it travels with every stage.
+template <Kind KIND, int KA>
+struct SfStage {
+  static constexpr int a = KIND == Kind::NVFP4 ? SF_ATOM_BYTES : (KIND == Kind::FP8_UE8M0 ? SF_BLOCK_BYTES : 0);
+  static constexpr int b = KIND == Kind::NVFP4 ? SF_ATOM_BYTES * KA : (KIND == Kind::FP8_UE8M0 ? SF_BLOCK_BYTES : 0);
+};
+
+template <int BN, int KA, int SA, int SB, int SFA_BYTES = 0, int SFB_BYTES = 0>
 struct SmemLayout {
   static constexpr int a_stage = BM * ATOM_BYTES;
   static constexpr int b_box = BN * ATOM_BYTES;       // one TMA box: BN rows x 128 bytes of K
   static constexpr int b_stage = b_box * KA;          // KA K-adjacent boxes per stage
   static constexpr int a_off = 0;
   static constexpr int b_off = a_off + SA * a_stage;
-  static constexpr int sfa_stage = HAS_SF ? SF_ATOM_BYTES : 0;
-  static constexpr int sfb_stage = HAS_SF ? SF_ATOM_BYTES * KA : 0;
+  static constexpr int sfa_stage = SFA_BYTES;
+  static constexpr int sfb_stage = SFB_BYTES;
   static constexpr int sfa_off = b_off + SB * b_stage;
   static constexpr int sfb2_off = sfa_off + SA * sfa_stage;
   static constexpr int bar_off = sfb2_off + SB * sfb_stage;
@@ -286,7 +304,8 @@ __global__ void __launch_bounds__(num_threads_of<KIND, BN, REG_ACC>(), 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_s, const GemmParams p) {
   using T = KindTraits<KIND>;
-  using L = SmemLayout<BN, KA, SA, SB, T::block_scaled>;
+  using L = SmemLayout<BN, KA, SA, SB, SfStage<KIND, KA>::a, SfStage<KIND, KA>::b>;
+  static_assert(KIND != Kind::FP8_UE8M0 || (KA == 1 || KA == 2 || KA == 4), "a UE8M0 scale block spans four K atoms");
   static_assert(BN == 32 || BN == 64 || BN == 128, "BN must be 32, 64 or 128");
   static_assert(!T::block_scaled || BN >= 64, "block-scaled kinds need BN >= 64");
   // TMEM plan: 512 / BN slots of BN columns. Hardware-accumulated kinds keep one output tile per slot; software-scaled
@@ -296,7 +315,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int RAW_SLOTS = REG_ACC ? NUM_SLOTS : 2;                 // raw product slots (software-scaled kinds)
   constexpr int CHUNK_TILES = T::sw_scale ? (REG_ACC ? 1 : NUM_SLOTS - 2) : NUM_SLOTS;
   constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
-  constexpr uint32_t IDESC = T::block_scaled ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);
+  constexpr uint32_t IDESC = KIND == Kind::NVFP4 ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);   // FP8_UE8M0: per K atom
   constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, BN, REG_ACC>();   // one arrival per drain warp
   constexpr uint32_t SF_COL0 = NUM_SLOTS * BN;   // first TMEM column of the scale-factor area
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
@@ -391,8 +410,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if constexpr (T::block_scaled) {
               // scales of this stage: KA x 2 KB, contiguous in the blocked layout (the K direction is padded)
               const long long tile128 = static_cast<long long>(it.expert) * p.sfb_rows + ((it.nt * BN) >> 7);
-              bulk_load_1d(smem_sfb + s * L::sfb_stage,
-                           sfb_blocked + (tile128 * p.sf_k + static_cast<long long>(ks) * KA * 4) * SF_BLOCK_BYTES, L::sfb_stage, &b_full[s]);
+              const long long blk = KIND == Kind::NVFP4 ? static_cast<long long>(ks) * KA * 4 : (static_cast<long long>(ks) * KA) >> 2;
+              bulk_load_1d(smem_sfb + s * L::sfb_stage, sfb_blocked + (tile128 * p.sf_k + blk) * SF_BLOCK_BYTES, L::sfb_stage, &b_full[s]);
             }
 #pragma unroll
             for (int bx = 0; bx < KA; ++bx) {
@@ -445,8 +464,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               mbar_arrive_expect_tx(&a_full[s], L::a_stage + L::sfa_stage);
               const int a_row = it.row0 + (m0 + mt) * BM;
               if constexpr (T::block_scaled) {
-                bulk_load_1d(smem_sfa + s * L::sfa_stage,
-                             sfa_blocked + (static_cast<long long>(a_row >> 7) * p.sf_k + static_cast<long long>(kb) * 4) * SF_BLOCK_BYTES,
+                const long long blk = KIND == Kind::NVFP4 ? static_cast<long long>(kb) * 4 : static_cast<long long>(kb >> 2);
+                bulk_load_1d(smem_sfa + s * L::sfa_stage, sfa_blocked + (static_cast<long long>(a_row >> 7) * p.sf_k + blk) * SF_BLOCK_BYTES,
                              L::sfa_stage, &a_full[s]);
               }
               tma_load_2d(smem_a + s * L::a_stage, &tmap_a, &a_full[s], kb * ATOM_BYTES, a_row);
@@ -497,15 +516,16 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               uint32_t sfa_col = 0, sfb_col = 0;
               if constexpr (T::block_scaled) {
                 // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
+                constexpr int BLOCKS = KIND == Kind::NVFP4 ? 4 : 1;   // 512-byte blocks per stage and operand
                 sfa_col = SF_COL0 + (it_a & 1) * 16;
                 sfb_col = SF_COL0 + 32 + (kb & 1) * 16;
                 const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
+                for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
                 if (mt == 0) {
-                  const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + bx * SF_ATOM_BYTES);
+                  const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + (KIND == Kind::NVFP4 ? bx * SF_ATOM_BYTES : 0));
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
+                  for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
                 }
                 // a 64-row weight tile uses half of its 128-row scale block: words 0-1 or 2-3 of each lane
                 if constexpr (BN == 64) sfb_col += ((it.nt & 1) ? 2 : 0);
@@ -515,8 +535,14 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const uint64_t da = make_kmajor_sw128_desc(a_addr + j * MMA_K_BYTES);
                 const uint64_t db = make_kmajor_sw128_desc(b_addr + j * MMA_K_BYTES);
                 const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
-                if constexpr (T::block_scaled) umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
-                else umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+                if constexpr (KIND == Kind::NVFP4) {
+                  umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
+                } else if constexpr (KIND == Kind::FP8_UE8M0) {
+                  // all four MMAs of this K atom use the atom's scale byte: byte (kb % 4) of the scale words
+                  umma_mxfp8(tmem_base + d_col, da, db, make_idesc_mxfp8(BN, kb & 3), tmem_base + sfa_col, tmem_base + sfb_col, acc);
+                } else {
+                  umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+                }
               }
               umma_commit(&a_empty[sa]);
               if constexpr (T::sw_scale) {

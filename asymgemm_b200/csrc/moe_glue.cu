@@ -34,9 +34,17 @@ __device__ __forceinline__ uint32_t quantise4(const float (&v)[4], float inv) {
 // One warp per (row, 128-column block): scale = max(amax, 1e-4) / 448, q = e4m3(x * (1 / scale)).
 // MODE 0: x is bf16 [rows, cols]. MODE 1: x is bf16 [rows, 2*cols] holding gate | up; the value quantised is
 // bf16(silu(gate) * up), the activation the reference's CPU MoE bucket forms (csrc/cpu/module.cpp:337-347).
+// Smallest power of two >= x (x > 0, finite): what ceil_to_ue8m0 of the quantisers computes (asym_gemm/utils/math.py:17-21).
+__device__ __forceinline__ float ceil_pow2(float x) {
+  const uint32_t bits = __float_as_uint(x);
+  return __uint_as_float((bits & 0x7F800000u) + ((bits & 0x007FFFFFu) ? 0x00800000u : 0u));
+}
+
+// `pow2_scales`: round every scale up to a power of two (use_ue8m0=True of the quantisers), for the hardware-scaled GEMM.
 template <int MODE>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                                                         float* __restrict__ sf, long long rows, int cols, int blocks_per_row) {
+                                                         float* __restrict__ sf, long long rows, int cols, int blocks_per_row,
+                                                         int pow2_scales) {
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = rows * blocks_per_row;
@@ -75,7 +83,8 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   }
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
   amax = fmaxf(warp_max(amax), 1e-4f);
-  const float scale = amax * (1.0f / kFp8Max);  // torch's CUDA division by a scalar multiplies by its fp32 reciprocal
+  float scale = amax * (1.0f / kFp8Max);  // torch's CUDA division by a scalar multiplies by its fp32 reciprocal
+  if (pow2_scales) scale = ceil_pow2(scale);
   const float inv = 1.0f / scale;
   const uint32_t packed = quantise4(v, inv);
   uint8_t* qr = q + row * cols;
@@ -188,23 +197,23 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 extern "C" {
 
-int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream) {
+int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, void* stream) {
   if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || cols % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   const int bpr = static_cast<int>((cols + 127) / 128);
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<0><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr);
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales);
   return launch_check();
 }
 
-int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, void* stream) {
+int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales, void* stream) {
   if (!gate_up_bf16 || !q || !sf || rows < 0 || inter <= 0 || inter % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (inter must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   const int bpr = static_cast<int>((inter + 127) / 128);
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<1><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr);
+      static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, pow2_scales);
   return launch_check();
 }
 

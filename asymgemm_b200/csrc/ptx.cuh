@@ -211,6 +211,18 @@ __device__ __forceinline__ void umma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+// FP8 E4M3 operands with one UE8M0 (power-of-two) scale per 32 elements of K and operand row, scales read from TMEM;
+// the scale byte of each operand is selected inside its 32-bit TMEM word by the sf-id fields of the descriptor.
+__device__ __forceinline__ void umma_mxfp8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(
+          d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+
 // Copy 32 rows x 16 bytes from shared memory into 4 TMEM columns, replicated into all four 32-lane quarters.
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t s_desc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(s_desc) : "memory");
@@ -230,6 +242,12 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t ab_fm
 // Block-scaled descriptor for kind::mxf4nvf4: E2M1 operands (format 1), UE4M3 scales (scale format 0), SF ids 0.
 __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t n) {
   return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((128u >> 4) << 24);
+}
+
+// Block-scaled descriptor for kind::mxf8f6f4 with E4M3 operands (format 0) and UE8M0 scales (scale format 1);
+// sf_id (0..3) selects which byte of the scale words both operands use.
+__host__ __device__ constexpr uint32_t make_idesc_mxfp8(uint32_t n, uint32_t sf_id) {
+  return (sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
 }
 
 }  // namespace agb

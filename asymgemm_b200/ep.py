@@ -286,8 +286,11 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
-                 expert_ranges: Optional[List[Tuple[int, int]]] = None):
+                 expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False):
+        """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
+        (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly."""
         self.dispatcher = EPDispatcher(num_experts, group, expert_ranges)
+        self.ue8m0_scales = bool(ue8m0_scales)
         self.hidden, self.inter = hidden, inter
         self.w13, self.w2 = w13, w2
         epr = self.dispatcher.experts_per_rank
@@ -303,14 +306,15 @@ class ExpertParallelMoE:
         d2 = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=dev)
         if m == 0:
             return d2
-        api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), self.w13, d1, state.offsets, state.experts, None)
-        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter)
-        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), self.w2, d2, state.offsets, state.experts, None)
+        hw = self.ue8m0_scales
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), self.w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
+        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw)
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), self.w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
         return d2
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
-        x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous())
+        x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous(), pow2_scales=self.ue8m0_scales)
         state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)

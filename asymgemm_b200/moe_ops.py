@@ -17,19 +17,20 @@ def _stream(t: torch.Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def quant_rows_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [rows, cols] -> (e4m3 [rows, cols], fp32 scales [rows, ceil(cols/128)]), one kernel."""
+def quant_rows_fp8(x: torch.Tensor, pow2_scales: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, cols] -> (e4m3 [rows, cols], fp32 scales [rows, ceil(cols/128)]), one kernel.
+    `pow2_scales` rounds the scales up to powers of two (the quantisers' use_ue8m0=True)."""
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
         raise RuntimeError("quant_rows_fp8 wants a contiguous 2-D bf16 CUDA tensor")
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
     sf = torch.empty((rows, (cols + 127) // 128), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.load().ag_quant_rows_fp8(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, cols, _stream(x)))
+        _lib.check(_lib.load().ag_quant_rows_fp8(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, cols, int(pow2_scales), _stream(x)))
     return q, sf
 
 
-def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int) -> Tuple[torch.Tensor, torch.Tensor]:
+def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int, pow2_scales: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [rows, 2*inter] -> bf16(silu(gate) * up) quantised to (e4m3 [rows, inter], fp32 [rows, ceil(inter/128)])."""
     if not (gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.dim() == 2 and gate_up.is_contiguous()
             and gate_up.shape[1] == 2 * inter):
@@ -38,7 +39,7 @@ def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int) -> Tuple[torch.Tensor,
     q = torch.empty((rows, inter), dtype=torch.float8_e4m3fn, device=gate_up.device)
     sf = torch.empty((rows, (inter + 127) // 128), dtype=torch.float32, device=gate_up.device)
     with torch.cuda.device(gate_up.device):
-        _lib.check(_lib.load().ag_silu_mul_quant_fp8(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, inter, _stream(gate_up)))
+        _lib.check(_lib.load().ag_silu_mul_quant_fp8(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, inter, int(pow2_scales), _stream(gate_up)))
     return q, sf
 
 

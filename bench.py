@@ -56,7 +56,7 @@ def rows_per_expert(cfg, seed=0):
     return torch.bincount(picks.flatten(), minlength=e).tolist()
 
 
-def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False, expert_range=None):
+def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False, expert_range=None, ue8m0=False):
     """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
     from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
                                      per_token_cast_to_fp8, per_token_cast_to_int8)
@@ -77,7 +77,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     for e, start, rows in segs:
         x = torch.randn((rows, k), device=device, generator=gen)
         if kind == "fp8":
-            q, s = per_token_cast_to_fp8(x, use_ue8m0=False)
+            q, s = per_token_cast_to_fp8(x, use_ue8m0=ue8m0)
             a[start:start + rows], sfa[start:start + rows] = q, s
         elif kind == "int8":
             q, s = per_token_cast_to_int8(x)
@@ -98,7 +98,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     for e in range(g):
         w = torch.randn((n, k), device=device, generator=gen) * 0.02
         if kind == "fp8":
-            q, s = per_block_cast_to_fp8(w, use_ue8m0=False)
+            q, s = per_block_cast_to_fp8(w, use_ue8m0=ue8m0)
             sfb[e] = s
         elif kind == "int8":
             q, s = per_channel_cast_to_int8(w)
@@ -116,7 +116,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
 
 
-def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None):
+def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None, ue8m0=False):
     """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
     GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing."""
     from asymgemm_b200 import ep
@@ -130,14 +130,14 @@ def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None):
     s13 = torch.empty((epr, 2 * i // 128, h // 128), dtype=torch.float32, device=device)
     s2 = torch.empty((epr, h // 128, i // 128), dtype=torch.float32, device=device)
     for e in range(epr):
-        q, s = per_block_cast_to_fp8(torch.randn((2 * i, h), device=device, generator=gen) * 0.02, use_ue8m0=False)
+        q, s = per_block_cast_to_fp8(torch.randn((2 * i, h), device=device, generator=gen) * 0.02, use_ue8m0=ue8m0)
         w13[e].copy_(q, non_blocking=True)
         s13[e] = s
-        q, s = per_block_cast_to_fp8(torch.randn((h, i), device=device, generator=gen) * 0.02, use_ue8m0=False)
+        q, s = per_block_cast_to_fp8(torch.randn((h, i), device=device, generator=gen) * 0.02, use_ue8m0=ue8m0)
         w2[e].copy_(q, non_blocking=True)
         s2[e] = s
     torch.cuda.synchronize(device)
-    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges)
+    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges, ue8m0_scales=ue8m0)
     t_local = cfg["tokens"] // world
     x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
     logits = torch.randn((t_local, e_total), device=device, generator=gen)
@@ -327,6 +327,9 @@ def main():
     ap.add_argument("--weights", default="host", choices=["host", "device"],
                     help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
     ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
+    ap.add_argument("--fp8-scales", default="fp32", choices=["fp32", "ue8m0"],
+                    help="fp32 (default): arbitrary fp32 block scales applied exactly in the TMEM drain; ue8m0: power-of-two scales "
+                         "(use_ue8m0 quantisers) applied by the tensor core, the reference's SM100 numerics")
     ap.add_argument("--even-shards", action="store_true",
                     help="N > 1: give every rank the same number of experts even when the host links are measured unequal")
     ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
@@ -386,11 +389,15 @@ def main():
         config["sharding"] = ("contiguous expert ranges sized by each rank's host-link rate measured with all ranks streaming at once "
                               f"({[round(x, 1) for x in rates.tolist()]} GB/s); equal when the rates are within 10 %")
     if moe:
-        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges)
+        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=args.fp8_scales == "ue8m0")
     elif cfg["kind"] == "fp4":
         w = build_masked_fp4(cfg, rank, world, device)
     else:
-        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages, expert_range=expert_range)
+        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages, expert_range=expert_range,
+                           ue8m0=args.fp8_scales == "ue8m0")
+    if args.fp8_scales == "ue8m0":
+        ag.set_fp8_scale_mode("ue8m0")
+        config["fp8_scales"] = "power-of-two (UE8M0), applied by the tensor core"
     if on_dev:
         config["workload"] = config["workload"].replace("B in pinned host DRAM", "B resident in HBM")
     ag.set_tile_config(args.tile)

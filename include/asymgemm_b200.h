@@ -93,6 +93,17 @@ int ag_m_grouped_bf16_gemm_nt(const ag_gemm_desc_t* desc);
  * result whenever the quantiser produced power-of-two scales. */
 int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc);
 
+/* FP8 E4M3 with the block scales applied by the tensor core as UE8M0 (power-of-two) factors: the numerics of the
+ * reference's SM100 FP8 kernel (asym_gemm/include/asym_gemm/impls/sm100_fp8_asym_gemm_1d1d.cuh:433-462), which drops the
+ * mantissa of every fp32 scale (impls/smxx_layout.cuh:96-100). Exact when the quantiser produced power-of-two scales
+ * (use_ue8m0=True); no per-block arithmetic in the drain, so it is the faster path when rows per expert are many.
+ * `sfa` and `sfb` are DEVICE buffers in the blocked layout written by ag_fp8_sf_to_blocked_ue8m0 (sfa: groups = 1, rows =
+ * all rows of A, rows_per_scale = 1; sfb: groups = G, rows = N, rows_per_scale = 128). Segments must start on multiples
+ * of 128 rows; masked M_max % 128 == 0; tile_config 0, 1 or 4. */
+int ag_m_grouped_fp8_ue8m0_gemm_nt(const ag_gemm_desc_t* desc);
+uint64_t ag_fp8_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t kb);
+int ag_fp8_sf_to_blocked_ue8m0(const float* src, void* dst, int64_t groups, int64_t rows, int64_t kb, int32_t rows_per_scale, void* stream);
+
 /* INT8 x INT8 -> exact int32 per 128-wide K block, then fp32 sfa[row,kb] * sfb[col,kb] * sum, summed over
  * K blocks in ascending order. Replaces m_grouped_int8_asym_gemm_nt_contiguous / _masked
  * (csrc/apis/gemm.hpp:569-630; kernel asym_gemm/include/asym_gemm/impls/sm90_int8_asym_gemm_1d1d.cuh:34-41). */
@@ -156,12 +167,13 @@ int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out);
  * (asym_gemm/unified_moe/runtime.py:1422-1476,1570,1620-1627; asym_gemm/unified_moe/_triton.py). */
 
 /* x bf16 [rows, cols] -> q e4m3 [rows, cols], sf fp32 [rows, ceil(cols/128)]; sf = max(amax, 1e-4) / 448 per 1x128 block,
- * q = e4m3(x * (1 / sf)): the arithmetic of per_token_cast_to_fp8 (asym_gemm/utils/math.py:24-34). cols % 4 == 0. */
-int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream);
+ * q = e4m3(x * (1 / sf)): the arithmetic of per_token_cast_to_fp8 (asym_gemm/utils/math.py:24-34). cols % 4 == 0.
+ * pow2_scales != 0 rounds every sf up to a power of two first (use_ue8m0=True), for ag_m_grouped_fp8_ue8m0_gemm_nt. */
+int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, void* stream);
 
 /* gate_up bf16 [rows, 2*inter] (gate columns first) -> bf16(silu(gate) * up) quantised as above into q [rows, inter],
  * sf [rows, ceil(inter/128)] (activation of csrc/cpu/module.cpp:337-347 followed by the 1x128 quantiser). */
-int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, void* stream);
+int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales, void* stream);
 
 /* dst[dst_rows ? dst_rows[i] : i] = src[src_rows ? src_rows[i] : i], i < rows; rows of row_bytes (multiple of 16) bytes. */
 int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes,

@@ -154,3 +154,49 @@ def test_helper_kernels_match_torch():
     y = moe_ops.combine_topk(rows, pos, w, tokens, k)
     ref = (rows[pos].view(tokens, k, -1).float() * w.unsqueeze(-1)).sum(1)
     assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+
+
+def test_pow2_quantiser_and_hardware_scaled_layer():
+    """Row quantiser with power-of-two scales against the torch quantiser with use_ue8m0=True, and the MoE layer on the
+    hardware-scaled FP8 path against the same layer on the exact path (same inputs, weights quantised with UE8M0 scales)."""
+    import asymgemm_b200 as ag
+    from asymgemm_b200 import ep, moe_ops
+    from asymgemm_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp8
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    x = (torch.randn((300, 512), device="cuda", generator=gen) * 2).to(torch.bfloat16)
+    q, sf = moe_ops.quant_rows_fp8(x, pow2_scales=True)
+    q_ref, sf_ref = per_token_cast_to_fp8(x.float(), use_ue8m0=True)
+    assert torch.equal(torch.log2(sf), torch.log2(sf).round())                 # powers of two
+    assert (sf != sf_ref).float().mean() < 1e-3                                # log2f-based torch version: rare edge cases only
+    same = sf == sf_ref
+    assert torch.equal(q.view(torch.uint8)[same.repeat_interleave(128, 1)], q_ref.view(torch.uint8)[same.repeat_interleave(128, 1)])
+
+    num_experts, hidden, inter, tokens, top_k = 4, 512, 256, 260, 2
+    cpu_gen = torch.Generator().manual_seed(10)
+    def qw(n, k):
+        return per_block_cast_to_fp8(torch.randn((n, k), generator=cpu_gen) * 0.05, use_ue8m0=True)
+    w13 = [qw(2 * inter, hidden) for _ in range(num_experts)]
+    w2 = [qw(hidden, inter) for _ in range(num_experts)]
+    pack = lambda ws: (torch.stack([q for q, _ in ws]).pin_memory(), torch.stack([s for _, s in ws]).cuda())
+    ids = torch.stack([torch.randperm(num_experts, generator=cpu_gen)[:top_k] for _ in range(tokens)]).cuda()
+    wts = torch.rand((tokens, top_k), generator=cpu_gen).cuda()
+    xin = torch.randn((tokens, hidden), generator=cpu_gen).to(torch.bfloat16).cuda()
+    outs = []
+    for hw in (True, False):
+        layer = ep.ExpertParallelMoE(num_experts, hidden, inter, pack(w13), pack(w2), ue8m0_scales=hw)
+        # both layers quantise activations with power-of-two scales so that they see identical operands
+        layer_out = None
+        x_q, sfx = moe_ops.quant_rows_fp8(xin, pow2_scales=True)
+        state, recv_q, (recv_s,) = layer.dispatcher.dispatch(x_q, ids, (sfx,))
+        a_q, sfa = ep.to_contiguous_layout(recv_q, state), ep.to_contiguous_layout(recv_s, state)
+        d1 = torch.empty((state.padded_rows, 2 * inter), dtype=torch.bfloat16, device="cuda")
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), layer.w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
+        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, inter, pow2_scales=True)
+        d2 = torch.zeros((state.padded_rows, hidden), dtype=torch.bfloat16, device="cuda")
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), layer.w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
+        outs.append(layer.dispatcher.combine(d2, state, wts))
+    ag.check_status()
+    err = float((outs[0].float() - outs[1].float()).abs().max() / outs[1].float().abs().max())
+    assert err <= 2e-2, f"hardware-scaled vs exact layer: max-rel {err:.3e}"
+    y = ep.ExpertParallelMoE(num_experts, hidden, inter, pack(w13), pack(w2), ue8m0_scales=True).forward(xin, ids, wts)
+    assert float((y.float() - outs[0].float()).abs().max()) == 0.0

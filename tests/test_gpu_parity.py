@@ -328,3 +328,50 @@ def test_two_streams_do_not_share_replay_scratch():
     torch.cuda.synchronize()
     for c, d in zip(cases, outs):
         _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
+
+
+@pytest.mark.parametrize("tile", [0, 1, 4], indirect=True)
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_fp8_hardware_ue8m0_scaling_contiguous(tile, b_on_host):
+    """FP8 with the block scales applied by the tensor core (UE8M0): exact for power-of-two scales, so it must agree with
+    the oracle and, up to fp32 summation order, with the exact-fp32-scale path. Ragged rows, long segments, N and K tails."""
+    rows = [300, 0, 1, 129, 2300, 64]
+    n, k = 392, 640
+    c = H.make_contiguous_case("fp8", rows, n, k, seed=61, b_on_host=b_on_host, use_ue8m0=True)
+    d_hw = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    d_sw = torch.full_like(d_hw, float("nan"))
+    args = ((c["a"], c["sfa"]), (c["b"], c["sfb"]))
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d_hw, c["offsets"], c["experts"], c["list_size"], ue8m0_scales=True)
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d_sw, c["offsets"], c["experts"], c["list_size"], ue8m0_scales=False)
+    torch.cuda.synchronize()
+    _check("fp8", d_hw.float().cpu().numpy(), c["ref"], c["segments"])
+    mask = H.valid_row_mask(c["segments"], c["m_total"])
+    a, b = d_hw.float().cpu().numpy()[mask], d_sw.float().cpu().numpy()[mask]
+    assert oracle.max_rel(a, b) <= 2 ** -7          # at most one bf16 ulp apart anywhere
+    assert (a != b).mean() < 0.05
+
+
+def test_fp8_hardware_ue8m0_scaling_masked_and_mode_switch():
+    masked_m = [64, 0, 128, 384, 1]
+    c = H.make_masked_case("fp8", masked_m, 384, 256, 512, seed=62, use_ue8m0=True)
+    d = torch.full((5, 384, 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ag.set_fp8_scale_mode("ue8m0")
+    try:
+        ag.m_grouped_fp8_asym_gemm_nt_masked((c["a"], c["sfa"]), (c["b"], c["sfb"]), d, c["masked_m"], 100)
+    finally:
+        ag.set_fp8_scale_mode("fp32")
+    torch.cuda.synchronize()
+    d_np = d.float().cpu().numpy().reshape(-1, 256)
+    _check("fp8", d_np, c["ref"], c["segments"])
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], d_np.shape[0])]).all()
+    # scales that are not powers of two lose their mantissa on this path, exactly as in the reference's SM100 kernel:
+    # the result equals the oracle evaluated with floored scales
+    c2 = H.make_contiguous_case("fp8", [128, 200], 128, 256, seed=63, use_ue8m0=False)
+    d2 = torch.zeros((c2["m_total"], 128), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c2["a"], c2["sfa"]), (c2["b"], c2["sfb"]), d2, c2["offsets"], c2["experts"],
+                                             c2["list_size"], ue8m0_scales=True)
+    torch.cuda.synchronize()
+    floor2 = lambda t: np.exp2(np.floor(np.log2(t)))
+    ref = oracle.gemm_fp8(H.np_bits(c2["a"]), floor2(c2["sfa"].cpu().numpy()), H.np_bits(c2["b"]), floor2(c2["sfb"].cpu().numpy()),
+                          c2["segments"])
+    _check("fp8", d2.float().cpu().numpy(), ref, c2["segments"])
