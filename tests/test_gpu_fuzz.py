@@ -68,3 +68,41 @@ def test_random_case(seed):
     except AssertionError as e:
         raise AssertionError(f"{e} [{info}]")
     assert np.isnan(d_np[~H.valid_row_mask(c["segments"], rows_total)]).all(), info
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_case_fp8_hardware_scaled(seed):
+    """The same sweep for FP8 with UE8M0 scales applied by the tensor core (power-of-two scales from the quantisers)."""
+    rng = random.Random(5000 + seed)
+    masked = rng.random() < 0.4
+    groups = rng.randint(1, 5)
+    n, k = 8 * rng.randint(1, 60), 16 * rng.randint(1, 64)
+    tile = rng.choice([0, 1, 4])
+    host = rng.random() < 0.6
+    counts = [rng.choice([0, rng.randint(1, 400), rng.randint(1, 400), rng.randint(1800, 2600)]) for _ in range(groups)]
+    if sum(counts) == 0:
+        counts[0] = 17
+    ag.set_tile_config(tile)
+    try:
+        if masked:
+            m_max = -(-max(counts) // 128) * 128
+            c = H.make_masked_case("fp8", counts, m_max, n, k, seed=seed, b_on_host=host, use_ue8m0=True)
+            d = torch.full((groups, m_max, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ag.m_grouped_fp8_asym_gemm_nt_masked((c["a"], c["sfa"]), (c["b"], c["sfb"]), d, c["masked_m"], 64, ue8m0_scales=True)
+            rows_total = groups * m_max
+        else:
+            c = H.make_contiguous_case("fp8", counts, n, k, seed=seed, b_on_host=host, use_ue8m0=True)
+            d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (c["b"], c["sfb"]), d, c["offsets"], c["experts"],
+                                                     c["list_size"], ue8m0_scales=True)
+            rows_total = c["m_total"]
+        ag.check_status()
+    finally:
+        ag.set_tile_config(0)
+    d_np = d.float().cpu().numpy().reshape(rows_total, n)
+    info = f"masked={masked} counts={counts} n={n} k={k} tile={tile} host={host}"
+    try:
+        _check("fp8", d_np, c["ref"], c["segments"])
+    except AssertionError as e:
+        raise AssertionError(f"{e} [{info}]")
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], rows_total)]).all(), info
