@@ -19,7 +19,7 @@ from __future__ import annotations
 import ctypes
 import mmap
 from dataclasses import dataclass
-from typing import Callable, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist

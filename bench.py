@@ -244,7 +244,6 @@ def cpu_reference_sample(cfg, w, threads, max_experts):
     operands dequantised to bf16 beforehand (dequantisation is not timed).
     Returns (tflops, description, kind, cores).
     """
-    import numpy as np
     from oracle import oracle as O
     kind, n, k = w["kind"], w["n"], w["k"]
     if kind == "fp4":

@@ -5,9 +5,7 @@ leftovers in the shared scratch array and must not be affected by them.
 Collected last on purpose (file name), so a run that stops at the first failure has already run every other test.
 The test itself allocates its tensors with torch before the calls; the entry point under test allocates nothing.
 """
-import ctypes
 
-import numpy as np
 import pytest
 import torch
 
