@@ -35,7 +35,7 @@ from .layout_api import (  # noqa: F401
     set_tc_util,
     transform_sf_into_required_layout,
 )
-from . import ep, int8_moe, moe_ops, testing, utils  # noqa: F401
+from . import ep, expert_cache, int8_moe, moe_ops, testing, utils  # noqa: F401
 
 __version__ = "0.1.0"
 

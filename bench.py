@@ -179,6 +179,12 @@ def build_masked_fp4(cfg, rank, world, device, seed=0):
 
 
 def run_op(w, a=None, sfa=None, d=None):
+    if w.get("cache") is not None:
+        a_ = w["a"] if a is None else a
+        d_ = w["d"] if d is None else d
+        if w["kind"] == "fp8":
+            return w["cache"].fp8_gemm((a_, w["sfa"] if sfa is None else sfa), d_, w["offsets"], w["experts"])
+        return w["cache"].bf16_gemm(a_, d_, w["offsets"], w["experts"])
     if w["kind"] == "moe":
         return w["layer"].forward(w["x"] if a is None else a, w["ids"], w["w"])
     if w["kind"] == "fp4":
@@ -329,6 +335,8 @@ def main():
     ap.add_argument("--fp8-scales", default="fp32", choices=["fp32", "ue8m0"],
                     help="fp32 (default): arbitrary fp32 block scales applied exactly in the TMEM drain; ue8m0: power-of-two scales "
                          "(use_ue8m0 quantisers) applied by the tensor core, the reference's SM100 numerics")
+    ap.add_argument("--cache-experts", type=int, default=0,
+                    help="keep this many of the most popular experts resident in HBM (HotExpertCache); the rest stream from the host")
     ap.add_argument("--even-shards", action="store_true",
                     help="N > 1: give every rank the same number of experts even when the host links are measured unequal")
     ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
@@ -394,6 +402,18 @@ def main():
     else:
         w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages, expert_range=expert_range,
                            ue8m0=args.fp8_scales == "ue8m0")
+    if args.cache_experts > 0 and cfg["kind"] in ("fp8", "bf16") and not on_dev:
+        from asymgemm_b200.expert_cache import HotExpertCache
+        cache = HotExpertCache(w["b"], w["sfb"], args.cache_experts, device)
+        counts = [0] * w["g"]
+        for e, _, r in w["segs"]:
+            counts[e] = r
+        cache.refresh(counts)
+        torch.cuda.synchronize(device)
+        w["cache"] = cache
+        streamed = sum(1 for e, _, r in w["segs"] if r > 0 and e not in set(cache.cached))
+        w["host_bytes"] = streamed * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]
+        config["hot_expert_cache"] = f"{len(cache.cached)} most popular experts resident in HBM, {streamed} streamed from the host"
     if args.fp8_scales == "ue8m0":
         ag.set_fp8_scale_mode("ue8m0")
         config["fp8_scales"] = "power-of-two (UE8M0), applied by the tensor core"

@@ -375,3 +375,28 @@ def test_fp8_hardware_ue8m0_scaling_masked_and_mode_switch():
     ref = oracle.gemm_fp8(H.np_bits(c2["a"]), floor2(c2["sfa"].cpu().numpy()), H.np_bits(c2["b"]), floor2(c2["sfb"].cpu().numpy()),
                           c2["segments"])
     _check("fp8", d2.float().cpu().numpy(), ref, c2["segments"])
+
+
+@pytest.mark.parametrize("capacity", [0, 2, 5])
+def test_hot_expert_cache_matches_plain_call(capacity):
+    """Cached experts are served from HBM, the rest streamed; together they must give the plain call's result."""
+    from asymgemm_b200.expert_cache import HotExpertCache
+    rows = [300, 40, 0, 900, 129]
+    c = H.make_contiguous_case("fp8", rows, 256, 512, seed=71)
+    cache = HotExpertCache(c["b"], c["sfb"], capacity)
+    assert cache.refresh(rows) == capacity
+    if capacity == 2:
+        assert sorted(cache.cached) == [0, 3]
+        assert cache.refresh([0, 0, 5, 9, 0]) == 1 and sorted(cache.cached) == [2, 3]      # one expert replaced, one kept
+        assert cache.refresh(rows) == 1
+    d = torch.full((c["m_total"], 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    cache.fp8_gemm((c["a"], c["sfa"]), d, c["offsets"], c["experts"])
+    torch.cuda.synchronize()
+    _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
+    cb = H.make_contiguous_case("bf16", rows, 256, 512, seed=72)
+    cache_b = HotExpertCache(cb["b"], None, capacity)
+    cache_b.refresh(rows)
+    db = torch.full((cb["m_total"], 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    cache_b.bf16_gemm(cb["a"], db, cb["offsets"], cb["experts"])
+    torch.cuda.synchronize()
+    _check("bf16", db.float().cpu().numpy(), cb["ref"], cb["segments"])

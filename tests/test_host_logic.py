@@ -159,3 +159,16 @@ def test_proportional_expert_ranges():
     assert [hi - lo for lo, hi in pr([1.0, 100.0], 4)] == [1, 3]
     with pytest.raises(RuntimeError):
         pr([1.0, 1.0, 1.0], 2)
+
+
+def test_hot_expert_cache_table_split():
+    from asymgemm_b200.expert_cache import HotExpertCache
+    c = HotExpertCache.__new__(HotExpertCache)
+    c.slot_of = torch.tensor([-1, 0, -1, 1], dtype=torch.int32)      # experts 1 and 3 are cached in slots 0 and 1
+    offsets = torch.tensor([0, 128, 128, 384, 384, 512, 0, 0], dtype=torch.int32)
+    experts = torch.tensor([3, 0, 1, -1], dtype=torch.int32)
+    (oc, ec), (os_, es) = c.split_tables(offsets, experts)
+    assert oc.tolist() == [0, 128, 0, 0, 384, 512, 0, 0] and ec.tolist() == [1, 0, 0, -1]
+    assert os_.tolist() == [0, 0, 128, 384, 0, 0, 0, 0] and es.tolist() == [0, 0, 0, -1]
+    # every row range lands in exactly one of the two launches
+    assert (oc.view(-1, 2) + os_.view(-1, 2)).reshape(-1).tolist() == offsets.tolist()
