@@ -143,11 +143,13 @@ def test_masked(kind, tile):
     assert np.isnan(d_np[~mask]).all()
 
 
-def test_int8_block_sums_bit_exact():
-    """INT8: the int32 sums per 128-wide K block must equal the oracle's exactly; fp32 output within tolerance."""
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_int8_block_sums_bit_exact(b_on_host):
+    """INT8: the int32 sums per 128-wide K block must equal the oracle's exactly; fp32 output within tolerance.
+    Host-resident B runs the TMEM-accumulating drain, device-resident B the register-accumulating one."""
     rows = [200, 128, 3, 640]
     n, k = 256, 1024
-    c = H.make_contiguous_case("int8", rows, n, k, seed=5)
+    c = H.make_contiguous_case("int8", rows, n, k, seed=5, b_on_host=b_on_host)
     raw = torch.zeros((k // 128, c["m_total"], n), dtype=torch.int32, device="cuda")
     c["raw"] = raw
     d = torch.zeros((c["m_total"], n), dtype=torch.float32, device="cuda")
