@@ -329,8 +329,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--experts", type=int, default=0, help="shrink the expert count (tokens shrink in proportion); 0 = full size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--weights", default="host", choices=["host", "device"],
-                    help="host (default): B in pinned host memory; device: B resident in HBM (tensor-bound regime)")
+    ap.add_argument("--weights", default="host", choices=["host", "device", "staged"],
+                    help="host (default): B in pinned host memory, read by the kernel itself; device: B resident in HBM (tensor-bound "
+                         "regime); staged: B in pinned host memory, copied chunk by chunk into an HBM double buffer by the copy engine "
+                         "(StagedExpertStream) -- the alternative the in-kernel stream is compared with")
+    ap.add_argument("--stage-chunk", type=int, default=8, help="--weights staged: experts per staged chunk")
     ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
     ap.add_argument("--fp8-scales", default="fp32", choices=["fp32", "ue8m0"],
                     help="fp32 (default): arbitrary fp32 block scales applied exactly in the TMEM drain; ue8m0: power-of-two scales "
@@ -414,6 +417,15 @@ def main():
         streamed = sum(1 for e, _, r in w["segs"] if r > 0 and e not in set(cache.cached))
         w["host_bytes"] = streamed * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]
         config["hot_expert_cache"] = f"{len(cache.cached)} most popular experts resident in HBM, {streamed} streamed from the host"
+    if args.weights == "staged":
+        if cfg["kind"] not in ("fp8", "bf16") or moe:
+            raise SystemExit("--weights staged covers the fp8 and bf16 contiguous workloads")
+        from asymgemm_b200.expert_cache import StagedExpertStream
+        w["cache"] = StagedExpertStream(w["b"], w["sfb"], args.stage_chunk, device)
+        w["host_bytes"] = w["g"] * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]      # every expert is copied, active or not
+        config["staged"] = (f"weights cross the link through the copy engine, {args.stage_chunk} experts per chunk into a double buffer "
+                            f"in HBM ({2 * args.stage_chunk * w['n'] * w['k'] * ELEM_BYTES[cfg['kind']] / 1e6:.0f} MB); the grouped "
+                            "GEMM of a chunk runs from HBM while the next chunk is copied")
     if args.fp8_scales == "ue8m0":
         ag.set_fp8_scale_mode("ue8m0")
         config["fp8_scales"] = "power-of-two (UE8M0), applied by the tensor core"
@@ -591,7 +603,8 @@ def main():
                                               + (sfa_host.numel() * sfa_host.element_size() if sfa_host is not None else 0)),
                     "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
                     "note": "weights are read from pinned host memory inside the kernel in both timings"},
-            "gpu_launches": args.steps * (2 if moe else 1),
+            "gpu_launches": args.steps * (2 if moe else (w["cache"].num_chunks if args.weights == "staged" else
+                                                         (2 if w.get("cache") is not None else 1))),
             "clocks": clocks,
         }
         if on_dev and not moe:
@@ -601,6 +614,11 @@ def main():
                                 "note": "weights resident in HBM: bound by the tensor pipe; peak = MEASURED_PEAKS.json bf16_tflops"
                                         " (x2 for 8-bit operands), of measured"}
             line.pop("host_link", None)
+        if args.weights == "staged":
+            line["roofline"]["note"] = ("weights are moved by cudaMemcpyAsync (copy engine), not by the kernel: achieved is the "
+                                        "weight bytes over the whole step, against the copy-engine rate measured in this run")
+            line["roofline"]["traffic"] = None
+            line["e2e"]["note"] = "weights are copied from pinned host memory by the copy engine inside both timings"
         if moe:
             line["metric"] = "MoE-layer TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)"
             line["config"]["numa_node_of_weights"] = w["numa_node"]

@@ -402,3 +402,27 @@ def test_hot_expert_cache_matches_plain_call(capacity):
     cache_b.bf16_gemm(cb["a"], db, cb["offsets"], cb["experts"])
     torch.cuda.synchronize()
     _check("bf16", db.float().cpu().numpy(), cb["ref"], cb["segments"])
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 5])
+def test_staged_expert_stream_matches_plain_call(chunk):
+    """Weights staged through HBM by the copy engine, chunk by chunk, must give the in-kernel stream's result bit for bit,
+    on two calls in a row (the second call reuses buffers the first call's GEMMs read)."""
+    from asymgemm_b200.expert_cache import StagedExpertStream
+    rows = [300, 40, 0, 900, 129]
+    c = H.make_contiguous_case("fp8", rows, 256, 512, seed=73)
+    plain = torch.full((c["m_total"], 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (c["b"], c["sfb"]), plain, c["offsets"], c["experts"], None)
+    staged = StagedExpertStream(c["b"], c["sfb"], chunk)
+    for _ in range(2):
+        d = torch.full((c["m_total"], 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+        staged.fp8_gemm((c["a"], c["sfa"]), d, c["offsets"], c["experts"])
+        torch.cuda.synchronize()
+        _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
+        for _, r0, r1 in c["segments"]:
+            assert torch.equal(d[r0:r1], plain[r0:r1])
+    cb = H.make_contiguous_case("bf16", rows, 256, 512, seed=74)
+    db = torch.full((cb["m_total"], 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    StagedExpertStream(cb["b"], None, chunk).bf16_gemm(cb["a"], db, cb["offsets"], cb["experts"])
+    torch.cuda.synchronize()
+    _check("bf16", db.float().cpu().numpy(), cb["ref"], cb["segments"])
