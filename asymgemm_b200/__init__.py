@@ -21,6 +21,8 @@ from .api import (  # noqa: F401
     set_split_segments,
     set_tile_config,
     set_use_scratch,
+    set_weight_path,
+    get_weight_path,
     set_wait_limit_ms,
 )
 from .layout_api import (  # noqa: F401

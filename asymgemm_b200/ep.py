@@ -288,7 +288,9 @@ class ExpertParallelMoE:
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
                  expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False):
         """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
-        (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly."""
+        (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly.
+        Whether the kernel reads the pinned weights itself or the copy engine stages them is the operators' setting
+        (`asymgemm_b200.set_weight_path`)."""
         self.dispatcher = EPDispatcher(num_experts, group, expert_ranges)
         self.ue8m0_scales = bool(ue8m0_scales)
         self.hidden, self.inter = hidden, inter

@@ -6,12 +6,6 @@ operators: one grouped GEMM call is split into a device-resident part (cached ex
 others) without touching the host -- both launches see the caller's full segment table, with the segments that belong to
 the other part turned into empty row ranges, which the kernel skips before fetching anything. Every weight byte of a
 cached expert stays off the host link; the streamed launch moves `(active - cached) / active` of the bytes.
-
-`StagedExpertStream` is the copy-engine alternative to reading the weights from inside the kernel: chunks of experts are
-copied into a small double buffer in HBM while the previous chunk is multiplied from there. Reads issued by the SMs (TMA,
-bulk or plain loads alike) top out a few percent below the copy engine's rate on the same link, so for a batch in which
-every expert is active staging is the faster way to move the same bytes; the in-kernel stream remains the default
-because it fetches only the experts that received rows -- something only the device knows -- and needs no HBM buffer.
 """
 from __future__ import annotations
 
@@ -93,71 +87,3 @@ class HotExpertCache:
             api.m_grouped_bf16_asym_gemm_nt_contiguous(a, self.b_dev, d, oc, ec, None)
         api.m_grouped_bf16_asym_gemm_nt_contiguous(a, self.b_host, d, os_, es, None)
 
-
-class StagedExpertStream:
-    """Grouped GEMM with host-resident weights moved by the copy engine: experts [i*chunk, (i+1)*chunk) are copied into
-    one of `buffers` HBM buffers on a copy stream while the GEMM of the previous chunk runs from the other buffer on the
-    caller's stream. Every expert is copied, whether or not it received rows."""
-
-    def __init__(self, b_host: torch.Tensor, sfb: Optional[torch.Tensor], chunk_experts: int = 8, device="cuda", buffers: int = 2):
-        if b_host.dim() != 3 or not b_host.is_pinned():
-            raise RuntimeError("b_host must be a [G, N, K] tensor in pinned host memory")
-        if chunk_experts < 1 or buffers < 2:
-            raise RuntimeError("chunk_experts must be >= 1 and buffers >= 2")
-        self.b_host = b_host
-        self.device = torch.device(device)
-        self.num_experts = int(b_host.shape[0])
-        self.chunk = min(int(chunk_experts), self.num_experts)
-        self.num_chunks = (self.num_experts + self.chunk - 1) // self.chunk
-        self.buffers = [torch.empty((self.chunk,) + tuple(b_host.shape[1:]), dtype=b_host.dtype, device=self.device)
-                        for _ in range(buffers)]
-        self.sfb_full = sfb.to(self.device) if sfb is not None else None
-        # one view per chunk, created once: the operator caches prepared weight scales by tensor identity
-        self.sfb_chunks = [self.sfb_full[i * self.chunk:(i + 1) * self.chunk] for i in range(self.num_chunks)] \
-            if sfb is not None else [None] * self.num_chunks
-        self.copy_stream = torch.cuda.Stream(device=self.device)
-        self.ready = [torch.cuda.Event() for _ in range(buffers)]
-        self.free = [torch.cuda.Event() for _ in range(buffers)]
-
-    def chunk_tables(self, offsets: torch.Tensor, experts: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        """([num_chunks, 2n] offsets, [num_chunks, n] expert ids relative to the chunk): row i keeps the segments whose
-        expert lies in chunk i and empties all others. Pure device arithmetic."""
-        n = experts.numel()
-        valid = experts >= 0
-        e = experts.clamp(min=0)
-        which = torch.div(e, self.chunk, rounding_mode="floor")
-        ids = torch.arange(self.num_chunks, device=experts.device).unsqueeze(1)
-        mine = valid.unsqueeze(0) & (which.unsqueeze(0) == ids)                        # [chunks, n]
-        pairs = offsets[: 2 * n].view(n, 2) if offsets.numel() >= 2 * n else torch.cat(
-            [offsets, offsets.new_zeros(2 * n - offsets.numel())]).view(n, 2)
-        off = torch.where(mine.unsqueeze(2), pairs.unsqueeze(0), torch.zeros_like(pairs).unsqueeze(0)).reshape(self.num_chunks, 2 * n)
-        rel = (e - which * self.chunk).to(torch.int32)
-        keep_end = torch.where(valid, torch.zeros_like(experts), experts).to(torch.int32)   # end markers (-1) stay in place
-        exp = torch.where(mine, rel.unsqueeze(0), keep_end.unsqueeze(0))
-        return off.contiguous(), exp.contiguous()
-
-    def _run(self, gemm, a, d, offsets, experts, with_scales: bool, **kw) -> None:
-        main = torch.cuda.current_stream(self.device)
-        off, exp = self.chunk_tables(offsets, experts)
-        start = torch.cuda.Event()
-        start.record(main)
-        for i in range(self.num_chunks):
-            j = i % len(self.buffers)
-            lo, hi = i * self.chunk, min((i + 1) * self.chunk, self.num_experts)
-            with torch.cuda.stream(self.copy_stream):
-                # buffer j is free once the GEMM that last read it is done (first round: once the caller's earlier work is)
-                self.copy_stream.wait_event(self.free[j] if i >= len(self.buffers) else start)
-                self.buffers[j][: hi - lo].copy_(self.b_host[lo:hi], non_blocking=True)
-                self.ready[j].record(self.copy_stream)
-            main.wait_event(self.ready[j])
-            b = self.buffers[j][: hi - lo]
-            gemm(a, (b, self.sfb_chunks[i]) if with_scales else b, d, off[i], exp[i], None, **kw)
-            self.free[j].record(main)
-
-    def fp8_gemm(self, a, d, offsets, experts, **kw) -> None:
-        """`m_grouped_fp8_asym_gemm_nt_contiguous` with every chunk of experts staged through HBM by the copy engine."""
-        self._run(api.m_grouped_fp8_asym_gemm_nt_contiguous, a, d, offsets, experts, True, **kw)
-
-    def bf16_gemm(self, a, d, offsets, experts) -> None:
-        """`m_grouped_bf16_asym_gemm_nt_contiguous` with every chunk of experts staged through HBM by the copy engine."""
-        self._run(api.m_grouped_bf16_asym_gemm_nt_contiguous, a, d, offsets, experts, False)

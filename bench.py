@@ -203,6 +203,22 @@ def run_op(w, a=None, sfa=None, d=None):
         ag.m_grouped_bf16_asym_gemm_nt_contiguous(a, w["b"], d, w["offsets"], w["experts"], None)
 
 
+def gemm_launches_per_step(w, args):
+    """Grouped-GEMM kernel launches of this library in one step (helper kernels of the MoE layer not counted)."""
+    def chunks(g, group_bytes):
+        if args.weights != "staged":
+            return 1
+        per = max(1, min(g, (args.stage_mb << 20) // int(group_bytes)))
+        return (g + per - 1) // per
+    if w["kind"] == "moe":
+        layer = w["layer"]
+        g = layer.w13[0].shape[0]
+        return chunks(g, layer.w13[0][0].numel()) + chunks(g, layer.w2[0][0].numel())
+    if w.get("cache") is not None:
+        return 2
+    return chunks(w["g"], w["b"][0].numel() * w["b"].element_size())
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -332,8 +348,8 @@ def main():
     ap.add_argument("--weights", default="host", choices=["host", "device", "staged"],
                     help="host (default): B in pinned host memory, read by the kernel itself; device: B resident in HBM (tensor-bound "
                          "regime); staged: B in pinned host memory, copied chunk by chunk into an HBM double buffer by the copy engine "
-                         "(StagedExpertStream) -- the alternative the in-kernel stream is compared with")
-    ap.add_argument("--stage-chunk", type=int, default=8, help="--weights staged: experts per staged chunk")
+                         "(set_weight_path) -- the alternative the in-kernel stream is compared with")
+    ap.add_argument("--stage-mb", type=int, default=128, help="--weights staged: size of one staged chunk of whole experts, MiB")
     ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
     ap.add_argument("--fp8-scales", default="fp32", choices=["fp32", "ue8m0"],
                     help="fp32 (default): arbitrary fp32 block scales applied exactly in the TMEM drain; ue8m0: power-of-two scales "
@@ -418,14 +434,10 @@ def main():
         w["host_bytes"] = streamed * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]
         config["hot_expert_cache"] = f"{len(cache.cached)} most popular experts resident in HBM, {streamed} streamed from the host"
     if args.weights == "staged":
-        if cfg["kind"] not in ("fp8", "bf16") or moe:
-            raise SystemExit("--weights staged covers the fp8 and bf16 contiguous workloads")
-        from asymgemm_b200.expert_cache import StagedExpertStream
-        w["cache"] = StagedExpertStream(w["b"], w["sfb"], args.stage_chunk, device)
-        w["host_bytes"] = w["g"] * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]      # every expert is copied, active or not
-        config["staged"] = (f"weights cross the link through the copy engine, {args.stage_chunk} experts per chunk into a double buffer "
-                            f"in HBM ({2 * args.stage_chunk * w['n'] * w['k'] * ELEM_BYTES[cfg['kind']] / 1e6:.0f} MB); the grouped "
-                            "GEMM of a chunk runs from HBM while the next chunk is copied")
+        ag.set_weight_path("staged", chunk_bytes=args.stage_mb << 20)
+        config["staged"] = (f"weights cross the link through the copy engine, about {args.stage_mb} MiB of whole experts per chunk "
+                            "into a double buffer in HBM; the grouped GEMM of a chunk runs from HBM while the next chunk is copied; every expert "
+                            "is copied, the reported GB/s count the active experts' bytes only")
     if args.fp8_scales == "ue8m0":
         ag.set_fp8_scale_mode("ue8m0")
         config["fp8_scales"] = "power-of-two (UE8M0), applied by the tensor core"
@@ -603,8 +615,7 @@ def main():
                                               + (sfa_host.numel() * sfa_host.element_size() if sfa_host is not None else 0)),
                     "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
                     "note": "weights are read from pinned host memory inside the kernel in both timings"},
-            "gpu_launches": args.steps * (2 if moe else (w["cache"].num_chunks if args.weights == "staged" else
-                                                         (2 if w.get("cache") is not None else 1))),
+            "gpu_launches": args.steps * gemm_launches_per_step(w, args),
             "clocks": clocks,
         }
         if on_dev and not moe:
