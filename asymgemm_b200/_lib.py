@@ -54,6 +54,8 @@ class GemmDesc(Structure):
         ("alpha", c_float),
         ("tile_config", c_int32),
         ("no_split", c_int32),
+        ("stage", c_void_p),
+        ("stage_bytes", c_uint64),
     ]
 
 

@@ -81,7 +81,8 @@ def set_weight_path(path: str, chunk_bytes: Optional[int] = None) -> None:
 
     "stream" (default): the GEMM kernel reads pinned memory itself and fetches only the experts that received rows.
     "staged": the copy engine moves every expert, about `chunk_bytes` (default 128 MiB) of whole experts at a time, into
-    a double buffer in HBM while the grouped GEMM of the previous chunk runs from there; same results, a few percent
+    a double buffer in HBM while the grouped GEMM of the previous chunk runs from there (`stage` of the C descriptor; this
+    module owns one such buffer per device); same results, a few percent
     more of the link, for calls in which (nearly) all experts are active. The reference's unified runtime stages its
     streamed partition the same way, by default (`_StageRing`, asym_gemm/unified_moe/runtime.py:110-200; its in-kernel
     reads reach 21.5 of the copy engine's 50 GB/s); here the in-kernel stream reaches 0.92 of the copy engine's rate, so
@@ -216,98 +217,37 @@ def _common_checks(a, b, d, masked: bool, k_div: int = 1):
     return int(g), int(m), int(n), int(k * k_div)
 
 
-class _Stager:
-    """Double buffer in HBM plus the copy stream and events that hand its halves back and forth; one per (device, stream)."""
-
-    def __init__(self, device: torch.device):
-        self.buffers = [None, None]
-        self.copy_stream = torch.cuda.Stream(device=device)
-        self.ready = [torch.cuda.Event(), torch.cuda.Event()]
-        self.free = [torch.cuda.Event(), torch.cuda.Event()]
-
-    def ensure(self, nbytes: int, device: torch.device) -> None:
-        for j in range(2):
-            if self.buffers[j] is None or self.buffers[j].numel() < nbytes:
-                # the old buffer goes back to the allocator of the launching stream, whose later work is ordered after the
-                # GEMMs that read it; copies into it ended before those GEMMs started
-                self.buffers[j] = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
-
-    def buffer_ptr(self, j: int) -> int:
-        p = self.buffers[j].data_ptr()
-        return p + (-p) % 1024
-
-
-def _per_group_bytes(t: Optional[torch.Tensor], g: int) -> int:
-    return 0 if t is None else t.numel() * t.element_size() // g
-
-
-def _launch_staged(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m,
-                   m: int, n: int, k: int, g: int, alpha: float) -> bool:
-    """The launch as a series of launches over chunks of experts whose weights the copy engine brings into HBM (see
-    set_weight_path). Returns False, having done nothing, where the call cannot be cut at expert boundaries."""
-    from .utils.layout import chunk_segment_tables
-    masked = layout == _lib.LAYOUT_MASKED
-    block_scaled_rows = kind in (_lib.KIND_FP8_UE8M0, _lib.KIND_NVFP4)
-    if masked and block_scaled_rows and m % 128 != 0:
-        return False           # the blocked scale layout of A packs 128 rows: groups would share a block
-    dev = a.device
+def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor:
+    """Double buffer in HBM for the staged weight path, one per device, sized for two chunks of whole experts of `b`.
+    The library orders the copies into it after the GEMMs of earlier calls that read it, on whichever stream they ran."""
     group_bytes = b.numel() * b.element_size() // g
     chunk = max(1, min(g, _state["stage_bytes"] // max(1, group_bytes)))
-    num_chunks = (g + chunk - 1) // chunk
-    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-    stager = _stager_cache.get(key)
-    if stager is None:
-        if len(_stager_cache) >= 8:
-            _stager_cache.clear()
-        stager = _stager_cache[key] = _Stager(dev)
-    stager.ensure(chunk * group_bytes, dev)
-    main = torch.cuda.current_stream(dev)
-    b_bytes = b.view(torch.uint8).view(g, group_bytes) if b.dtype != torch.uint8 else b.view(g, group_bytes)
-    sfb_group = _per_group_bytes(sfb, g)
-    if masked:
-        a_group, d_group, sfa_group = _per_group_bytes(a, g), _per_group_bytes(d, g), _per_group_bytes(sfa, g)
-    else:
-        off_tab, exp_tab = chunk_segment_tables(offsets, experts, chunk, num_chunks)
-    for i in range(num_chunks):
-        j = i & 1
-        lo, hi = i * chunk, min((i + 1) * chunk, g)
-        with torch.cuda.stream(stager.copy_stream):
-            stager.copy_stream.wait_event(stager.free[j])      # the GEMM that last read this half is done
-            dst = stager.buffers[j]
-            pad = (-dst.data_ptr()) % 1024
-            dst[pad:pad + (hi - lo) * group_bytes].view(hi - lo, group_bytes).copy_(b_bytes[lo:hi], non_blocking=True)
-            stager.ready[j].record(stager.copy_stream)
-        main.wait_event(stager.ready[j])
-        ptrs = dict(b=stager.buffer_ptr(j), sfb=(sfb.data_ptr() + lo * sfb_group) if sfb is not None else None)
-        if masked:
-            ptrs.update(a=a.data_ptr() + lo * a_group, d=d.data_ptr() + lo * d_group,
-                        sfa=(sfa.data_ptr() + lo * sfa_group) if sfa is not None else None,
-                        masked_m=masked_m.data_ptr() + lo * 4, offsets=None, experts=None)
-        else:
-            ptrs.update(a=a.data_ptr(), d=d.data_ptr(), sfa=sfa.data_ptr() if sfa is not None else None, masked_m=None,
-                        offsets=off_tab[i].data_ptr(), experts=exp_tab[i].data_ptr())
-        _launch_desc(kind, fn_name, dev, layout, d.dtype, ptrs, max_segments, m, n, k, hi - lo, None, alpha)
-        stager.free[j].record(main)
-    return True
+    need = 2 * (chunk * group_bytes + 1023) // 1024 * 1024 + 2048
+    t = _stager_cache.get(device.index)
+    if t is None or t.numel() < need + 1024:
+        # a buffer that is replaced goes back to the allocator only after the GEMMs that read it: wait for them here
+        if t is not None:
+            torch.cuda.synchronize(device)
+        t = torch.empty(need + 1024, dtype=torch.uint8, device=device)
+        _stager_cache[device.index] = t
+    off = (-t.data_ptr()) % 1024
+    return t[off:off + need]
 
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
             masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0) -> None:
-    if _state["weight_path"] == "staged" and not b.is_cuda and raw_dump is None and d.is_cuda:
-        if _launch_staged(kind, fn_name, layout=layout, a=a, sfa=sfa, b=b, sfb=sfb, d=d, offsets=offsets, experts=experts,
-                          max_segments=max_segments, masked_m=masked_m, m=m, n=n, k=k, g=g, alpha=alpha):
-            return
+    stage = _stage_buffer(b, g, a.device) if _state["weight_path"] == "staged" and not b.is_cuda and raw_dump is None else None
     ptrs = dict(a=a.data_ptr(), sfa=sfa.data_ptr() if sfa is not None else None, b=b.data_ptr(),
                 sfb=sfb.data_ptr() if sfb is not None else None, d=d.data_ptr(),
                 offsets=offsets.data_ptr() if offsets is not None else None,
                 experts=experts.data_ptr() if experts is not None else None,
                 masked_m=masked_m.data_ptr() if masked_m is not None else None)
     _launch_desc(kind, fn_name, a.device, layout, d.dtype, ptrs, max_segments, m, n, k, g,
-                 raw_dump.data_ptr() if raw_dump is not None else None, alpha)
+                 raw_dump.data_ptr() if raw_dump is not None else None, alpha, stage)
 
 
 def _launch_desc(kind: int, fn_name: str, dev: torch.device, layout: int, d_dtype, ptrs: dict, max_segments: int,
-                 m: int, n: int, k: int, g: int, raw_dump: Optional[int], alpha: float) -> None:
+                 m: int, n: int, k: int, g: int, raw_dump: Optional[int], alpha: float, stage: Optional[torch.Tensor]) -> None:
     lib = _lib.load()
     with torch.cuda.device(dev):
         desc = GemmDesc()
@@ -333,6 +273,9 @@ def _launch_desc(kind: int, fn_name: str, dev: torch.device, layout: int, d_dtyp
         desc.timeout_ms = _state["timeout_ms"]
         desc.raw_dump = raw_dump
         desc.alpha = alpha
+        if stage is not None:
+            desc.stage = stage.data_ptr()
+            desc.stage_bytes = stage.numel()
         desc.tile_config = _state["tile_config"]
         desc.no_split = _state["no_split"]
         _lib.check(getattr(lib, fn_name)(desc))

@@ -123,7 +123,11 @@ uint64_t k_bytes_of(int kind, int64_t k) {
   }
 }
 
-int run(int kind, const ag_gemm_desc_t* g) {
+int run_staged(int kind, const ag_gemm_desc_t* g, uint64_t expert_bytes);
+
+// One launch. `win_n` >= 0: `g->b` holds only the experts [win_lo, win_lo + win_n) (a staged chunk) and the launch
+// skips the segments of all others; `g->num_groups` stays the size of the whole weight tensor.
+int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   AG_REQUIRE(g != nullptr, "desc is NULL");
   AG_REQUIRE(g->layout == AG_LAYOUT_CONTIGUOUS || g->layout == AG_LAYOUT_MASKED, "unknown layout %d", g->layout);
   AG_REQUIRE(g->d_dtype == AG_D_BF16 || g->d_dtype == AG_D_FP32, "unknown d_dtype %d", g->d_dtype);
@@ -157,6 +161,9 @@ int run(int kind, const ag_gemm_desc_t* g) {
     return fail(AG_E_NOT_MAPPED, "b (%p) is neither device memory nor pinned/registered host memory: pin it "
                 "(cudaHostAlloc / cudaHostRegister / torch pin_memory) before the call", g->b);
   AG_REQUIRE((reinterpret_cast<uintptr_t>(b_dev) & 15) == 0, "b must be 16-byte aligned");
+  if (g->stage != nullptr && win_n < 0 && res == RES_HOST_MAPPED && !(kind == 2 && g->raw_dump != nullptr))
+    return run_staged(kind, g, static_cast<uint64_t>(g->n) * kbytes);
+  const int b_groups = win_n >= 0 ? win_n : g->num_groups;
 
   agb::GemmParams p;
   std::memset(&p, 0, sizeof(p));
@@ -180,6 +187,8 @@ int run(int kind, const ag_gemm_desc_t* g) {
   p.max_segments = masked ? g->num_groups : g->max_segments;
   p.m_max = masked ? static_cast<int>(g->m) : 0;
   p.num_groups = g->num_groups;
+  p.expert_lo = win_n >= 0 ? win_lo : 0;
+  p.expert_n = b_groups;
   p.n = static_cast<int>(g->n);
   int tile = g->tile_config > 0 ? g->tile_config - 1
                                 : (res == RES_HOST_MAPPED ? agb::kTileHost
@@ -220,7 +229,7 @@ int run(int kind, const ag_gemm_desc_t* g) {
 
   CUtensorMap ma, mb, ms;
   if (int rc = encode_bytes_2d(&ma, g->a, kbytes, static_cast<uint64_t>(rows_total), kbytes, 128, "a")) return rc;
-  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * g->num_groups, kbytes, bn, "b")) return rc;
+  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * b_groups, kbytes, bn, "b")) return rc;
   if (p.use_scratch) {
     if (int rc = encode_bytes_2d(&ms, g->scratch, kpad, static_cast<uint64_t>(grid) * bn, kpad, bn, "scratch")) return rc;
   } else {
@@ -230,6 +239,59 @@ int run(int kind, const ag_gemm_desc_t* g) {
   cudaStream_t stream = static_cast<cudaStream_t>(g->stream);
   cudaError_t e = agb::launch_mgrouped(kind, tile, grid, stream, ma, mb, ms, p);
   if (e != cudaSuccess) return fail(AG_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return AG_OK;
+}
+
+// Copy stream and hand-over events of the staged weight path, one set per device, created on first use and kept for
+// the life of the process. `free_[j]` is recorded after the GEMM that read half j, `ready[j]` after the copy into it.
+struct StageState {
+  cudaStream_t copy = nullptr;
+  cudaEvent_t ready[2] = {nullptr, nullptr};
+  cudaEvent_t free_[2] = {nullptr, nullptr};
+};
+std::mutex g_stage_mu;
+StageState g_stage[64];
+
+// The grouped GEMM as a series of launches over chunks of whole experts that the copy engine brings into `g->stage`.
+// The lock is held for the whole series: the events of one device then always belong to one call at a time, and the
+// copies of a call wait for the GEMMs of the previous call that read the same half.
+int run_staged(int kind, const ag_gemm_desc_t* g, uint64_t expert_bytes) {
+  AG_REQUIRE((reinterpret_cast<uintptr_t>(g->stage) & 1023) == 0, "stage must be 1024-byte aligned");
+  const uint64_t half = (g->stage_bytes / 2) & ~static_cast<uint64_t>(1023);
+  AG_REQUIRE(half >= expert_bytes, "stage_bytes (%llu) must hold two experts of %llu bytes each",
+             static_cast<unsigned long long>(g->stage_bytes), static_cast<unsigned long long>(expert_bytes));
+  const void* stage_alias = nullptr;
+  AG_REQUIRE(classify(g->stage, &stage_alias) == RES_DEVICE, "stage must be device memory");
+  int dev = 0;
+  AG_CUDA(cudaGetDevice(&dev));
+  AG_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  StageState& st = g_stage[dev];
+  if (st.copy == nullptr) {
+    AG_CUDA(cudaStreamCreateWithFlags(&st.copy, cudaStreamNonBlocking));
+    for (int j = 0; j < 2; ++j) {
+      AG_CUDA(cudaEventCreateWithFlags(&st.ready[j], cudaEventDisableTiming));
+      AG_CUDA(cudaEventCreateWithFlags(&st.free_[j], cudaEventDisableTiming));
+    }
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(g->stream);
+  const int chunk = static_cast<int>(half / expert_bytes < static_cast<uint64_t>(g->num_groups) ? half / expert_bytes : g->num_groups);
+  ag_gemm_desc_t c = *g;
+  c.stage = nullptr;
+  for (int lo = 0, i = 0; lo < g->num_groups; lo += chunk, ++i) {
+    const int j = i & 1;
+    const int cnt = g->num_groups - lo < chunk ? g->num_groups - lo : chunk;
+    char* dst = static_cast<char*>(g->stage) + static_cast<uint64_t>(j) * half;
+    AG_CUDA(cudaStreamWaitEvent(st.copy, st.free_[j], 0));   // an event never recorded yet does not block
+    AG_CUDA(cudaMemcpyAsync(dst, static_cast<const char*>(g->b) + static_cast<uint64_t>(lo) * expert_bytes,
+                            static_cast<uint64_t>(cnt) * expert_bytes, cudaMemcpyDefault, st.copy));
+    AG_CUDA(cudaEventRecord(st.ready[j], st.copy));
+    AG_CUDA(cudaStreamWaitEvent(stream, st.ready[j], 0));
+    c.b = dst;
+    const int rc = run(kind, &c, lo, cnt);
+    AG_CUDA(cudaEventRecord(st.free_[j], stream));   // also after a failed launch: the half is not in use then
+    if (rc != AG_OK) return rc;
+  }
   return AG_OK;
 }
 

@@ -77,6 +77,8 @@ struct GemmParams {
   int use_scratch;         // 1 = replay long segments from the scratch copy, 0 = re-read B from its source
   int b_streaming;         // 1 = B is host memory: mark its lines evict-first in L2
   int split_rows;          // > 0: split segments into chunks of this many rows (one accumulator chunk) per item
+  int expert_lo;           // this launch serves the experts [expert_lo, expert_lo + expert_n) only (a staged chunk of the
+  int expert_n;            // weights): segments of other experts are skipped, and B holds just these experts' rows
   float alpha;             // NVFP4 global scale (product of the two tensor-level scales), 1.0 otherwise
 };
 
@@ -95,6 +97,7 @@ __device__ __forceinline__ int read_segment(const GemmParams& p, int seg, int& e
     row0 = seg * p.m_max;
     const int r = __ldg(p.masked_m + seg);
     rows = r < 0 ? 0 : (r > p.m_max ? p.m_max : r);
+    if (static_cast<unsigned>(seg - p.expert_lo) >= static_cast<unsigned>(p.expert_n)) rows = 0;  // another launch's expert
   } else {
     const int e = __ldg(p.experts + seg);
     if (e < 0) return 0;
@@ -107,6 +110,8 @@ __device__ __forceinline__ int read_segment(const GemmParams& p, int seg, int& e
     if (e >= p.num_groups) {  // would read outside B: flag it and skip
       atomicCAS(p.status, 0, ST_BAD_EXPERT | (static_cast<int>(blockIdx.x) << 8));
       rows = 0;
+    } else if (static_cast<unsigned>(e - p.expert_lo) >= static_cast<unsigned>(p.expert_n)) {
+      rows = 0;  // another launch's expert
     }
   }
   return 1;
@@ -380,7 +385,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mtiles = (it.rows + BM - 1) / BM;
         const int chunks = (mtiles + CHUNK_TILES - 1) / CHUNK_TILES;
         const bool spill = p.use_scratch && chunks > 1;
-        const int b_row = it.expert * p.n + it.nt * BN;
+        const int b_row = (it.expert - p.expert_lo) * p.n + it.nt * BN;
         const int s_row = static_cast<int>(blockIdx.x) * BN;
         if (spill) {
           // Loads of the previous item may still be reading this CTA's scratch rows: let them land first.

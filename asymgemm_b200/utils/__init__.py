@@ -8,5 +8,4 @@ from .math import (  # noqa: F401
     per_token_cast_to_int8,
     per_token_cast_to_nvfp4_e4m3,
 )
-from .layout import (build_contiguous_layout, chunk_segment_tables, get_mk_alignment_for_contiguous_layout,  # noqa: F401
-                     get_tma_aligned_size)
+from .layout import build_contiguous_layout, get_mk_alignment_for_contiguous_layout, get_tma_aligned_size  # noqa: F401

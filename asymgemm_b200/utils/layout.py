@@ -41,24 +41,3 @@ def build_contiguous_layout(rows_per_expert: Sequence[int], device="cuda", align
     return (torch.tensor(offsets, dtype=torch.int32, device=device),
             torch.tensor(experts, dtype=torch.int32, device=device), len(experts), start, segs)
 
-
-def chunk_segment_tables(offsets: torch.Tensor, experts: torch.Tensor, chunk: int, num_chunks: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-chunk segment tables of the contiguous layout, for running one grouped GEMM as `num_chunks` launches that each
-    see only the experts [i*chunk, (i+1)*chunk).
-
-    Returns (int32 [num_chunks, 2n] offsets, int32 [num_chunks, n] expert ids relative to the chunk): row i keeps the
-    segments whose expert lies in chunk i and turns all others into empty row ranges (expert id 0), the -1 terminator
-    stays where it is. Pure tensor arithmetic on the device of the inputs -- no host synchronisation."""
-    n = experts.numel()
-    valid = experts >= 0
-    e = experts.clamp(min=0)
-    which = torch.div(e, chunk, rounding_mode="floor")
-    ids = torch.arange(num_chunks, device=experts.device).unsqueeze(1)
-    mine = valid.unsqueeze(0) & (which.unsqueeze(0) == ids)                        # [chunks, n]
-    pairs = offsets[: 2 * n].view(n, 2) if offsets.numel() >= 2 * n else torch.cat(
-        [offsets, offsets.new_zeros(2 * n - offsets.numel())]).view(n, 2)
-    off = torch.where(mine.unsqueeze(2), pairs.unsqueeze(0), torch.zeros_like(pairs).unsqueeze(0)).reshape(num_chunks, 2 * n)
-    rel = (e - which * chunk).to(torch.int32)
-    keep_end = torch.where(valid, torch.zeros_like(experts), experts).to(torch.int32)
-    exp = torch.where(mine, rel.unsqueeze(0), keep_end.unsqueeze(0))
-    return off.to(torch.int32).contiguous(), exp.contiguous()

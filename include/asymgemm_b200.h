@@ -80,6 +80,16 @@ typedef struct ag_gemm_desc {
                           (fp8 / int8 with device-resident b) */
   int32_t no_split;    /* device-resident b only: 1 = keep one item per (segment, n-tile) instead of splitting long segments into
                           accumulator-sized row chunks across CTAs (tests / tuning); ignored for host-resident b */
+
+  /* Optional copy-engine staging of host-resident b (ignored when b is device memory or raw_dump is set). With a
+     non-NULL `stage`, the call does not read b from inside the kernel: it copies as many whole experts as fit in
+     one half of the buffer (cudaMemcpyAsync on a stream of the library's own), runs the grouped GEMM over those experts
+     from the buffer while the next ones are copied into the other half, and so on; same results, every expert of b
+     crosses the link whether or not it received rows. The reference stages its streamed weights the same way
+     (asym_gemm/unified_moe/runtime.py:110-200). The buffer belongs to the library from the first call that names it
+     until the last such call has finished on the GPU; such a call cannot be captured into a CUDA graph. */
+  void* stage;          /* device, 1024-byte aligned; NULL = the kernel reads b itself (default) */
+  uint64_t stage_bytes; /* at least 2 * N * K bytes of one expert (+ alignment); half of it holds one chunk */
 } ag_gemm_desc_t;
 
 /* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked

@@ -172,17 +172,3 @@ def test_hot_expert_cache_table_split():
     assert os_.tolist() == [0, 0, 128, 384, 0, 0, 0, 0] and es.tolist() == [0, 0, 0, -1]
     # every row range lands in exactly one of the two launches
     assert (oc.view(-1, 2) + os_.view(-1, 2)).reshape(-1).tolist() == offsets.tolist()
-
-
-def test_chunk_segment_tables():
-    from asymgemm_b200.utils import chunk_segment_tables
-    offsets = torch.tensor([0, 128, 128, 384, 384, 512, 512, 512, 0, 0], dtype=torch.int32)
-    experts = torch.tensor([3, 0, 4, 1, -1], dtype=torch.int32)
-    off, exp = chunk_segment_tables(offsets, experts, 2, 3)                # chunks {0,1}, {2,3}, {4}
-    assert off.dtype == torch.int32 and exp.dtype == torch.int32
-    assert off.tolist() == [[0, 0, 128, 384, 0, 0, 512, 512, 0, 0],
-                            [0, 128, 0, 0, 0, 0, 0, 0, 0, 0],
-                            [0, 0, 0, 0, 384, 512, 0, 0, 0, 0]]
-    assert exp.tolist() == [[0, 0, 0, 1, -1], [1, 0, 0, 0, -1], [0, 0, 0, 0, -1]]
-    # every row range lands in exactly one chunk's launch
-    assert off.sum(dim=0).tolist() == offsets.tolist()
