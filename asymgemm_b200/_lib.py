@@ -9,6 +9,7 @@ from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int32, c_i
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libasymgemm_b200.so"
+TORCH_OPS_PATH = LIB_PATH.with_name("libasymgemm_b200_torch.so")
 
 AG_OK = 0
 AG_E_INVALID = -1
@@ -155,6 +156,25 @@ def load() -> ctypes.CDLL:
     lib.ag_version.restype = c_char_p
     _lib = lib
     return lib
+
+
+_torch_ops = None
+
+
+def torch_ops():
+    """`torch.ops.asymgemm_b200` (csrc/torch_ops.cpp, built beside the C library); raises if it has not been built."""
+    global _torch_ops
+    if _torch_ops is None:
+        import torch
+        load()                      # the extension links against the C library: load that first, from the same folder
+        if not TORCH_OPS_PATH.exists():
+            raise RuntimeError(
+                f"{TORCH_OPS_PATH} is missing: build it with `python -m asymgemm_b200.build`. "
+                "asymgemm_b200 has no CPU or PyTorch fallback."
+            )
+        torch.ops.load_library(str(TORCH_OPS_PATH))
+        _torch_ops = torch.ops.asymgemm_b200
+    return _torch_ops
 
 
 def last_error() -> str:

@@ -21,7 +21,6 @@ from typing import Optional, Tuple, Union
 import torch
 
 from . import _lib
-from ._lib import GemmDesc
 
 _MK_ALIGNMENT = 128
 _state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0, "fp8_ue8m0": False,
@@ -236,49 +235,14 @@ def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
             masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0) -> None:
-    stage = _stage_buffer(b, g, a.device) if _state["weight_path"] == "staged" and not b.is_cuda and raw_dump is None else None
-    ptrs = dict(a=a.data_ptr(), sfa=sfa.data_ptr() if sfa is not None else None, b=b.data_ptr(),
-                sfb=sfb.data_ptr() if sfb is not None else None, d=d.data_ptr(),
-                offsets=offsets.data_ptr() if offsets is not None else None,
-                experts=experts.data_ptr() if experts is not None else None,
-                masked_m=masked_m.data_ptr() if masked_m is not None else None)
-    _launch_desc(kind, fn_name, a.device, layout, d.dtype, ptrs, max_segments, m, n, k, g,
-                 raw_dump.data_ptr() if raw_dump is not None else None, alpha, stage)
-
-
-def _launch_desc(kind: int, fn_name: str, dev: torch.device, layout: int, d_dtype, ptrs: dict, max_segments: int,
-                 m: int, n: int, k: int, g: int, raw_dump: Optional[int], alpha: float, stage: Optional[torch.Tensor]) -> None:
-    lib = _lib.load()
+    """Every operator ends here: one call of the torch extension's op, which fills the C descriptor from the tensors and
+    launches on the current stream of a's device (csrc/torch_ops.cpp)."""
+    dev = a.device
+    stage = _stage_buffer(b, g, dev) if _state["weight_path"] == "staged" and not b.is_cuda and raw_dump is None else None
+    op = _lib.torch_ops().m_grouped_gemm_nt
     with torch.cuda.device(dev):
-        desc = GemmDesc()
-        desc.layout = layout
-        desc.d_dtype = _lib.D_FP32 if d_dtype == torch.float32 else _lib.D_BF16
-        desc.a = ptrs["a"]
-        desc.sfa = ptrs["sfa"]
-        desc.b = ptrs["b"]
-        desc.sfb = ptrs["sfb"]
-        desc.d = ptrs["d"]
-        desc.offsets = ptrs["offsets"]
-        desc.experts = ptrs["experts"]
-        desc.max_segments = max_segments
-        desc.masked_m = ptrs["masked_m"]
-        desc.m, desc.n, desc.k, desc.num_groups = m, n, k, g
-        scratch = _scratch(kind, n, k, dev)
-        if scratch is not None:
-            desc.scratch = scratch.data_ptr()
-            desc.scratch_bytes = scratch.numel()
-        desc.status = _status_word(dev).data_ptr()
-        desc.stream = torch.cuda.current_stream(dev).cuda_stream
-        desc.num_sms = 0
-        desc.timeout_ms = _state["timeout_ms"]
-        desc.raw_dump = raw_dump
-        desc.alpha = alpha
-        if stage is not None:
-            desc.stage = stage.data_ptr()
-            desc.stage_bytes = stage.numel()
-        desc.tile_config = _state["tile_config"]
-        desc.no_split = _state["no_split"]
-        _lib.check(getattr(lib, fn_name)(desc))
+        op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
+           _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage)
 
 
 def _check_index_tensors(offsets, experts, g):

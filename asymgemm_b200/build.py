@@ -17,6 +17,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libasymgemm_b200.so"
+TORCH_OPS_PATH = LIB_DIR / "libasymgemm_b200_torch.so"
+TORCH_OPS_SRC = CSRC / "torch_ops.cpp"
 OBJ_DIR = CSRC / "build"
 
 SOURCES = ["capi.cu", "inst_bf16.cu", "inst_fp8.cu", "inst_int8.cu", "inst_fp4.cu", "inst_fp8_ue8m0.cu", "sf_layout.cu", "no_alloc.cu", "selftest.cu", "moe_glue.cu", "hostlink.cu"]
@@ -49,8 +51,42 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > t for d in _deps() if d.exists())
 
 
+def build_torch_ops(force: bool = False) -> Path:
+    """Compile the thin PyTorch extension (csrc/torch_ops.cpp: tensors -> C descriptor -> C ABI) with the host compiler
+    against this interpreter's torch headers, linked to the C library that sits in the same folder."""
+    header = PKG_DIR.parent / "include" / "asymgemm_b200.h"
+    if not force and TORCH_OPS_PATH.exists() and all(
+            TORCH_OPS_PATH.stat().st_mtime >= p.stat().st_mtime for p in (TORCH_OPS_SRC, header, LIB_PATH)):
+        return TORCH_OPS_PATH
+    import logging
+    import torch
+    logging.getLogger("torch.utils.cpp_extension").setLevel(logging.ERROR)
+    from torch.utils import cpp_extension as ce
+    cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
+    tmp = TORCH_OPS_PATH.with_suffix(".so.tmp")
+    cmd = [os.environ.get("CXX") or shutil.which("g++") or "g++", "-O2", "-std=c++17", "-fPIC", "-shared", str(TORCH_OPS_SRC),
+           "-o", str(tmp), f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in ce.include_paths() + [str(Path(cuda_home) / "include")]:
+        cmd += ["-isystem", inc]
+    for lib in ce.library_paths():
+        cmd += ["-L", lib]
+    cmd += ["-L", str(LIB_DIR), "-lasymgemm_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the torch extension failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, TORCH_OPS_PATH)
+    return TORCH_OPS_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every CUDA source for sm_100a and link the shared library. Returns its path."""
+    """Compile every CUDA source for sm_100a, link the shared library, then build the torch extension over it.
+    Returns the path of the C library."""
+    _build_c_library(force, verbose)
+    build_torch_ops(force)
+    return LIB_PATH
+
+
+def _build_c_library(force: bool, verbose: bool) -> Path:
     if not force and not is_stale():
         return LIB_PATH
     nvcc = _nvcc()

@@ -172,3 +172,16 @@ def test_hot_expert_cache_table_split():
     assert os_.tolist() == [0, 0, 128, 384, 0, 0, 0, 0] and es.tolist() == [0, 0, 0, -1]
     # every row range lands in exactly one of the two launches
     assert (oc.view(-1, 2) + os_.view(-1, 2)).reshape(-1).tolist() == offsets.tolist()
+
+
+def test_torch_extension_loads_and_registers_the_launch_op():
+    """The operators launch through `torch.ops.asymgemm_b200.m_grouped_gemm_nt`; it has a CUDA kernel only, so a call
+    with CPU tensors is refused by the dispatcher instead of computing anything on the host."""
+    from asymgemm_b200 import _lib
+    ops = _lib.torch_ops()
+    schema = str(ops.m_grouped_gemm_nt.default._schema)
+    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema
+    z = torch.zeros(4, 4)
+    with pytest.raises(NotImplementedError):
+        ops.m_grouped_gemm_nt(0, 0, z, None, z, None, z, None, None, 0, None, 4, 4, 4, 1, None,
+                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None)
