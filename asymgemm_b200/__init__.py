@@ -20,6 +20,8 @@ from .api import (  # noqa: F401
     set_num_sms,
     set_split_segments,
     set_tile_config,
+    prepare_weights,
+    release_weights,
     set_use_scratch,
     set_weight_path,
     get_weight_path,

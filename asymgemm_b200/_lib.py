@@ -77,6 +77,8 @@ EXPORTS = [
     "ag_get_mk_alignment_for_contiguous_layout",
     "ag_fp4_sf_blocked_bytes",
     "ag_fp4_sf_to_blocked",
+    "ag_prepare_weights",
+    "ag_release_weights",
     "ag_measure_host_link",
     "ag_measure_host_stream",
     "ag_selftest_wait_limit",
@@ -148,6 +150,10 @@ def load() -> ctypes.CDLL:
     lib.ag_combine_topk_f32.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
+    lib.ag_prepare_weights.argtypes = [c_void_p, c_uint64, c_int32]
+    lib.ag_prepare_weights.restype = c_int32
+    lib.ag_release_weights.argtypes = [c_void_p]
+    lib.ag_release_weights.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]
     lib.ag_measure_host_link.restype = c_int32
     lib.ag_last_error.argtypes = []

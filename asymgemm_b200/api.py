@@ -97,6 +97,23 @@ def get_weight_path() -> str:
     return _state["weight_path"]
 
 
+def prepare_weights(b: torch.Tensor, read_only: bool = False) -> torch.Tensor:
+    """Page-lock and map an ordinary (pageable) CPU tensor in place so that it can be passed as `b` (extension; the
+    reference registers its weight slabs the same way, asym_gemm/unified_moe/runtime.py:236-279). A tensor that is
+    already pinned or on the GPU is returned untouched. Keep the tensor alive, and call `release_weights` before its
+    memory is freed."""
+    _require(b.is_contiguous(), "weights must be contiguous")
+    if b.is_cuda or b.is_pinned():
+        return b
+    _lib.check(_lib.load().ag_prepare_weights(b.data_ptr(), b.numel() * b.element_size(), 1 if read_only else 0))
+    return b
+
+
+def release_weights(b: torch.Tensor) -> None:
+    """Undo `prepare_weights` for this tensor's memory (raises for memory it did not register)."""
+    _lib.check(_lib.load().ag_release_weights(b.data_ptr()))
+
+
 def set_use_scratch(flag: bool) -> None:
     """Whether long segments replay their weight column from device scratch (default) or re-read B."""
     _state["use_scratch"] = bool(flag)

@@ -388,6 +388,44 @@ int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t row
   return AG_OK;
 }
 
+namespace {
+std::mutex g_reg_mu;
+void* g_registered[256] = {};   // host ranges registered by ag_prepare_weights, by start address
+}  // namespace
+
+int ag_prepare_weights(void* ptr, uint64_t bytes, int32_t read_only) {
+  AG_REQUIRE(ptr != nullptr && bytes > 0, "ptr must be non-NULL and bytes positive");
+  const void* alias = nullptr;
+  if (classify(ptr, &alias) != RES_UNREACHABLE) return AG_OK;   // device memory, or already pinned / registered
+  std::lock_guard<std::mutex> lk(g_reg_mu);
+  int slot = -1;
+  for (int i = 0; i < 256 && slot < 0; ++i)
+    if (g_registered[i] == nullptr) slot = i;
+  AG_REQUIRE(slot >= 0, "too many ranges registered through ag_prepare_weights (256)");
+  unsigned flags = cudaHostRegisterPortable | cudaHostRegisterMapped;
+  if (read_only) flags |= cudaHostRegisterReadOnly;
+  cudaError_t e = cudaHostRegister(ptr, bytes, flags);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(AG_E_CUDA, "cudaHostRegister(%p, %llu bytes%s) failed: %s", ptr, static_cast<unsigned long long>(bytes),
+                read_only ? ", read-only" : "", cudaGetErrorString(e));
+  }
+  g_registered[slot] = ptr;
+  return AG_OK;
+}
+
+int ag_release_weights(void* ptr) {
+  AG_REQUIRE(ptr != nullptr, "ptr must be non-NULL");
+  std::lock_guard<std::mutex> lk(g_reg_mu);
+  for (int i = 0; i < 256; ++i) {
+    if (g_registered[i] != ptr) continue;
+    AG_CUDA(cudaHostUnregister(ptr));
+    g_registered[i] = nullptr;
+    return AG_OK;
+  }
+  return fail(AG_E_INVALID, "%p was not registered through ag_prepare_weights", ptr);
+}
+
 int ag_measure_host_link(uint64_t bytes, int32_t reps, double* gbps_out) {
   AG_REQUIRE(gbps_out != nullptr && bytes > 0, "bad arguments");
   void *h = nullptr, *d = nullptr;

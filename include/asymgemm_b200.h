@@ -167,6 +167,15 @@ int32_t ag_get_mk_alignment_for_contiguous_layout(void);
 uint64_t ag_fp4_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t k16);
 int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t rows, int64_t k16, void* stream);
 
+/* Makes an ordinary host allocation (malloc, mmap, a framework's pageable tensor) usable as `b`: page-locks and maps
+ * [ptr, ptr + bytes) for the current device's context with cudaHostRegister (portable, mapped; read_only != 0 adds the
+ * read-only flag, which file-backed or write-protected mappings need). Memory that is already pinned, registered or
+ * device memory is left alone and counts as success. ag_release_weights undoes a registration made here; it refuses a
+ * pointer this library did not register. Neither call touches the contents. Reference counterpart: `_pin_on_node`
+ * (asym_gemm/unified_moe/runtime.py:236-279), which registers NUMA-placed slabs through libcudart the same way. */
+int ag_prepare_weights(void* ptr, uint64_t bytes, int32_t read_only);
+int ag_release_weights(void* ptr);
+
 /* Measures pinned-host -> device copy-engine bandwidth (GB/s) with cudaMemcpyAsync over `bytes`, best of
  * `reps`: the denominator for "fraction of host link". Reference counterpart: none (its authors quote
  * ~50 GB/s for the same copy, asym_gemm/unified_moe/runtime.py:115-116). */

@@ -450,3 +450,27 @@ def test_staged_weight_path_matches_in_kernel_stream(kind, layout):
     finally:
         ag.set_weight_path("stream", chunk_bytes=128 << 20)
     _check(kind, plain.float().cpu().numpy().reshape(-1, 256), c["ref"], c["segments"])
+
+
+def test_prepare_weights_registers_pageable_memory_in_place():
+    """Weights in an ordinary CPU tensor are refused; after `prepare_weights` the same memory serves as B and gives the
+    result of a pinned copy; `release_weights` undoes it and refuses memory it did not register."""
+    c = H.make_contiguous_case("fp8", [200, 0, 129], 256, 512, seed=91)
+    plain = torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda")
+    _run_contiguous(c, plain)
+    pageable = torch.empty(c["b"].shape, dtype=torch.uint8).copy_(c["b"].view(torch.uint8)).view(torch.float8_e4m3fn)
+    assert not pageable.is_pinned()
+    d = torch.zeros_like(plain)
+    with pytest.raises(RuntimeError, match="pinned"):
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (pageable, c["sfb"]), d, c["offsets"], c["experts"], None)
+    assert ag.prepare_weights(pageable) is pageable and pageable.is_pinned()
+    try:
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (pageable, c["sfb"]), d, c["offsets"], c["experts"], None)
+        torch.cuda.synchronize()
+        assert torch.equal(d.view(torch.int16), plain.view(torch.int16))
+    finally:
+        ag.release_weights(pageable)
+    assert not pageable.is_pinned()
+    with pytest.raises(RuntimeError, match="not registered"):
+        ag.release_weights(pageable)
+    assert ag.prepare_weights(c["b"]) is c["b"]          # already pinned: nothing to do, nothing to release
