@@ -82,11 +82,15 @@ def set_weight_path(path: str, chunk_bytes: Optional[int] = None) -> None:
     "staged": the copy engine moves every expert, about `chunk_bytes` (default 128 MiB) of whole experts at a time, into
     a double buffer in HBM while the grouped GEMM of the previous chunk runs from there (`stage` of the C descriptor; this
     module owns one such buffer per device); same results, a few percent
-    more of the link, for calls in which (nearly) all experts are active. The reference's unified runtime stages its
+    more of the link, for calls in which (nearly) all experts are active.
+    "auto": staged for calls that can have rows for every expert (contiguous: at least 128 rows of `a` per expert, the
+    padded size of one active expert; masked: `expected_m` >= 8) over at least 256 MiB of weights, the in-kernel stream
+    otherwise (decode-sized batches, where most experts get no rows: 8 tokens x top-8 over 256 experts take 33 ms
+    streamed and 135 ms staged). The reference's unified runtime stages its
     streamed partition the same way, by default (`_StageRing`, asym_gemm/unified_moe/runtime.py:110-200; its in-kernel
     reads reach 21.5 of the copy engine's 50 GB/s); here the in-kernel stream reaches 0.92 of the copy engine's rate, so
     staging is the option and the stream the default."""
-    _require(path in ("stream", "staged"), "weight path must be 'stream' or 'staged'")
+    _require(path in ("stream", "staged", "auto"), "weight path must be 'stream', 'staged' or 'auto'")
     _state["weight_path"] = path
     if chunk_bytes is not None:
         _require(int(chunk_bytes) > 0, "chunk_bytes must be positive")
@@ -233,6 +237,25 @@ def _common_checks(a, b, d, masked: bool, k_div: int = 1):
     return int(g), int(m), int(n), int(k * k_div)
 
 
+# "auto" weight path: stage when the call can have rows for (nearly) every expert and the weights are large enough for
+# the per-chunk launches to disappear behind the copies. Only the device knows which experts are active, so the rule
+# reads what the host has: a contiguous layout pads every active expert to 128 rows, so fewer than 128 rows of `a` per
+# expert prove that some experts are idle; a masked call states its expected rows per group. (256 experts, Zipf(0.8)
+# routing, K=7168, N=4096: the two paths tie near 4 valid rows per expert; 8 tokens x top-8 take 33 ms streamed and
+# 135 ms staged, 512 tokens 150 and 136.)
+_AUTO_ROWS_PER_EXPERT = {_lib.LAYOUT_CONTIGUOUS: 128, _lib.LAYOUT_MASKED: 8}
+_AUTO_MIN_WEIGHT_BYTES = 256 << 20
+
+
+def _use_staging(b: torch.Tensor, g: int, rows: int, layout: int, raw_dump) -> bool:
+    mode = _state["weight_path"]
+    if mode == "stream" or b.is_cuda or raw_dump is not None:
+        return False
+    if mode == "staged":
+        return True
+    return rows >= _AUTO_ROWS_PER_EXPERT[layout] * g and b.numel() * b.element_size() >= _AUTO_MIN_WEIGHT_BYTES
+
+
 def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor:
     """Double buffer in HBM for the staged weight path, one per device, sized for two chunks of whole experts of `b`.
     The library orders the copies into it after the GEMMs of earlier calls that read it, on whichever stream they ran."""
@@ -251,11 +274,13 @@ def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor
 
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
-            masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0) -> None:
+            masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0,
+            rows_hint: Optional[int] = None) -> None:
     """Every operator ends here: one call of the torch extension's op, which fills the C descriptor from the tensors and
-    launches on the current stream of a's device (csrc/torch_ops.cpp)."""
+    launches on the current stream of a's device (csrc/torch_ops.cpp). `rows_hint`: rows the call is expected to
+    multiply (masked layout: expected_m * groups; contiguous: m), for the "auto" weight path."""
     dev = a.device
-    stage = _stage_buffer(b, g, dev) if _state["weight_path"] == "staged" and not b.is_cuda and raw_dump is None else None
+    stage = _stage_buffer(b, g, dev) if _use_staging(b, g, m if rows_hint is None else rows_hint, layout, raw_dump) else None
     op = _lib.torch_ops().m_grouped_gemm_nt
     with torch.cuda.device(dev):
         op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
@@ -292,7 +317,7 @@ def m_grouped_bf16_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, compi
     if m == 0 or expected_m == 0:
         return
     _launch(_lib.KIND_BF16, "ag_m_grouped_bf16_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a, sfa=None, b=b, sfb=None, d=d,
-            masked_m=masked_m, m=m, n=n, k=k, g=g)
+            masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g)
 
 
 # --------------------------------------------------------------------------------------------- FP8
@@ -374,10 +399,10 @@ def m_grouped_fp8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe
         cacheable = b[1].is_contiguous() and (b[1].is_cuda or b[1].is_pinned())
         sfb_b = _fp8_blocked_ue8m0(b[1] if cacheable else sfb, g, n, kb, 128, dev, cache=cacheable)
         _launch(_lib.KIND_FP8_UE8M0, "ag_m_grouped_fp8_ue8m0_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
-                masked_m=masked_m, m=m, n=n, k=k, g=g)
+                masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g)
         return
     _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
-            masked_m=masked_m, m=m, n=n, k=k, g=g)
+            masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g)
 
 
 # --------------------------------------------------------------------------------------------- INT8
@@ -426,7 +451,7 @@ def m_grouped_int8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recip
     if m == 0 or expected_m == 0:
         return
     _launch(_lib.KIND_INT8, "ag_m_grouped_int8_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
-            masked_m=masked_m, m=m, n=n, k=k, g=g, raw_dump=raw_accumulators)
+            masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g, raw_dump=raw_accumulators)
 
 
 # --------------------------------------------------------------------------------------------- NVFP4
@@ -507,4 +532,4 @@ def m_grouped_fp4_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe
     sfa_b = _fp4_blocked(a[1], 1, g * m, k16, dev, cache=False)
     sfb_b = _fp4_blocked(b[1], g, n, k16, dev, cache=True)
     _launch(_lib.KIND_NVFP4, "ag_m_grouped_fp4_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
-            masked_m=masked_m, m=m, n=n, k=k, g=g, alpha=alpha)
+            masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g, alpha=alpha)

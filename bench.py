@@ -344,6 +344,9 @@ def main():
     ap.add_argument("--workload", default="c3_fp8", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--experts", type=int, default=0, help="shrink the expert count (tokens shrink in proportion); 0 = full size")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the token count of the workload (decode-sized batches leave experts without rows: the in-kernel "
+                         "stream skips those, the staged path copies them all); 0 = the named config")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weights", default="host", choices=["host", "device", "staged"],
                     help="host (default): B in pinned host memory, read by the kernel itself; device: B resident in HBM (tensor-bound "
@@ -370,6 +373,8 @@ def main():
     if args.experts and args.experts < cfg["experts"]:
         cfg["tokens"] = max(1, cfg["tokens"] * args.experts // cfg["experts"])
         cfg["experts"] = args.experts
+    if args.tokens > 0:
+        cfg["tokens"] = args.tokens
     if cfg["kind"] == "moe":
         desc = (f"{args.workload}: FP8 MoE layer (gate+up K={cfg['hidden']} N={2 * cfg['inter']}, SiLU*mul, down K={cfg['inter']} "
                 f"N={cfg['hidden']}), {cfg['experts']} experts sharded over the ranks, {cfg['tokens']} tokens x top-{cfg['top_k']} "

@@ -185,3 +185,26 @@ def test_torch_extension_loads_and_registers_the_launch_op():
     with pytest.raises(NotImplementedError):
         ops.m_grouped_gemm_nt(0, 0, z, None, z, None, z, None, None, 0, None, 4, 4, 4, 1, None,
                               torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None)
+
+
+def test_auto_weight_path_rule():
+    """"auto" stages only host-resident weights of at least 256 MiB in calls that can have rows for every expert."""
+    from asymgemm_b200 import _lib, api
+    big = torch.empty((64, 2048, 2048), dtype=torch.uint8)           # 256 MiB, 64 experts
+    small = torch.empty((64, 256, 256), dtype=torch.uint8)
+    C, M = _lib.LAYOUT_CONTIGUOUS, _lib.LAYOUT_MASKED
+    try:
+        api.set_weight_path("auto")
+        assert api._use_staging(big, 64, 64 * 128, C, None)
+        assert not api._use_staging(big, 64, 64 * 128 - 1, C, None)      # some expert is certainly idle
+        assert api._use_staging(big, 64, 64 * 8, M, None) and not api._use_staging(big, 64, 64 * 7, M, None)
+        assert not api._use_staging(small, 64, 1 << 20, C, None)
+        assert not api._use_staging(big, 64, 1 << 20, C, object())        # the INT8 debug dump keeps the plain path
+        api.set_weight_path("staged")
+        assert api._use_staging(small, 64, 1, C, None)
+        api.set_weight_path("stream")
+        assert not api._use_staging(big, 64, 1 << 20, C, None)
+        with pytest.raises(RuntimeError):
+            api.set_weight_path("pipelined")
+    finally:
+        api.set_weight_path("stream")
