@@ -16,6 +16,7 @@ The activation between the GEMMs follows the reference's CPU MoE bucket: silu(ga
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import mmap
 from dataclasses import dataclass
@@ -111,7 +112,7 @@ class EPDispatcher:
         padded_bound = total_recv rounded up plus 127 rows per expert, an upper bound of the rows the layout can use.
         """
         dev = recv_counts.device
-        epr = self.experts_per_rank
+        epr = int(recv_counts.shape[1])       # all local experts, or one group of them (pipelined)
         rc = recv_counts.to(torch.int64)
         per_expert = rc.sum(dim=0)                                   # [epr]
         padded = (per_expert + ALIGN - 1) // ALIGN * ALIGN
@@ -168,6 +169,107 @@ class EPDispatcher:
         state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded_rows, offsets, experts, tokens, top_k,
                               src_token if self.world == 1 else None)
         return state, outs[0], tuple(outs[1:])
+
+    def pipelined(self, rows: torch.Tensor, extras: Tuple[torch.Tensor, ...], topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                  groups: int, expert_fn) -> torch.Tensor:
+        """dispatch -> experts -> combine with every rank's experts cut into `groups` groups, so that on a GPU the
+        exchanges of one group run while another group is being multiplied.
+
+        Cutting by experts (not by tokens) leaves every weight byte in exactly one round. The exchanges run on a
+        communication stream, `expert_fn` on the caller's stream: dispatch of group g+1 and the return of group g-1
+        overlap the GEMMs of group g. All ranks issue the collectives in the same order (every dispatch, then the
+        returns). `expert_fn(recv_rows, recv_extras, state, first, count)` multiplies the rows received for the local
+        experts [first, first + count) -- `state` describes their padded contiguous layout, expert ids relative to
+        `first` -- and returns the result in that layout. On CPU tensors the same steps run one after the other.
+        Returns y [T, H] like `combine`.
+        """
+        tokens, top_k = topk_ids.shape
+        dev = topk_ids.device
+        cuda = dev.type == "cuda"
+        main = torch.cuda.current_stream(dev) if cuda else None
+        comm = self._side_stream(dev)
+
+        def on_comm():
+            return torch.cuda.stream(comm) if cuda else contextlib.nullcontext()
+
+        if cuda:
+            comm.wait_stream(main)
+        with on_comm():
+            order, send_counts, recv_counts = self.plan(topk_ids)
+            send_host, recv_host = send_counts.cpu().to(torch.int64), recv_counts.cpu().to(torch.int64)   # waits for this stream only
+            src_token = torch.div(order, top_k, rounding_mode="floor")
+        groups = max(1, min(int(groups), min(hi - lo for lo, hi in self.expert_ranges)))
+        # the (token, slot) pairs sorted by expert are also sorted by (rank, local expert): start of every such block
+        flat = send_host.reshape(-1)
+        block_start = (torch.cumsum(flat, 0) - flat).reshape(send_host.shape)
+
+        def cut(n, g):
+            return g * n // groups
+
+        rounds = []
+        for g in range(groups):
+            spans, send_splits = [], []
+            for r, (lo, hi) in enumerate(self.expert_ranges):
+                a, b = cut(hi - lo, g), cut(hi - lo, g + 1)
+                cnt = int(send_host[r, a:b].sum())
+                send_splits.append(cnt)
+                if cnt:
+                    spans.append((int(block_start[r, a]), cnt))
+            a, b = cut(self.experts_per_rank, g), cut(self.experts_per_rank, g + 1)
+            rounds.append((spans, send_splits, [int(v) for v in recv_host[:, a:b].sum(dim=1)], a, b))
+
+        # ---- every dispatch, on the communication stream
+        keep, arrived = [], []
+        with on_comm():
+            for spans, send_splits, recv_splits, a, b in rounds:
+                idx = (torch.cat([torch.arange(s0, s0 + cnt, device=dev) for s0, cnt in spans]) if spans
+                       else torch.zeros(0, dtype=torch.int64, device=dev))
+                rows_src = src_token.index_select(0, idx)
+                total = sum(recv_splits)
+                recvd = []
+                for t in (rows,) + tuple(extras):
+                    send = moe_ops.move_rows(t.contiguous(), idx.numel(), src_rows=rows_src)
+                    as_bytes = send.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else send
+                    recv = torch.empty((total,) + tuple(as_bytes.shape[1:]), dtype=as_bytes.dtype, device=dev)
+                    self._all_to_all(recv, as_bytes, recv_splits, send_splits)
+                    recvd.append(recv.view(t.dtype) if t.dtype == torch.float8_e4m3fn else recv)
+                    keep.append(send)
+                ev = None
+                if cuda:
+                    ev = torch.cuda.Event()
+                    ev.record(comm)
+                arrived.append((idx, recvd, ev))
+
+        # ---- group by group: multiply on the caller's stream, send the results home on the communication stream
+        ret_sorted = None
+        for (spans, send_splits, recv_splits, a, b), (idx, recvd, ev) in zip(rounds, arrived):
+            if cuda:
+                main.wait_event(ev)
+            total = sum(recv_splits)
+            dest_rows, per_expert, padded, offsets, experts = self.layout(recv_counts[:, a:b], total)
+            state = DispatchState(order, send_splits, recv_splits, dest_rows, per_expert, padded, offsets, experts, tokens, top_k)
+            out = expert_fn(recvd[0], tuple(recvd[1:]), state, a, b - a)
+            back = moe_ops.move_rows(out, total, src_rows=dest_rows)
+            done = None
+            if cuda:
+                done = torch.cuda.Event()
+                done.record(main)
+            with on_comm():
+                if cuda:
+                    comm.wait_event(done)
+                ret = torch.empty((idx.numel(),) + tuple(back.shape[1:]), dtype=back.dtype, device=dev)
+                self._all_to_all(ret, back, send_splits, recv_splits)
+                if ret_sorted is None:
+                    ret_sorted = torch.empty((tokens * top_k,) + tuple(back.shape[1:]), dtype=back.dtype, device=dev)
+                moe_ops.move_rows_into(ret_sorted, ret, idx)
+            keep += [out, back, ret, state]          # alive until both streams are done with them
+        if cuda:
+            main.wait_stream(comm)
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=dev)
+        y = moe_ops.combine_topk(ret_sorted, inv, topk_weights, tokens, top_k)
+        del keep
+        return y
 
     def _side_stream(self, device):
         if device.type != "cuda":
@@ -286,22 +388,43 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
-                 expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False):
+                 expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False, pipeline_groups: int = 1,
+                 comm_sms: int = 24):
         """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
         (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly.
         Whether the kernel reads the pinned weights itself or the copy engine stages them is the operators' setting
-        (`asymgemm_b200.set_weight_path`)."""
+        (`asymgemm_b200.set_weight_path`). `pipeline_groups` > 1 (several ranks only): the layer runs in that many
+        rounds over groups of each rank's experts so that the token exchanges overlap the GEMMs
+        (`EPDispatcher.pipelined`); the persistent GEMMs then leave `comm_sms` SMs free for the exchange kernels --
+        they are bound by the host link, not by SMs."""
+        self.pipeline_groups = max(1, int(pipeline_groups))
+        self.comm_sms = max(0, int(comm_sms))
         self.dispatcher = EPDispatcher(num_experts, group, expert_ranges)
         self.ue8m0_scales = bool(ue8m0_scales)
         self.hidden, self.inter = hidden, inter
         self.w13, self.w2 = w13, w2
+        self._weight_views: dict = {}
         epr = self.dispatcher.experts_per_rank
         if tuple(w13[0].shape) != (epr, 2 * inter, hidden) or tuple(w2[0].shape) != (epr, hidden, inter):
             raise RuntimeError("weight shapes do not match (experts_per_rank, 2*inter, hidden) / (experts_per_rank, hidden, inter)")
 
-    def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState) -> torch.Tensor:
-        """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]."""
+    def _weights_of(self, first: int, count: int):
+        """(w13, w2) of the local experts [first, first + count): views made once, because the operators cache prepared
+        weight scales by tensor identity."""
+        if count >= self.dispatcher.experts_per_rank:
+            return self.w13, self.w2
+        hit = self._weight_views.get((first, count))
+        if hit is None:
+            sl = slice(first, first + count)
+            hit = self._weight_views[(first, count)] = ((self.w13[0][sl], self.w13[1][sl]), (self.w2[0][sl], self.w2[1][sl]))
+        return hit
+
+    def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState, first: int = 0,
+                        count: Optional[int] = None) -> torch.Tensor:
+        """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]. `first` / `count`: the local
+        experts `state` describes (expert id 0 of its segment table = local expert `first`); default: all of them."""
         from . import api
+        w13, w2 = self._weights_of(first, self.dispatcher.experts_per_rank if count is None else count)
         m = state.padded_rows
         dev = a_q.device
         d1 = torch.empty((m, 2 * self.inter), dtype=torch.bfloat16, device=dev)
@@ -309,14 +432,29 @@ class ExpertParallelMoE:
         if m == 0:
             return d2
         hw = self.ue8m0_scales
-        api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), self.w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
         a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw)
-        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), self.w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
         return d2
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
         x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous(), pow2_scales=self.ue8m0_scales)
+        if self.pipeline_groups > 1 and self.dispatcher.world > 1:
+            from . import api
+
+            def group_forward(recv_q, recv_extras, state, first, count):
+                a_q = to_contiguous_layout(recv_q, state)
+                sfa = to_contiguous_layout(recv_extras[0], state)
+                return self.experts_forward(a_q, sfa, state, first, count)
+
+            cap = api.get_num_sms()
+            sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+            api.set_num_sms(max(8, (cap if cap > 0 else sms) - self.comm_sms))
+            try:
+                return self.dispatcher.pipelined(x_q, (sfx,), topk_ids, topk_weights, self.pipeline_groups, group_forward)
+            finally:
+                api.set_num_sms(cap)
         state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)

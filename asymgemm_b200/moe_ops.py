@@ -100,6 +100,19 @@ def move_rows(src: torch.Tensor, out_rows: int, src_rows: Optional[torch.Tensor]
     return out
 
 
+def move_rows_into(out: torch.Tensor, src: torch.Tensor, dst_rows: torch.Tensor) -> None:
+    """out[dst_rows[i]] = src[i] for every row of src, in place (rows of out that are not named keep their contents)."""
+    count = int(dst_rows.numel())
+    if count == 0:
+        return
+    rb = _row_bytes(src)
+    if src.is_cuda and rb % 16 == 0 and src.is_contiguous() and out.is_contiguous():
+        with torch.cuda.device(src.device):
+            _lib.check(_lib.load().ag_move_rows(src.data_ptr(), out.data_ptr(), None, dst_rows.data_ptr(), count, rb, _stream(src)))
+        return
+    out.index_copy_(0, dst_rows, src)
+
+
 def combine_topk(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, tokens: int, top_k: int) -> torch.Tensor:
     """y[t] = sum_j weights[t, j] * rows[pos[t*top_k + j]] (fp32 accumulation), as rows.dtype."""
     cols = rows.shape[1]

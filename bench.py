@@ -116,7 +116,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
 
 
-def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None, ue8m0=False):
+def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None, ue8m0=False, pipeline_groups=1):
     """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
     GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing."""
     from asymgemm_b200 import ep
@@ -137,7 +137,8 @@ def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None, ue8m0
         w2[e].copy_(q, non_blocking=True)
         s2[e] = s
     torch.cuda.synchronize(device)
-    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges, ue8m0_scales=ue8m0)
+    layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges, ue8m0_scales=ue8m0,
+                                 pipeline_groups=pipeline_groups)
     t_local = cfg["tokens"] // world
     x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
     logits = torch.randn((t_local, e_total), device=device, generator=gen)
@@ -213,6 +214,10 @@ def gemm_launches_per_step(w, args):
     if w["kind"] == "moe":
         layer = w["layer"]
         g = layer.w13[0].shape[0]
+        rounds = layer.pipeline_groups if layer.dispatcher.world > 1 else 1
+        if rounds > 1:      # every round launches both GEMMs over its share of the experts
+            per = max(1, g // rounds)
+            return rounds * (chunks(per, layer.w13[0][0].numel()) + chunks(per, layer.w2[0][0].numel()))
         return chunks(g, layer.w13[0][0].numel()) + chunks(g, layer.w2[0][0].numel())
     if w.get("cache") is not None:
         return 2
@@ -347,6 +352,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the token count of the workload (decode-sized batches leave experts without rows: the in-kernel "
                          "stream skips those, the staged path copies them all); 0 = the named config")
+    ap.add_argument("--pipeline-groups", type=int, default=1,
+                    help="c5_moe_fp8 on several GPUs: run the layer in this many rounds over groups of each rank's experts so that "
+                         "the token exchanges overlap the GEMMs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weights", default="host", choices=["host", "device", "staged"],
                     help="host (default): B in pinned host memory, read by the kernel itself; device: B resident in HBM (tensor-bound "
@@ -420,7 +428,11 @@ def main():
         config["sharding"] = ("contiguous expert ranges sized by each rank's host-link rate measured with all ranks streaming at once "
                               f"({[round(x, 1) for x in rates.tolist()]} GB/s); equal when the rates are within 10 %")
     if moe:
-        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=args.fp8_scales == "ue8m0")
+        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=args.fp8_scales == "ue8m0",
+                      pipeline_groups=args.pipeline_groups)
+        if args.pipeline_groups > 1 and world > 1:
+            config["pipeline"] = (f"{args.pipeline_groups} rounds over groups of each rank's experts; exchanges on a second stream "
+                                  "overlap the GEMMs")
     elif cfg["kind"] == "fp4":
         w = build_masked_fp4(cfg, rank, world, device)
     else:

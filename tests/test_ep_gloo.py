@@ -58,6 +58,21 @@ def _roundtrip_worker(rank, world, port, q, ranges=None):
         y = disp.combine(_fake_experts(a, state, first_expert), state, w)
         want = ((ids + 1).float() * w).sum(dim=1, keepdim=True) * x
         assert torch.allclose(y, want, rtol=1e-5, atol=1e-5), (y - want).abs().max()
+        # the same layer in rounds over groups of each rank's experts (on a GPU the exchanges overlap the GEMMs)
+        tags = torch.arange(tokens, dtype=torch.float32).unsqueeze(1)
+        for groups in (2, 3, 16):
+            seen = []
+
+            def group_fn(recv_rows, recv_extras, st, first, count):
+                seen.append((first, count))
+                assert st.experts.tolist() == list(range(count)) + [-1] and recv_extras[0].shape == (recv_rows.shape[0], 1)
+                return _fake_experts(to_contiguous_layout(recv_rows, st), st, first_expert + first)
+
+            y2 = disp.pipelined(x, (tags,), ids, w, groups, group_fn)
+            assert torch.allclose(y2, want, rtol=1e-5, atol=1e-5), (groups, (y2 - want).abs().max())
+            # the groups tile this rank's experts in order, none empty
+            assert seen[0][0] == 0 and sum(c for _, c in seen) == disp.experts_per_rank and all(c > 0 for _, c in seen)
+            assert all(seen[i][0] + seen[i][1] == seen[i + 1][0] for i in range(len(seen) - 1))
         dist.barrier()
         q.put((rank, "ok"))
     except Exception as e:  # pragma: no cover - reported through the queue

@@ -64,6 +64,12 @@ def _case(rank, world, device, weight_path="stream"):
     wts = (wts / wts.sum(-1, keepdim=True)).to(device)
     ids = ids.to(device)
     y = layer.forward(x, ids, wts)
+    if world > 1:
+        # rounds over groups of each rank's experts, exchanges on a second stream: every row's result is unchanged
+        for groups in (2, 4):
+            piped = ep.ExpertParallelMoE(num_experts, hidden, inter, layer.w13, layer.w2, pipeline_groups=groups)
+            assert torch.equal(piped.forward(x, ids, wts), y), f"pipeline_groups={groups}"
+            assert torch.equal(piped.forward(x, ids, wts), y), f"pipeline_groups={groups}, second call"
     if weight_path == "staged":
         # the copy engine moves the same bytes the kernel would read: same result, also when the staging buffers are reused
         import asymgemm_b200 as ag
