@@ -4,7 +4,7 @@ host-link peak.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3_fp8|c2_bf16|c1_int8] [--impl ours|reference]
 
-One step = one grouped GEMM over one batch of synthetic, seeded input (the shapes of BASELINE.json's configs; no
+One step = one grouped GEMM over one batch of synthetic, seeded input (the shapes of the benchmark configurations named in WORKLOADS; no
 dataset or checkpoint is involved). The default workload is the DeepSeek-V3-shaped FP8 gate+up GEMM: 256 experts,
 K=7168, N=4096, 16384 tokens x top-8 with Zipf(0.8) expert popularity, B (7.5 GB) in pinned host memory.
 With N > 1 ranks the experts (and the rows routed to them) are split across ranks in contiguous ranges -- evenly when the

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Generates the golden fixtures in this directory by IMPORTING the reference's own Python code.
 
-Run once in a container that has the reference checkout (default /root/reference); the fixtures are committed, the
+Run once in a container that has the reference checkout (pass its path with --reference); the fixtures are committed, the
 checkout is not needed to run the tests. What is imported from bytedance-iaas/AsymGEMM:
   * asym_gemm/utils/math.py          -- the quantisers that define the FP8 / INT8 / NVFP4 formats
   * tests/test_fp4_asym_gemm.py      -- _quantize_nvfp4_e4m3, _manual_dequant_reference (NVFP4 dequantised reference)
@@ -11,7 +11,7 @@ checkout is not needed to run the tests. What is imported from bytedance-iaas/As
 The compiled extension `asym_gemm._C` cannot be built here; a stub package stands in for it so that the pure-Python
 helpers import. The reference's GPU kernels themselves are never run.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout of the reference>]
 """
 from __future__ import annotations
 

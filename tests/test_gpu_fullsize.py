@@ -1,4 +1,4 @@
-"""Full-size runs (BASELINE.json configs) checked through size-independent properties: a column checksum of D against
+"""Full-size runs (the benchmark configurations of bench.WORKLOADS) checked through size-independent properties: a column checksum of D against
 A x (column sum of B), sampled blocks against a torch fp32 product on the device, and run-to-run bit identity."""
 import pytest
 import torch
