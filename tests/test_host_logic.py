@@ -208,3 +208,27 @@ def test_auto_weight_path_rule():
             api.set_weight_path("pipelined")
     finally:
         api.set_weight_path("stream")
+
+
+def test_plain_c_program_compiles_against_the_header_and_links():
+    """include/asymgemm_b200.h is a C header: a C99 program built with gcc and nothing else must compile with all
+    warnings on, link against the library and get error codes (not crashes) for malformed requests, without a GPU."""
+    import shutil
+    import subprocess
+    import tempfile
+    from pathlib import Path
+    from asymgemm_b200 import _lib
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    root = Path(__file__).resolve().parent.parent
+    lib_dir = _lib.LIB_PATH.parent
+    assert _lib.LIB_PATH.exists()
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = Path(tmp) / "consumer"
+        subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", str(root / "include"),
+                        str(root / "tests" / "c_abi" / "consumer.c"), "-o", str(exe), "-L", str(lib_dir), "-lasymgemm_b200",
+                        f"-Wl,-rpath,{lib_dir}"], check=True, capture_output=True, text=True)
+        res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "c_abi consumer: ok" in res.stdout
