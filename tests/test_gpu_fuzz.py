@@ -106,3 +106,36 @@ def test_random_case_fp8_hardware_scaled(seed):
     except AssertionError as e:
         raise AssertionError(f"{e} [{info}]")
     assert np.isnan(d_np[~H.valid_row_mask(c["segments"], rows_total)]).all(), info
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_case_staged_weights(seed):
+    """The same sweep with host-resident weights moved by the copy engine in chunks of 1..G whole experts."""
+    rng = random.Random(9000 + seed)
+    kind, masked, counts, n, k, tile, _ = _random_case(rng)
+    chunk = rng.randint(1, len(counts))
+    ag.set_tile_config(tile)
+    try:
+        if masked:
+            m_max = max(counts)
+            m_max = -(-m_max // 128) * 128 if kind == "fp4" or rng.random() < 0.5 else m_max + rng.randint(0, 40)
+            c = H.make_masked_case(kind, counts, m_max, n, k, seed=seed, b_on_host=True)
+            d = torch.full((len(counts), m_max, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            rows_total = len(counts) * m_max
+        else:
+            c = H.make_contiguous_case(kind, counts, n, k, seed=seed, b_on_host=True)
+            d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            rows_total = c["m_total"]
+        ag.set_weight_path("staged", chunk_bytes=chunk * (c["b"].numel() * c["b"].element_size() // len(counts)))
+        (_run_masked if masked else _run_contiguous)(c, d)
+        ag.check_status()
+    finally:
+        ag.set_tile_config(0)
+        ag.set_weight_path("stream", chunk_bytes=128 << 20)
+    d_np = d.float().cpu().numpy().reshape(rows_total, n)
+    info = f"kind={kind} masked={masked} counts={counts} n={n} k={k} tile={tile} chunk={chunk}"
+    try:
+        _check(kind, d_np, c["ref"], c["segments"])
+    except AssertionError as e:
+        raise AssertionError(f"{e} [{info}]")
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], rows_total)]).all(), info
