@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     set_num_sms,
     set_split_segments,
     set_tile_config,
+    prefetch_weights,
     prepare_weights,
     release_weights,
     set_use_scratch,

@@ -57,6 +57,7 @@ class GemmDesc(Structure):
         ("no_split", c_int32),
         ("stage", c_void_p),
         ("stage_bytes", c_uint64),
+        ("stage_chunk_bytes", c_uint64),
     ]
 
 
@@ -77,6 +78,7 @@ EXPORTS = [
     "ag_get_mk_alignment_for_contiguous_layout",
     "ag_fp4_sf_blocked_bytes",
     "ag_fp4_sf_to_blocked",
+    "ag_prefetch_staged_weights",
     "ag_prepare_weights",
     "ag_release_weights",
     "ag_measure_host_link",
@@ -150,6 +152,8 @@ def load() -> ctypes.CDLL:
     lib.ag_combine_topk_f32.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
+    lib.ag_prefetch_staged_weights.argtypes = [c_void_p, c_uint64, c_int32, c_void_p, c_uint64, c_uint64]
+    lib.ag_prefetch_staged_weights.restype = c_int32
     lib.ag_prepare_weights.argtypes = [c_void_p, c_uint64, c_int32]
     lib.ag_prepare_weights.restype = c_int32
     lib.ag_release_weights.argtypes = [c_void_p]

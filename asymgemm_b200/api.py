@@ -24,7 +24,7 @@ from . import _lib
 
 _MK_ALIGNMENT = 128
 _state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0, "fp8_ue8m0": False,
-          "weight_path": "stream", "stage_bytes": 128 << 20}
+          "weight_path": "stream", "stage_bytes": 128 << 20, "stage_slots": 2}
 _scratch_cache: dict = {}
 _stager_cache: dict = {}
 _status_cache: dict = {}
@@ -75,13 +75,14 @@ def set_split_segments(flag: bool) -> None:
     _state["no_split"] = 0 if flag else 1
 
 
-def set_weight_path(path: str, chunk_bytes: Optional[int] = None) -> None:
+def set_weight_path(path: str, chunk_bytes: Optional[int] = None, slots: Optional[int] = None) -> None:
     """How host-resident weights reach the GPU (extension; weights already in HBM are unaffected).
 
     "stream" (default): the GEMM kernel reads pinned memory itself and fetches only the experts that received rows.
     "staged": the copy engine moves every expert, about `chunk_bytes` (default 128 MiB) of whole experts at a time, into
     a double buffer in HBM while the grouped GEMM of the previous chunk runs from there (`stage` of the C descriptor; this
-    module owns one such buffer per device); same results, a few percent
+    module owns one such buffer per device; `slots` > 2 makes it a ring of that many chunks, which lets
+    `prefetch_weights` bank more of the next call's weights while the link would otherwise idle); same results, a few percent
     more of the link, for calls in which (nearly) all experts are active.
     "auto": staged for calls that can have rows for every expert (contiguous: at least 128 rows of `a` per expert, the
     padded size of one active expert; masked: `expected_m` >= 8) over at least 256 MiB of weights, the in-kernel stream
@@ -95,10 +96,29 @@ def set_weight_path(path: str, chunk_bytes: Optional[int] = None) -> None:
     if chunk_bytes is not None:
         _require(int(chunk_bytes) > 0, "chunk_bytes must be positive")
         _state["stage_bytes"] = int(chunk_bytes)
+    if slots is not None:
+        _require(2 <= int(slots) <= 8, "slots must be 2 .. 8")
+        _state["stage_slots"] = int(slots)
 
 
 def get_weight_path() -> str:
     return _state["weight_path"]
+
+
+def prefetch_weights(b: torch.Tensor, device: Union[torch.device, int, None] = None) -> None:
+    """With the "staged" weight path: start copying the first chunks of the host-resident weights `b` into the staging
+    buffer now, ahead of the operator call that will use them (the next layer's weights while this layer's results are
+    still being exchanged and combined). The next staged call on the same `b` does not copy them again. Does nothing for
+    the other weight paths and for weights on the GPU. The weights must not change between this call and that one."""
+    if _state["weight_path"] != "staged" or b.is_cuda:
+        return
+    _require(b.dim() == 3 and b.is_contiguous() and b.is_pinned(), "weights must be a contiguous pinned [G, N, K] tensor")
+    dev = torch.device("cuda", torch.cuda.current_device() if device is None else (device if isinstance(device, int) else device.index))
+    g = int(b.shape[0])
+    stage, slot_bytes = _stage_buffer(b, g, dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().ag_prefetch_staged_weights(b.data_ptr(), b.numel() * b.element_size() // g, g,
+                                                          stage.data_ptr(), stage.numel(), slot_bytes))
 
 
 def prepare_weights(b: torch.Tensor, read_only: bool = False) -> torch.Tensor:
@@ -256,12 +276,14 @@ def _use_staging(b: torch.Tensor, g: int, rows: int, layout: int, raw_dump) -> b
     return rows >= _AUTO_ROWS_PER_EXPERT[layout] * g and b.numel() * b.element_size() >= _AUTO_MIN_WEIGHT_BYTES
 
 
-def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor:
-    """Double buffer in HBM for the staged weight path, one per device, sized for two chunks of whole experts of `b`.
-    The library orders the copies into it after the GEMMs of earlier calls that read it, on whichever stream they ran."""
+def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> Tuple[torch.Tensor, int]:
+    """(ring buffer in HBM for the staged weight path, bytes of one slot): one buffer per device, `stage_slots` slots of
+    one chunk of whole experts of `b` each. The library orders the copies into it after the GEMMs of earlier calls that
+    read it, on whichever stream they ran."""
     group_bytes = b.numel() * b.element_size() // g
     chunk = max(1, min(g, _state["stage_bytes"] // max(1, group_bytes)))
-    need = 2 * (chunk * group_bytes + 1023) // 1024 * 1024 + 2048
+    slot = (chunk * group_bytes + 1023) // 1024 * 1024
+    need = _state["stage_slots"] * slot
     t = _stager_cache.get(device.index)
     if t is None or t.numel() < need + 1024:
         # a buffer that is replaced goes back to the allocator only after the GEMMs that read it: wait for them here
@@ -270,7 +292,7 @@ def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> torch.Tensor
         t = torch.empty(need + 1024, dtype=torch.uint8, device=device)
         _stager_cache[device.index] = t
     off = (-t.data_ptr()) % 1024
-    return t[off:off + need]
+    return t[off:off + need], slot
 
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
@@ -280,11 +302,12 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
     launches on the current stream of a's device (csrc/torch_ops.cpp). `rows_hint`: rows the call is expected to
     multiply (masked layout: expected_m * groups; contiguous: m), for the "auto" weight path."""
     dev = a.device
-    stage = _stage_buffer(b, g, dev) if _use_staging(b, g, m if rows_hint is None else rows_hint, layout, raw_dump) else None
+    stage, slot_bytes = (_stage_buffer(b, g, dev) if _use_staging(b, g, m if rows_hint is None else rows_hint, layout, raw_dump)
+                         else (None, 0))
     op = _lib.torch_ops().m_grouped_gemm_nt
     with torch.cuda.device(dev):
         op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
-           _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage)
+           _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage, slot_bytes)
 
 
 def _check_index_tensors(offsets, experts, g):

@@ -244,52 +244,101 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
 
 // Copy stream and hand-over events of the staged weight path, one set per device, created on first use and kept for
 // the life of the process. `free_[j]` is recorded after the GEMM that read half j, `ready[j]` after the copy into it.
+constexpr int kMaxStageSlots = 8;
+
 struct StageState {
   cudaStream_t copy = nullptr;
-  cudaEvent_t ready[2] = {nullptr, nullptr};
-  cudaEvent_t free_[2] = {nullptr, nullptr};
+  cudaEvent_t ready[kMaxStageSlots] = {};
+  cudaEvent_t free_[kMaxStageSlots] = {};
+  // chunks a prefetch has already put (or is putting) into the halves, for the next staged call on the same operands
+  const void* pf_b = nullptr;
+  void* pf_stage = nullptr;
+  uint64_t pf_expert_bytes = 0;
+  uint64_t pf_slot_bytes = 0;
+  int pf_slots = 0;
+  int pf_count = 0;
 };
+
+// The buffer as a ring of equal slots, each holding one chunk of whole experts.
+struct StageRing {
+  uint64_t slot_bytes;
+  int slots;
+  int chunk;   // experts per slot
+};
+
+int stage_ring(uint64_t stage_bytes, uint64_t chunk_bytes, uint64_t expert_bytes, int num_groups, StageRing* r) {
+  uint64_t slot = chunk_bytes > 0 ? chunk_bytes : stage_bytes / 2;
+  if (slot > stage_bytes / 2) slot = stage_bytes / 2;
+  slot &= ~static_cast<uint64_t>(1023);
+  AG_REQUIRE(slot >= expert_bytes, "the staging buffer (%llu bytes, slots of %llu) must hold at least two slots of one %llu-byte expert",
+             static_cast<unsigned long long>(stage_bytes), static_cast<unsigned long long>(slot), static_cast<unsigned long long>(expert_bytes));
+  const uint64_t n = stage_bytes / slot;
+  r->slot_bytes = slot;
+  r->slots = static_cast<int>(n < static_cast<uint64_t>(kMaxStageSlots) ? n : kMaxStageSlots);
+  r->chunk = static_cast<int>(slot / expert_bytes < static_cast<uint64_t>(num_groups) ? slot / expert_bytes : num_groups);
+  return AG_OK;
+}
 std::mutex g_stage_mu;
 StageState g_stage[64];
+
+int stage_state(StageState** out) {
+  int dev = 0;
+  AG_CUDA(cudaGetDevice(&dev));
+  AG_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  StageState& st = g_stage[dev];
+  if (st.copy == nullptr) {
+    AG_CUDA(cudaStreamCreateWithFlags(&st.copy, cudaStreamNonBlocking));
+    for (int j = 0; j < kMaxStageSlots; ++j) {
+      AG_CUDA(cudaEventCreateWithFlags(&st.ready[j], cudaEventDisableTiming));
+      AG_CUDA(cudaEventCreateWithFlags(&st.free_[j], cudaEventDisableTiming));
+    }
+  }
+  *out = &st;
+  return AG_OK;
+}
+
+// Copy of chunk `i` (experts [lo, lo + cnt)) into its slot of the ring, ordered after the GEMM that last read the slot.
+int stage_copy(StageState& st, const void* b, void* stage, const StageRing& ring, uint64_t expert_bytes, int i, int lo, int cnt) {
+  const int j = i % ring.slots;
+  char* dst = static_cast<char*>(stage) + static_cast<uint64_t>(j) * ring.slot_bytes;
+  AG_CUDA(cudaStreamWaitEvent(st.copy, st.free_[j], 0));   // an event never recorded yet does not block
+  AG_CUDA(cudaMemcpyAsync(dst, static_cast<const char*>(b) + static_cast<uint64_t>(lo) * expert_bytes,
+                          static_cast<uint64_t>(cnt) * expert_bytes, cudaMemcpyDefault, st.copy));
+  AG_CUDA(cudaEventRecord(st.ready[j], st.copy));
+  return AG_OK;
+}
 
 // The grouped GEMM as a series of launches over chunks of whole experts that the copy engine brings into `g->stage`.
 // The lock is held for the whole series: the events of one device then always belong to one call at a time, and the
 // copies of a call wait for the GEMMs of the previous call that read the same half.
 int run_staged(int kind, const ag_gemm_desc_t* g, uint64_t expert_bytes) {
   AG_REQUIRE((reinterpret_cast<uintptr_t>(g->stage) & 1023) == 0, "stage must be 1024-byte aligned");
-  const uint64_t half = (g->stage_bytes / 2) & ~static_cast<uint64_t>(1023);
-  AG_REQUIRE(half >= expert_bytes, "stage_bytes (%llu) must hold two experts of %llu bytes each",
-             static_cast<unsigned long long>(g->stage_bytes), static_cast<unsigned long long>(expert_bytes));
+  StageRing ring;
+  if (int rc = stage_ring(g->stage_bytes, g->stage_chunk_bytes, expert_bytes, g->num_groups, &ring)) return rc;
   const void* stage_alias = nullptr;
   AG_REQUIRE(classify(g->stage, &stage_alias) == RES_DEVICE, "stage must be device memory");
-  int dev = 0;
-  AG_CUDA(cudaGetDevice(&dev));
-  AG_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
   std::lock_guard<std::mutex> lk(g_stage_mu);
-  StageState& st = g_stage[dev];
-  if (st.copy == nullptr) {
-    AG_CUDA(cudaStreamCreateWithFlags(&st.copy, cudaStreamNonBlocking));
-    for (int j = 0; j < 2; ++j) {
-      AG_CUDA(cudaEventCreateWithFlags(&st.ready[j], cudaEventDisableTiming));
-      AG_CUDA(cudaEventCreateWithFlags(&st.free_[j], cudaEventDisableTiming));
-    }
-  }
+  StageState* stp = nullptr;
+  if (int rc = stage_state(&stp)) return rc;
+  StageState& st = *stp;
   cudaStream_t stream = static_cast<cudaStream_t>(g->stream);
-  const int chunk = static_cast<int>(half / expert_bytes < static_cast<uint64_t>(g->num_groups) ? half / expert_bytes : g->num_groups);
+  // chunks a matching ag_prefetch_staged_weights has already issued are not copied again
+  const bool hit = st.pf_b == g->b && st.pf_stage == g->stage && st.pf_expert_bytes == expert_bytes &&
+                   st.pf_slot_bytes == ring.slot_bytes && st.pf_slots == ring.slots;
+  const int prefetched = hit ? st.pf_count : 0;
+  st.pf_b = nullptr;
+  st.pf_count = 0;
   ag_gemm_desc_t c = *g;
   c.stage = nullptr;
-  for (int lo = 0, i = 0; lo < g->num_groups; lo += chunk, ++i) {
-    const int j = i & 1;
-    const int cnt = g->num_groups - lo < chunk ? g->num_groups - lo : chunk;
-    char* dst = static_cast<char*>(g->stage) + static_cast<uint64_t>(j) * half;
-    AG_CUDA(cudaStreamWaitEvent(st.copy, st.free_[j], 0));   // an event never recorded yet does not block
-    AG_CUDA(cudaMemcpyAsync(dst, static_cast<const char*>(g->b) + static_cast<uint64_t>(lo) * expert_bytes,
-                            static_cast<uint64_t>(cnt) * expert_bytes, cudaMemcpyDefault, st.copy));
-    AG_CUDA(cudaEventRecord(st.ready[j], st.copy));
+  for (int lo = 0, i = 0; lo < g->num_groups; lo += ring.chunk, ++i) {
+    const int j = i % ring.slots;
+    const int cnt = g->num_groups - lo < ring.chunk ? g->num_groups - lo : ring.chunk;
+    if (i >= prefetched)
+      if (int rc = stage_copy(st, g->b, g->stage, ring, expert_bytes, i, lo, cnt)) return rc;
     AG_CUDA(cudaStreamWaitEvent(stream, st.ready[j], 0));
-    c.b = dst;
+    c.b = static_cast<char*>(g->stage) + static_cast<uint64_t>(j) * ring.slot_bytes;
     const int rc = run(kind, &c, lo, cnt);
-    AG_CUDA(cudaEventRecord(st.free_[j], stream));   // also after a failed launch: the half is not in use then
+    AG_CUDA(cudaEventRecord(st.free_[j], stream));   // also after a failed launch: the slot is not in use then
     if (rc != AG_OK) return rc;
   }
   return AG_OK;
@@ -392,6 +441,34 @@ namespace {
 std::mutex g_reg_mu;
 void* g_registered[256] = {};   // host ranges registered by ag_prepare_weights, by start address
 }  // namespace
+
+int ag_prefetch_staged_weights(const void* b, uint64_t expert_bytes, int32_t num_groups, void* stage, uint64_t stage_bytes,
+                               uint64_t stage_chunk_bytes) {
+  AG_REQUIRE(b != nullptr && stage != nullptr && expert_bytes > 0 && num_groups > 0, "bad arguments");
+  AG_REQUIRE((reinterpret_cast<uintptr_t>(stage) & 1023) == 0, "stage must be 1024-byte aligned");
+  StageRing ring;
+  if (int rc = stage_ring(stage_bytes, stage_chunk_bytes, expert_bytes, num_groups, &ring)) return rc;
+  const void* alias = nullptr;
+  if (classify(b, &alias) != RES_HOST_MAPPED) return AG_OK;   // weights already on the device: nothing to stage
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  StageState* stp = nullptr;
+  if (int rc = stage_state(&stp)) return rc;
+  StageState& st = *stp;
+  st.pf_b = nullptr;
+  st.pf_count = 0;
+  int i = 0;
+  for (int lo = 0; lo < num_groups && i < ring.slots; lo += ring.chunk, ++i) {
+    const int cnt = num_groups - lo < ring.chunk ? num_groups - lo : ring.chunk;
+    if (int rc = stage_copy(st, b, stage, ring, expert_bytes, i, lo, cnt)) return rc;
+  }
+  st.pf_b = b;
+  st.pf_stage = stage;
+  st.pf_expert_bytes = expert_bytes;
+  st.pf_slot_bytes = ring.slot_bytes;
+  st.pf_slots = ring.slots;
+  st.pf_count = i;
+  return AG_OK;
+}
 
 int ag_prepare_weights(void* ptr, uint64_t bytes, int32_t read_only) {
   AG_REQUIRE(ptr != nullptr && bytes > 0, "ptr must be non-NULL and bytes positive");

@@ -110,6 +110,7 @@ int ag_m_grouped_fp8_gemm_nt_static_scratch(const ag_gemm_desc_t* desc) {
   g.scratch_bytes = usable;
   g.stage = nullptr;  // staging would create a stream and events on first use: this entry point reads b in the kernel
   g.stage_bytes = 0;
+  g.stage_chunk_bytes = 0;
   g.tile_config = tile + 1;
   return agb_run_desc(1, &g);
 }

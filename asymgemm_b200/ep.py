@@ -404,6 +404,9 @@ class ExpertParallelMoE:
         self.hidden, self.inter = hidden, inter
         self.w13, self.w2 = w13, w2
         self._weight_views: dict = {}
+        # staged weight path only: weights whose first chunks are copied while this layer's results travel home (the next
+        # layer's gate+up weights in a model; this layer's own when it is called in a loop). None = no prefetch.
+        self.prefetch_next: Optional[torch.Tensor] = None
         epr = self.dispatcher.experts_per_rank
         if tuple(w13[0].shape) != (epr, 2 * inter, hidden) or tuple(w2[0].shape) != (epr, hidden, inter):
             raise RuntimeError("weight shapes do not match (experts_per_rank, 2*inter, hidden) / (experts_per_rank, hidden, inter)")
@@ -459,4 +462,7 @@ class ExpertParallelMoE:
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)
         out = self.experts_forward(a_q, sfa, state)
+        if self.prefetch_next is not None and out.is_cuda:
+            from . import api
+            api.prefetch_weights(self.prefetch_next, out.device)
         return self.dispatcher.combine(out, state, topk_weights)

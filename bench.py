@@ -361,6 +361,9 @@ def main():
                          "regime); staged: B in pinned host memory, copied chunk by chunk into an HBM double buffer by the copy engine "
                          "(set_weight_path) -- the alternative the in-kernel stream is compared with")
     ap.add_argument("--stage-mb", type=int, default=128, help="--weights staged: size of one staged chunk of whole experts, MiB")
+    ap.add_argument("--stage-slots", type=int, default=2,
+                    help="--weights staged: slots of the staging ring (2 = double buffer); more slots let the MoE layer's prefetch bank "
+                         "more weight bytes while tokens are exchanged")
     ap.add_argument("--d-host", action="store_true", help="end-to-end leg: let the kernel write D straight into pinned host memory")
     ap.add_argument("--fp8-scales", default="fp32", choices=["fp32", "ue8m0"],
                     help="fp32 (default): arbitrary fp32 block scales applied exactly in the TMEM drain; ue8m0: power-of-two scales "
@@ -451,9 +454,13 @@ def main():
         w["host_bytes"] = streamed * w["n"] * w["k"] * ELEM_BYTES[cfg["kind"]]
         config["hot_expert_cache"] = f"{len(cache.cached)} most popular experts resident in HBM, {streamed} streamed from the host"
     if args.weights == "staged":
-        ag.set_weight_path("staged", chunk_bytes=args.stage_mb << 20)
+        ag.set_weight_path("staged", chunk_bytes=args.stage_mb << 20, slots=args.stage_slots)
+        if moe and args.pipeline_groups <= 1:
+            # the layer is called in a loop: the first chunks of its gate+up weights are copied while the previous step's
+            # results are combined and this step's tokens are routed (a model would prefetch the next layer's weights)
+            w["layer"].prefetch_next = w["layer"].w13[0]
         config["staged"] = (f"weights cross the link through the copy engine, about {args.stage_mb} MiB of whole experts per chunk "
-                            "into a double buffer in HBM; the grouped GEMM of a chunk runs from HBM while the next chunk is copied; every expert "
+                            f"into a ring of {args.stage_slots} slots in HBM; the grouped GEMM of a chunk runs from HBM while the next chunks are copied; every expert "
                             "is copied, the reported GB/s count the active experts' bytes only")
     if args.fp8_scales == "ue8m0":
         ag.set_fp8_scale_mode("ue8m0")

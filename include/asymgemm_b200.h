@@ -89,7 +89,11 @@ typedef struct ag_gemm_desc {
      (asym_gemm/unified_moe/runtime.py:110-200). The buffer belongs to the library from the first call that names it
      until the last such call has finished on the GPU; such a call cannot be captured into a CUDA graph. */
   void* stage;          /* device, 1024-byte aligned; NULL = the kernel reads b itself (default) */
-  uint64_t stage_bytes; /* at least 2 * N * K bytes of one expert (+ alignment); half of it holds one chunk */
+  uint64_t stage_bytes; /* at least two slots of one expert (N * K bytes) each */
+  uint64_t stage_chunk_bytes; /* bytes of one slot = one chunk of whole experts; 0 = stage_bytes / 2 (a double buffer).
+                                 With a smaller value the buffer is a ring of up to 8 slots: the copies then run further
+                                 ahead of the GEMMs, which matters when a prefetch (below) fills the ring while other
+                                 work keeps the link idle. */
 } ag_gemm_desc_t;
 
 /* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked
@@ -166,6 +170,17 @@ int32_t ag_get_mk_alignment_for_contiguous_layout(void);
  * Replaces get_mn_major_tma_aligned_packed_byte_sf_tensor (csrc/apis/layout.hpp:14-35). */
 uint64_t ag_fp4_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t k16);
 int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t rows, int64_t k16, void* stream);
+
+/* Starts the copy-engine transfer of the first chunks (as many as the ring has slots) of host-resident weights `b` ([num_groups] experts of
+ * `expert_bytes` each) into `stage` ahead of the staged call that will use them -- typically the next layer's weights
+ * while this layer's results are still being combined, so that the link does not idle between GEMMs. The next call
+ * whose descriptor names the same `b`, `stage`, `stage_bytes` and `stage_chunk_bytes` skips those copies; any other staged call simply
+ * overwrites them. The caller must not change the weights between the prefetch and that call. Returns at once (the
+ * copies run on the library's copy stream); a no-op for device-resident `b`. Reference counterpart: the unified runtime
+ * issues its staging copies "now", on a side stream, before the work that hides them
+ * (asym_gemm/unified_moe/runtime.py:1844-1848). */
+int ag_prefetch_staged_weights(const void* b, uint64_t expert_bytes, int32_t num_groups, void* stage, uint64_t stage_bytes,
+                               uint64_t stage_chunk_bytes);
 
 /* Makes an ordinary host allocation (malloc, mmap, a framework's pageable tensor) usable as `b`: page-locks and maps
  * [ptr, ptr + bytes) for the current device's context with cudaHostRegister (portable, mapped; read_only != 0 adds the

@@ -126,12 +126,13 @@ def test_random_case_staged_weights(seed):
             c = H.make_contiguous_case(kind, counts, n, k, seed=seed, b_on_host=True)
             d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
             rows_total = c["m_total"]
-        ag.set_weight_path("staged", chunk_bytes=chunk * (c["b"].numel() * c["b"].element_size() // len(counts)))
+        ag.set_weight_path("staged", chunk_bytes=chunk * (c["b"].numel() * c["b"].element_size() // len(counts)),
+                           slots=rng.randint(2, 8))
         (_run_masked if masked else _run_contiguous)(c, d)
         ag.check_status()
     finally:
         ag.set_tile_config(0)
-        ag.set_weight_path("stream", chunk_bytes=128 << 20)
+        ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
     d_np = d.float().cpu().numpy().reshape(rows_total, n)
     info = f"kind={kind} masked={masked} counts={counts} n={n} k={k} tile={tile} chunk={chunk}"
     try:

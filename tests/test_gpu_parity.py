@@ -424,7 +424,7 @@ def test_staged_weight_path_matches_in_kernel_stream(kind, layout):
     run(c, plain)
     group_bytes = c["b"].numel() * c["b"].element_size() // 5
     api._stager_cache.clear()
-    ag.set_weight_path("staged", chunk_bytes=2 * group_bytes + 1)          # chunks of 2, 2 and 1 experts
+    ag.set_weight_path("staged", chunk_bytes=2 * group_bytes + 1, slots=2 if layout == "contiguous" else 3)   # chunks of 2, 2, 1 experts
     try:
         assert ag.get_weight_path() == "staged"
         for _ in range(2):
@@ -448,7 +448,7 @@ def test_staged_weight_path_matches_in_kernel_stream(kind, layout):
             torch.cuda.synchronize()
             assert torch.equal(hw.view(torch.int16), hw_plain.view(torch.int16))
     finally:
-        ag.set_weight_path("stream", chunk_bytes=128 << 20)
+        ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
     _check(kind, plain.float().cpu().numpy().reshape(-1, 256), c["ref"], c["segments"])
 
 
@@ -474,3 +474,35 @@ def test_prepare_weights_registers_pageable_memory_in_place():
     with pytest.raises(RuntimeError, match="not registered"):
         ag.release_weights(pageable)
     assert ag.prepare_weights(c["b"]) is c["b"]          # already pinned: nothing to do, nothing to release
+
+
+def test_prefetch_of_staged_weights_is_used_or_discarded_correctly():
+    """`prefetch_weights` copies the first chunks early; the next staged call on the same weights must give the plain
+    result, and so must a call on other weights that finds a prefetch it cannot use -- for a double buffer and for rings."""
+    c1 = H.make_contiguous_case("fp8", [300, 40, 0, 900, 129], 256, 512, seed=95)
+    c2 = H.make_contiguous_case("fp8", [10, 700, 64, 0, 200], 256, 512, seed=96)
+    want = []
+    for c in (c1, c2):
+        d = torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda")
+        _run_contiguous(c, d)
+        want.append(d)
+    ag.prefetch_weights(c1["b"])                      # a no-op on the default weight path
+    group_bytes = c1["b"].numel() // 5
+
+    def check_all():
+        for first, second in ((c1, c1), (c1, c2), (c2, c1)):
+            ag.prefetch_weights(first["b"])
+            ag.prefetch_weights(first["b"])           # twice in a row: the second simply copies again
+            for c in (second, first):
+                d = torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda")
+                _run_contiguous(c, d)
+                torch.cuda.synchronize()
+                assert torch.equal(d.view(torch.int16), want[0 if c is c1 else 1].view(torch.int16))
+
+    try:
+        for slots, per_chunk in ((2, 2), (4, 1), (8, 1)):       # 3, 5 and 5 chunks; the ring holds 2, 4 and all of them
+            ag.set_weight_path("staged", chunk_bytes=per_chunk * group_bytes, slots=slots)
+            check_all()
+    finally:
+        ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
+    ag.check_status()
