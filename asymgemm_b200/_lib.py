@@ -91,6 +91,7 @@ EXPORTS = [
     "ag_quant_rows_int8",
     "ag_silu_mul_quant_int8",
     "ag_combine_topk_f32",
+    "ag_gemm_desc_size",
     "ag_last_error",
     "ag_version",
 ]
@@ -160,6 +161,11 @@ def load() -> ctypes.CDLL:
     lib.ag_release_weights.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]
     lib.ag_measure_host_link.restype = c_int32
+    lib.ag_gemm_desc_size.argtypes = []
+    lib.ag_gemm_desc_size.restype = c_uint64
+    if int(lib.ag_gemm_desc_size()) != ctypes.sizeof(GemmDesc):
+        raise RuntimeError(f"{LIB_PATH} was built from another version of include/asymgemm_b200.h "
+                           f"(descriptor of {int(lib.ag_gemm_desc_size())} bytes, this package expects {ctypes.sizeof(GemmDesc)}): rebuild it")
     lib.ag_last_error.argtypes = []
     lib.ag_last_error.restype = c_char_p
     lib.ag_version.argtypes = []

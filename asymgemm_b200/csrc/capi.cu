@@ -400,6 +400,8 @@ uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms) {
   return static_cast<uint64_t>(sms) * 128 * kpad;
 }
 
+uint64_t ag_gemm_desc_size(void) { return sizeof(ag_gemm_desc_t); }
+
 int ag_read_status(const int32_t* status_dev, void* stream, int32_t* out) {
   const int32_t* src = status_dev != nullptr ? status_dev : default_status_word();
   if (src == nullptr) return fail(AG_E_CUDA, "no status word");

@@ -240,6 +240,10 @@ int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
 int ag_measure_host_stream(uint64_t bytes, int64_t row_bytes, int32_t box_rows, int32_t boxes_per_stage, int32_t num_ctas,
                            int32_t reps, double* gbps_out);
 
+/* sizeof(ag_gemm_desc_t) as this library was compiled: lets a binding written in another language (ctypes, cgo, JNI)
+ * check its mirror of the struct before the first call. */
+uint64_t ag_gemm_desc_size(void);
+
 const char* ag_last_error(void);
 const char* ag_version(void);
 

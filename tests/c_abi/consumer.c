@@ -18,6 +18,7 @@ int main(void) {
 
   bad += expect(ag_version() != NULL && strlen(ag_version()) > 0, "ag_version returns a string");
   bad += expect(ag_get_mk_alignment_for_contiguous_layout() == 128, "contiguous-layout alignment is 128");
+  bad += expect(ag_gemm_desc_size() == sizeof(ag_gemm_desc_t), "the library and this program agree on the descriptor");
   bad += expect(ag_m_grouped_bf16_gemm_nt(NULL) == AG_E_INVALID, "NULL descriptor is refused");
   bad += expect(strstr(ag_last_error(), "desc") != NULL, "the message names the descriptor");
 
