@@ -153,7 +153,7 @@ def load() -> ctypes.CDLL:
     lib.ag_combine_topk_f32.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
-    lib.ag_prefetch_staged_weights.argtypes = [c_void_p, c_uint64, c_int32, c_void_p, c_uint64, c_uint64]
+    lib.ag_prefetch_staged_weights.argtypes = [c_void_p, c_uint64, c_int32, c_void_p, c_uint64, c_uint64, c_void_p, c_int32]
     lib.ag_prefetch_staged_weights.restype = c_int32
     lib.ag_prepare_weights.argtypes = [c_void_p, c_uint64, c_int32]
     lib.ag_prepare_weights.restype = c_int32

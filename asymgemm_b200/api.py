@@ -106,10 +106,13 @@ def get_weight_path() -> str:
 
 
 def prefetch_weights(b: torch.Tensor, device: Union[torch.device, int, None] = None) -> None:
-    """With the "staged" weight path: start copying the first chunks of the host-resident weights `b` into the staging
-    buffer now, ahead of the operator call that will use them (the next layer's weights while this layer's results are
-    still being exchanged and combined). The next staged call on the same `b` does not copy them again. Does nothing for
-    the other weight paths and for weights on the GPU. The weights must not change between this call and that one."""
+    """With the "staged" weight path: start copying the first chunks (as many as the staging ring has slots, see
+    `set_weight_path`) of the host-resident weights `b` into HBM now, ahead of the operator call that will use them -- the
+    next layer's weights while this layer's results are still being exchanged and combined, when the host link would idle
+    otherwise. The next staged call on the same `b` does not copy them again. The copies begin once the work already
+    queued on the current stream has finished. Does nothing on the other weight paths (measured: handing the prefetched
+    experts to the in-kernel stream as a separate launch gains nothing) and for weights on the GPU. The weights must not
+    change between this call and that one."""
     if _state["weight_path"] != "staged" or b.is_cuda:
         return
     _require(b.dim() == 3 and b.is_contiguous() and b.is_pinned(), "weights must be a contiguous pinned [G, N, K] tensor")
@@ -118,7 +121,8 @@ def prefetch_weights(b: torch.Tensor, device: Union[torch.device, int, None] = N
     stage, slot_bytes = _stage_buffer(b, g, dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().ag_prefetch_staged_weights(b.data_ptr(), b.numel() * b.element_size() // g, g,
-                                                          stage.data_ptr(), stage.numel(), slot_bytes))
+                                                          stage.data_ptr(), stage.numel(), slot_bytes,
+                                                          torch.cuda.current_stream(dev).cuda_stream, 1))
 
 
 def prepare_weights(b: torch.Tensor, read_only: bool = False) -> torch.Tensor:

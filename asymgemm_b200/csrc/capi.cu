@@ -250,6 +250,7 @@ struct StageState {
   cudaStream_t copy = nullptr;
   cudaEvent_t ready[kMaxStageSlots] = {};
   cudaEvent_t free_[kMaxStageSlots] = {};
+  cudaEvent_t gate = nullptr;   // "the caller's stream has reached the point of the prefetch call"
   // chunks a prefetch has already put (or is putting) into the halves, for the next staged call on the same operands
   const void* pf_b = nullptr;
   void* pf_stage = nullptr;
@@ -292,6 +293,7 @@ int stage_state(StageState** out) {
       AG_CUDA(cudaEventCreateWithFlags(&st.ready[j], cudaEventDisableTiming));
       AG_CUDA(cudaEventCreateWithFlags(&st.free_[j], cudaEventDisableTiming));
     }
+    AG_CUDA(cudaEventCreateWithFlags(&st.gate, cudaEventDisableTiming));
   }
   *out = &st;
   return AG_OK;
@@ -445,7 +447,7 @@ void* g_registered[256] = {};   // host ranges registered by ag_prepare_weights,
 }  // namespace
 
 int ag_prefetch_staged_weights(const void* b, uint64_t expert_bytes, int32_t num_groups, void* stage, uint64_t stage_bytes,
-                               uint64_t stage_chunk_bytes) {
+                               uint64_t stage_chunk_bytes, void* after_stream, int32_t wait_for_stream) {
   AG_REQUIRE(b != nullptr && stage != nullptr && expert_bytes > 0 && num_groups > 0, "bad arguments");
   AG_REQUIRE((reinterpret_cast<uintptr_t>(stage) & 1023) == 0, "stage must be 1024-byte aligned");
   StageRing ring;
@@ -458,6 +460,12 @@ int ag_prefetch_staged_weights(const void* b, uint64_t expert_bytes, int32_t num
   StageState& st = *stp;
   st.pf_b = nullptr;
   st.pf_count = 0;
+  if (wait_for_stream) {
+    // the copies start when the work already queued on the caller's stream is done, i.e. when the kernels that read
+    // weights over the link themselves have finished and the link would go idle
+    AG_CUDA(cudaEventRecord(st.gate, static_cast<cudaStream_t>(after_stream)));
+    AG_CUDA(cudaStreamWaitEvent(st.copy, st.gate, 0));
+  }
   int i = 0;
   for (int lo = 0; lo < num_groups && i < ring.slots; lo += ring.chunk, ++i) {
     const int cnt = num_groups - lo < ring.chunk ? num_groups - lo : ring.chunk;

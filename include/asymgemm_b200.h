@@ -175,12 +175,14 @@ int ag_fp4_sf_to_blocked(const void* src, void* dst, int64_t groups, int64_t row
  * `expert_bytes` each) into `stage` ahead of the staged call that will use them -- typically the next layer's weights
  * while this layer's results are still being combined, so that the link does not idle between GEMMs. The next call
  * whose descriptor names the same `b`, `stage`, `stage_bytes` and `stage_chunk_bytes` skips those copies; any other staged call simply
- * overwrites them. The caller must not change the weights between the prefetch and that call. Returns at once (the
- * copies run on the library's copy stream); a no-op for device-resident `b`. Reference counterpart: the unified runtime
+ * overwrites them. The caller must not change the weights between the prefetch and that call. With
+ * `wait_for_stream` != 0 the copies start only after the work already queued on `after_stream` (a cudaStream_t) -- for
+ * instance a grouped GEMM that is still reading its own weights over the link -- so that they use idle link time instead
+ * of competing for it. Returns at once (the copies run on the library's copy stream); a no-op for device-resident `b`. Reference counterpart: the unified runtime
  * issues its staging copies "now", on a side stream, before the work that hides them
  * (asym_gemm/unified_moe/runtime.py:1844-1848). */
 int ag_prefetch_staged_weights(const void* b, uint64_t expert_bytes, int32_t num_groups, void* stage, uint64_t stage_bytes,
-                               uint64_t stage_chunk_bytes);
+                               uint64_t stage_chunk_bytes, void* after_stream, int32_t wait_for_stream);
 
 /* Makes an ordinary host allocation (malloc, mmap, a framework's pageable tensor) usable as `b`: page-locks and maps
  * [ptr, ptr + bytes) for the current device's context with cudaHostRegister (portable, mapped; read_only != 0 adds the

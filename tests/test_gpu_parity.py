@@ -486,7 +486,6 @@ def test_prefetch_of_staged_weights_is_used_or_discarded_correctly():
         d = torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda")
         _run_contiguous(c, d)
         want.append(d)
-    ag.prefetch_weights(c1["b"])                      # a no-op on the default weight path
     group_bytes = c1["b"].numel() // 5
 
     def check_all():
@@ -503,6 +502,8 @@ def test_prefetch_of_staged_weights_is_used_or_discarded_correctly():
         for slots, per_chunk in ((2, 2), (4, 1), (8, 1)):       # 3, 5 and 5 chunks; the ring holds 2, 4 and all of them
             ag.set_weight_path("staged", chunk_bytes=per_chunk * group_bytes, slots=slots)
             check_all()
+            ag.set_weight_path("stream", chunk_bytes=per_chunk * group_bytes, slots=slots)
+            check_all()                 # prefetching is a no-op on the in-kernel path
     finally:
         ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
     ag.check_status()
