@@ -83,8 +83,8 @@ typedef struct ag_gemm_desc {
 
   /* Optional copy-engine staging of host-resident b (ignored when b is device memory or raw_dump is set). With a
      non-NULL `stage`, the call does not read b from inside the kernel: it copies as many whole experts as fit in
-     one half of the buffer (cudaMemcpyAsync on a stream of the library's own), runs the grouped GEMM over those experts
-     from the buffer while the next ones are copied into the other half, and so on; same results, every expert of b
+     one slot of the buffer (cudaMemcpyAsync on a stream of the library's own), runs the grouped GEMM over those experts
+     from the buffer while the next ones are copied into the next slot, and so on; same results, every expert of b
      crosses the link whether or not it received rows. The reference stages its streamed weights the same way
      (asym_gemm/unified_moe/runtime.py:110-200). The buffer belongs to the library from the first call that names it
      until the last such call has finished on the GPU; such a call cannot be captured into a CUDA graph. */
