@@ -97,6 +97,64 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   if (lane == 0) sf[row * blocks_per_row + blk] = scale;
 }
 
+// Wide form of quant_rows_kernel for 16-byte aligned rows with cols % 8 == 0: one warp per (row, pair of 128-column
+// blocks), each half-warp owns one block and each lane 8 consecutive columns (16-byte loads, 8-byte stores), so a warp
+// keeps twice the bytes in flight. Per-element arithmetic and the scale are those of quant_rows_kernel, bit for bit.
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                                              float* __restrict__ sf, long long rows, int cols, int blocks_per_row,
+                                                              int pairs_per_row, int pow2_scales) {
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= rows * pairs_per_row) return;
+  const long long row = warp_global / pairs_per_row;
+  const int pair = static_cast<int>(warp_global - row * pairs_per_row);
+  const int blk = pair * 2 + (lane >> 4);
+  const int c0 = blk * 128 + (lane & 15) * 8;
+  const bool live = blk < blocks_per_row && c0 < cols;       // cols % 8 == 0: a lane's 8 columns are all in or all out
+  const int in_cols = MODE == 1 ? 2 * cols : cols;
+  const __nv_bfloat16* xr = x + row * in_cols;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    const uint4 g = *reinterpret_cast<const uint4*>(xr + c0);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __low2float(gp[i]);
+      v[2 * i + 1] = __high2float(gp[i]);
+    }
+    if (MODE == 1) {
+      const uint4 u = *reinterpret_cast<const uint4*>(xr + cols + c0);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float u0 = __low2float(up[i]), u1 = __high2float(up[i]);
+        const float s0 = v[2 * i] / (1.0f + expf(-v[2 * i]));
+        const float s1 = v[2 * i + 1] / (1.0f + expf(-v[2 * i + 1]));
+        v[2 * i] = __bfloat162float(__float2bfloat16_rn(s0 * u0));
+        v[2 * i + 1] = __bfloat162float(__float2bfloat16_rn(s1 * u1));
+      }
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half-warp
+  amax = fmaxf(amax, 1e-4f);
+  float scale = amax * (1.0f / kFp8Max);
+  if (pow2_scales) scale = ceil_pow2(scale);
+  const float inv = 1.0f / scale;
+  if (live) {
+    const float lo[4] = {v[0], v[1], v[2], v[3]}, hi[4] = {v[4], v[5], v[6], v[7]};
+    uint2 packed;
+    packed.x = quantise4(lo, inv);
+    packed.y = quantise4(hi, inv);
+    *reinterpret_cast<uint2*>(q + row * cols + c0) = packed;
+  }
+  if ((lane & 15) == 0 && blk < blocks_per_row) sf[row * blocks_per_row + blk] = scale;
+}
+
 // dst[dst_rows ? dst_rows[i] : i] = src[src_rows ? src_rows[i] : i] for i < rows; one warp per row, 16-byte vectors.
 __global__ void __launch_bounds__(256) move_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                         const long long* __restrict__ src_rows, const long long* __restrict__ dst_rows,
@@ -201,6 +259,13 @@ int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int6
   if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || cols % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   const int bpr = static_cast<int>((cols + 127) / 128);
+  if (cols % 8 == 0 && aligned16(x_bf16) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
+    const int ppr = (bpr + 1) / 2;
+    const long long wide = rows * ppr;
+    agb::quant_rows_wide_kernel<0><<<static_cast<unsigned>((wide + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, ppr, pow2_scales);
+    return launch_check();
+  }
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<0><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales);
@@ -211,6 +276,13 @@ int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t 
   if (!gate_up_bf16 || !q || !sf || rows < 0 || inter <= 0 || inter % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (inter must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   const int bpr = static_cast<int>((inter + 127) / 128);
+  if (inter % 8 == 0 && aligned16(gate_up_bf16) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
+    const int ppr = (bpr + 1) / 2;
+    const long long wide = rows * ppr;
+    agb::quant_rows_wide_kernel<1><<<static_cast<unsigned>((wide + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, ppr, pow2_scales);
+    return launch_check();
+  }
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<1><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, pow2_scales);

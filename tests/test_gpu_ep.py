@@ -179,6 +179,34 @@ def test_helper_kernels_match_torch():
     assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
 
 
+def test_wide_quantiser_kernels_equal_the_narrow_ones():
+    """Rows that are 16-byte aligned take the wide kernels (16-byte loads, two 128-column blocks per warp); the same data at
+    an address that is only 8-byte aligned takes the narrow ones. Values and scales must agree bit for bit."""
+    from asymgemm_b200 import moe_ops
+    gen = torch.Generator(device="cuda").manual_seed(7)
+
+    def misaligned(t):
+        flat = torch.empty(t.numel() + 4, dtype=t.dtype, device=t.device)
+        view = flat[4:].view(t.shape)
+        view.copy_(t)
+        assert view.data_ptr() % 16 == 8 and t.data_ptr() % 16 == 0 and view.is_contiguous()
+        return view
+
+    for rows, cols in ((333, 640), (64, 128), (17, 1000), (5, 7168)):          # odd block counts, a ragged last block
+        x = (torch.randn((rows, cols), device="cuda", generator=gen) * 3).to(torch.bfloat16)
+        x[rows // 2] = 0
+        for pow2 in (False, True):
+            q1, s1 = moe_ops.quant_rows_fp8(x, pow2_scales=pow2)
+            q2, s2 = moe_ops.quant_rows_fp8(misaligned(x), pow2_scales=pow2)
+            assert torch.equal(s1, s2) and torch.equal(q1.view(torch.uint8), q2.view(torch.uint8)), (rows, cols, pow2)
+    for rows, inter in ((257, 384), (33, 128), (9, 2048), (21, 200)):
+        gu = (torch.randn((rows, 2 * inter), device="cuda", generator=gen) * 2).to(torch.bfloat16)
+        for pow2 in (False, True):
+            q1, s1 = moe_ops.silu_mul_quant_fp8(gu, inter, pow2_scales=pow2)
+            q2, s2 = moe_ops.silu_mul_quant_fp8(misaligned(gu), inter, pow2_scales=pow2)
+            assert torch.equal(s1, s2) and torch.equal(q1.view(torch.uint8), q2.view(torch.uint8)), (rows, inter, pow2)
+
+
 def test_pow2_quantiser_and_hardware_scaled_layer():
     """Row quantiser with power-of-two scales against the torch quantiser with use_ue8m0=True, and the MoE layer on the
     hardware-scaled FP8 path against the same layer on the exact path (same inputs, weights quantised with UE8M0 scales)."""
