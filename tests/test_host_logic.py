@@ -232,3 +232,44 @@ def test_plain_c_program_compiles_against_the_header_and_links():
         res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "c_abi consumer: ok" in res.stdout
+
+
+def test_expert_range_and_layout_invariants_random():
+    """Random link rates and routing counts: the ranges always tile the experts with one non-empty range per rank and
+    never make the slowest finisher worse than the even split; the device-built layout puts every received row in its
+    expert's 128-aligned segment exactly once."""
+    import random
+    from asymgemm_b200.ep import EPDispatcher, proportional_expert_ranges
+    rng = random.Random(11)
+    for _ in range(200):
+        world = rng.randint(1, 8)
+        experts = rng.randint(world, 64)
+        rates = [rng.uniform(5.0, 60.0) for _ in range(world)]
+        ranges = proportional_expert_ranges(rates, experts)
+        assert ranges[0][0] == 0 and ranges[-1][1] == experts
+        assert all(hi > lo for lo, hi in ranges) and all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+        even = [(r * experts // world, (r + 1) * experts // world) for r in range(world)]
+        finish = lambda rr: max((hi - lo) / rate for (lo, hi), rate in zip(rr, rates))
+        assert finish(ranges) <= finish(even) * (1 + 1e-9) + 1.0 / min(rates)       # at most one expert's time worse
+    disp = EPDispatcher(6)                    # one rank owning six experts
+    for _ in range(50):
+        world_src = rng.randint(1, 4)
+        counts = torch.tensor([[rng.choice([0, 0, 1, 5, 130, 257]) for _ in range(6)] for _ in range(world_src)], dtype=torch.int32)
+        total = int(counts.sum())
+        dest, per_expert, bound, offsets, experts_t = disp.layout(counts, total)
+        assert per_expert.tolist() == counts.sum(dim=0).tolist() and experts_t.tolist() == [0, 1, 2, 3, 4, 5, -1]
+        off = offsets.view(-1, 2).tolist()
+        assert all(s % 128 == 0 and e % 128 == 0 and e - s >= n for (s, e), n in zip(off, per_expert.tolist()))
+        assert all(off[i][1] == off[i + 1][0] for i in range(5)) and (total == 0 or off[-1][1] <= bound)
+        # rows arrive ordered by (source rank, expert): row i of expert j from source s lands inside expert j's segment
+        assert len(set(dest.tolist())) == total
+        pos = 0
+        seen = [0] * 6
+        for s in range(world_src):
+            for j in range(6):
+                for _ in range(int(counts[s, j])):
+                    d = int(dest[pos])
+                    assert off[j][0] <= d < off[j][0] + int(per_expert[j])
+                    seen[j] += 1
+                    pos += 1
+        assert seen == per_expert.tolist()
