@@ -72,6 +72,7 @@ EXPORTS = [
     "ag_fp8_sf_to_blocked_ue8m0",
     "ag_static_scratch_bytes",
     "ag_scratch_bytes",
+    "ag_scratch_bytes_for",
     "ag_read_status",
     "ag_set_num_sms",
     "ag_get_num_sms",
@@ -119,6 +120,8 @@ def load() -> ctypes.CDLL:
     lib.ag_static_scratch_bytes.restype = c_uint64
     lib.ag_scratch_bytes.argtypes = [c_int32, c_int64, c_int64, c_int32]
     lib.ag_scratch_bytes.restype = c_uint64
+    lib.ag_scratch_bytes_for.argtypes = [c_int32, POINTER(GemmDesc), POINTER(c_uint64)]
+    lib.ag_scratch_bytes_for.restype = c_int32
     lib.ag_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
     lib.ag_read_status.restype = c_int32
     lib.ag_set_num_sms.argtypes = [c_int32]

@@ -15,6 +15,8 @@ Differences from the reference, all on the permissive side:
 """
 from __future__ import annotations
 
+import contextlib
+import threading
 import weakref
 from typing import Optional, Tuple, Union
 
@@ -25,6 +27,7 @@ from . import _lib
 _MK_ALIGNMENT = 128
 _state = {"timeout_ms": 0, "use_scratch": True, "tile_config": 0, "no_split": 0, "fp8_ue8m0": False,
           "weight_path": "stream", "stage_bytes": 128 << 20, "stage_slots": 2}
+_call_caps = threading.local()
 _scratch_cache: dict = {}
 _stager_cache: dict = {}
 _status_cache: dict = {}
@@ -48,6 +51,19 @@ def set_num_sms(num_sms: int) -> None:
 
 def get_num_sms() -> int:
     return int(_lib.load().ag_get_num_sms())
+
+
+@contextlib.contextmanager
+def launch_sm_cap(num_sms: int):
+    """Within the block, every operator call of this thread launches at most `num_sms` CTAs (`num_sms` of the C
+    descriptor). Unlike `set_num_sms` this touches no process-wide state: other threads, other devices and calls after
+    the block are unaffected. 0 or None leaves the calls alone."""
+    prev = getattr(_call_caps, "num_sms", 0)
+    _call_caps.num_sms = int(num_sms) if num_sms else 0
+    try:
+        yield
+    finally:
+        _call_caps.num_sms = prev
 
 
 def set_wait_limit_ms(ms: int) -> None:
@@ -311,7 +327,8 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
     op = _lib.torch_ops().m_grouped_gemm_nt
     with torch.cuda.device(dev):
         op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
-           _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage, slot_bytes)
+           _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage, slot_bytes,
+           getattr(_call_caps, "num_sms", 0))
 
 
 def _check_index_tensors(offsets, experts, g):

@@ -123,6 +123,53 @@ uint64_t k_bytes_of(int kind, int64_t k) {
   }
 }
 
+// Everything about a launch that follows from the descriptor and from where b lives: tile configuration, grid, whether
+// long segments are split into row chunks, and the scratch a replay of long segments would use. run() and the
+// scratch-size queries share it, so that they cannot drift apart.
+struct LaunchPlan {
+  int tile = 0, bn = 0, ka = 0;
+  int n_tiles = 0, kb_count = 0;
+  int split_rows = 0;        // > 0: device-resident b, segments are cut into chunks of this many rows (no item ever replays)
+  int grid = 0;
+  uint64_t kpad = 0;         // bytes of one scratch row: K bytes padded to whole weight stages
+  uint64_t scratch_need = 0; // 0 = this launch has no use for scratch
+};
+
+int plan_launch(int kind, const ag_gemm_desc_t* g, bool host_b, LaunchPlan* out) {
+  LaunchPlan pl;
+  const bool masked = g->layout == AG_LAYOUT_MASKED;
+  const int64_t rows_total = masked ? g->m * g->num_groups : g->m;
+  int sms = 0;
+  if (int rc = device_sm_count(&sms)) return rc;
+  const int cap = g->num_sms > 0 ? g->num_sms : g_num_sms.load();
+  const int grid_cap = cap > 0 && cap < sms ? cap : sms;
+  pl.tile = g->tile_config > 0 ? g->tile_config - 1 : agb::default_tile(kind, host_b);
+  AG_REQUIRE(pl.tile >= 0 && pl.tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
+  AG_REQUIRE(agb::tile_supported(kind, pl.tile), "tile_config %d does not exist for this operand kind (%s)", pl.tile + 1,
+             agb::tile_support_text(kind));
+  if (kind == 3 || kind == 4) {
+    if (kind == 3) AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
+    if (masked) AG_REQUIRE(g->m % 128 == 0, "block-scaled masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
+  }
+  const agb::TileConfig tc = agb::tile_config_of(kind, pl.tile);
+  pl.bn = tc.bn;
+  pl.ka = tc.ka;
+  pl.n_tiles = static_cast<int>((g->n + pl.bn - 1) / pl.bn);
+  pl.kb_count = static_cast<int>((k_bytes_of(kind, g->k) + 127) / 128);
+  // Device-resident weights: split long segments into accumulator-sized row chunks so that work spreads evenly.
+  // Host-resident weights keep whole segments per item: the weight column must cross the host link only once.
+  if (!host_b && !g->no_split) pl.split_rows = 128 * agb::chunk_tiles_of(kind, pl.tile, pl.bn);
+  const long long segments = masked ? g->num_groups : g->max_segments;
+  const long long seg_items = pl.split_rows > 0 ? rows_total / pl.split_rows + segments : segments;
+  const long long items = seg_items * pl.n_tiles;
+  pl.grid = static_cast<int>(items < grid_cap ? items : grid_cap);
+  if (pl.grid < 0) pl.grid = 0;
+  pl.kpad = static_cast<uint64_t>((pl.kb_count + pl.ka - 1) / pl.ka) * pl.ka * 128;
+  pl.scratch_need = pl.split_rows > 0 ? 0 : static_cast<uint64_t>(pl.grid) * pl.bn * pl.kpad;
+  *out = pl;
+  return AG_OK;
+}
+
 int run_staged(int kind, const ag_gemm_desc_t* g, uint64_t expert_bytes);
 
 // One launch. `win_n` >= 0: `g->b` holds only the experts [win_lo, win_lo + win_n) (a staged chunk) and the launch
@@ -150,11 +197,6 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   AG_REQUIRE((reinterpret_cast<uintptr_t>(g->a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g->d) & 15) == 0,
              "a and d must be 16-byte aligned");
 
-  int sms = 0;
-  if (int rc = device_sm_count(&sms)) return rc;
-  int cap = g->num_sms > 0 ? g->num_sms : g_num_sms.load();
-  int grid_cap = cap > 0 && cap < sms ? cap : sms;
-
   const void* b_dev = nullptr;
   const Residency res = classify(g->b, &b_dev);
   if (res == RES_UNREACHABLE)
@@ -164,6 +206,12 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   if (g->stage != nullptr && win_n < 0 && res == RES_HOST_MAPPED && !(kind == 2 && g->raw_dump != nullptr))
     return run_staged(kind, g, static_cast<uint64_t>(g->n) * kbytes);
   const int b_groups = win_n >= 0 ? win_n : g->num_groups;
+
+  LaunchPlan plan;
+  if (int rc = plan_launch(kind, g, res == RES_HOST_MAPPED, &plan)) return rc;
+  if (plan.grid <= 0) return AG_OK;
+  const int tile = plan.tile, bn = plan.bn, grid = plan.grid;
+  const uint64_t kpad = plan.kpad, need = plan.scratch_need;
 
   agb::GemmParams p;
   std::memset(&p, 0, sizeof(p));
@@ -190,40 +238,18 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   p.expert_lo = win_n >= 0 ? win_lo : 0;
   p.expert_n = b_groups;
   p.n = static_cast<int>(g->n);
-  int tile = g->tile_config > 0 ? g->tile_config - 1
-                                : (res == RES_HOST_MAPPED ? agb::kTileHost
-                                                          : ((kind == 1 || kind == 2) ? agb::kTileDeviceRegAcc : agb::kTileDevice));
-  if (tile == agb::kTileDeviceRegAcc)
-    AG_REQUIRE(kind == 1 || kind == 2, "tile_config 5 (register accumulators) exists for fp8 and int8 only");
-  AG_REQUIRE(tile >= 0 && tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
-  if (kind == 3 || kind == 4) {
-    AG_REQUIRE(tile == 0 || tile == 3, "hardware block-scaled kinds support tile_config 1 and 4 only (128 or 64 columns per item)");
-    if (kind == 3) AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
-    if (masked) AG_REQUIRE(g->m % 128 == 0, "block-scaled masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
-  }
-  const int bn = agb::tile_config_of(kind, tile).bn, ka = agb::tile_config_of(kind, tile).ka;
-  p.n_tiles = static_cast<int>((g->n + bn - 1) / bn);
-  p.kb_count = static_cast<int>((kbytes + 127) / 128);
+  p.n_tiles = plan.n_tiles;
+  p.kb_count = plan.kb_count;
   p.sf_k = kind == 3 ? static_cast<int>(agb::fp4_sf_k4_padded_host((g->k + 15) / 16))
            : kind == 4 ? static_cast<int>(agb::fp8_sf_k4_padded_host((g->k + 127) / 128)) : static_cast<int>((g->k + 127) / 128);
   p.sfb_rows = kind == 2 ? static_cast<int>(g->n) : static_cast<int>((g->n + 127) / 128);
   p.d_fp32 = g->d_dtype == AG_D_FP32;
   p.b_streaming = res == RES_HOST_MAPPED;
   p.alpha = g->alpha == 0.f ? 1.f : g->alpha;
+  p.split_rows = plan.split_rows;
 
-  // Device-resident weights: split long segments into accumulator-sized row chunks so that work spreads evenly.
-  // Host-resident weights keep whole segments per item: the weight column must cross the host link only once.
-  if (res != RES_HOST_MAPPED && !g->no_split) {
-    p.split_rows = 128 * agb::chunk_tiles_of(kind, tile, bn);
-  }
-  const long long seg_items = p.split_rows > 0 ? rows_total / p.split_rows + p.max_segments : p.max_segments;
-  const long long items = seg_items * p.n_tiles;
-  const int grid = static_cast<int>(items < grid_cap ? items : grid_cap);
-  if (grid <= 0) return AG_OK;
-
-  const uint64_t kpad = static_cast<uint64_t>((p.kb_count + ka - 1) / ka) * ka * 128;
-  const uint64_t need = static_cast<uint64_t>(grid) * bn * kpad;
-  p.use_scratch = (g->scratch != nullptr && g->scratch_bytes >= need) ? 1 : 0;
+  // Replay from scratch needs the whole amount; with less (or none) long segments re-read their weight column from b.
+  p.use_scratch = (g->scratch != nullptr && need > 0 && g->scratch_bytes >= need) ? 1 : 0;
   if (g->scratch != nullptr)
     AG_REQUIRE((reinterpret_cast<uintptr_t>(g->scratch) & 1023) == 0, "scratch must be 1024-byte aligned");
 
@@ -361,10 +387,26 @@ const char* status_text(int code) {
   }
 }
 
+// Scratch the launch described by `g` would replay long segments from (0: it has no use for any).
+int scratch_need(int kind, const ag_gemm_desc_t* g, uint64_t* out) {
+  AG_REQUIRE(g != nullptr && out != nullptr, "desc and the output pointer must be non-NULL");
+  AG_REQUIRE(kind >= 0 && kind <= 4, "kind must be 0 .. 4");
+  AG_REQUIRE(g->layout == AG_LAYOUT_CONTIGUOUS || g->layout == AG_LAYOUT_MASKED, "unknown layout %d", g->layout);
+  AG_REQUIRE(g->n > 0 && g->k > 0 && g->num_groups > 0 && g->m >= 0 && g->b != nullptr, "n, k, num_groups must be positive and b non-NULL");
+  const void* alias = nullptr;
+  const Residency res = classify(g->b, &alias);
+  if (res == RES_UNREACHABLE) return fail(AG_E_NOT_MAPPED, "b (%p) is neither device memory nor pinned/registered host memory", g->b);
+  LaunchPlan plan;
+  if (int rc = plan_launch(kind, g, res == RES_HOST_MAPPED, &plan)) return rc;
+  *out = plan.scratch_need;
+  return AG_OK;
+}
+
 }  // namespace
 
 // Hooks for the other translation units of the library (not part of the public ABI).
 int agb_run_desc(int kind, const ag_gemm_desc_t* desc) { return run(kind, desc); }
+int agb_scratch_need(int kind, const ag_gemm_desc_t* desc, uint64_t* out) { return scratch_need(kind, desc, out); }
 int agb_fail(int code, const char* message) { return fail(code, "%s", message); }
 
 extern "C" {
@@ -401,6 +443,8 @@ uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms) {
   const uint64_t kpad = (k_bytes_of(kind, k) + 1023) / 1024 * 1024;
   return static_cast<uint64_t>(sms) * 128 * kpad;
 }
+
+int ag_scratch_bytes_for(int32_t kind, const ag_gemm_desc_t* desc, uint64_t* bytes_out) { return scratch_need(kind, desc, bytes_out); }
 
 uint64_t ag_gemm_desc_size(void) { return sizeof(ag_gemm_desc_t); }
 

@@ -7,53 +7,76 @@
 namespace agb {
 
 // Tile configurations. BN = output columns (= weight rows) per item, KA = 128-byte K atoms per weight stage,
-// SB = weight ring depth. Every configuration keeps 128 KB of weight reads in flight per CTA and a 64 KB
-// activation ring (SA = 4 stages of 128 rows x 128 B).
+// SB = weight ring depth, SA = activation ring depth (stages of 128 rows x 128 B). The host-streaming configurations keep
+// 128 KB of weight reads in flight per CTA; the device-resident ones balance the two rings by what one K step consumes.
 constexpr bool kind_is_block_scaled(int kind) { return kind == 3 || kind == 4; }
+constexpr bool kind_is_sw_scaled(int kind) { return kind == 1 || kind == 2; }
 
 struct TileConfig {
-  int bn, ka, sb;
+  int bn, ka, sb, sa;
 };
-constexpr int kNumTileConfigs = 5;
+constexpr int kNumTileConfigs = 7;
 constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
-    {128, 1, 8},  // 0: B resident in device memory (tensor-core efficiency)
-    {32, 4, 8},   // 1: B streamed from host memory, fewest host pages in flight per CTA
-    {32, 8, 4},   // 2: as 1 with longer contiguous runs per row
-    {64, 2, 8},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
-    {128, 1, 8},  // 4: FP8 / INT8 with B resident in device memory: scaled accumulators in registers, one tile per item
+    {128, 1, 8, 4},  // 0: B resident in device memory, 128-column items
+    {32, 4, 8, 4},   // 1: B streamed from host memory, fewest host pages in flight per CTA
+    {32, 8, 4, 4},   // 2: as 1 with longer contiguous runs per row
+    {64, 2, 8, 4},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
+    {128, 1, 8, 4},  // 4: FP8 / INT8 with B resident in device memory: scaled accumulators in registers, one tile per item
+    {256, 1, 3, 6},  // 5: B resident in device memory, 256-column items: BF16 keeps two 128 x 256 accumulators in TMEM (a weight
+                     //    stage serves 256 rows, an activation stage 256 columns: twice the flops per operand byte of 0);
+                     //    FP8 / INT8 keep one 128 x 256 tile's scaled accumulators in the registers of two drain warpgroups
+    {128, 1, 4, 8},  // 6: B resident in device memory, 128-column items with a deep activation ring: the hardware-scaled kinds
+                     //    keep three row tiles per weight stage, so one K step consumes three activation stages
 };
 constexpr int kTileDeviceRegAcc = 4;
+constexpr int kTileDeviceWide = 5;
+constexpr int kTileDeviceDeepA = 6;
+constexpr bool tile_reg_acc(int kind, int tile) { return kind_is_sw_scaled(kind) && (tile == kTileDeviceRegAcc || tile == kTileDeviceWide); }
 // rows of one accumulator chunk (what one item covers when long segments are split)
 constexpr int chunk_tiles_of(int kind, int tile, int bn) {
-  return kind_is_block_scaled(kind) ? (512 - 64) / bn : ((kind == 1 || kind == 2) ? (tile == kTileDeviceRegAcc ? 1 : 512 / bn - 2) : 512 / bn);
+  return kind_is_block_scaled(kind) ? (512 - 64) / bn : (kind_is_sw_scaled(kind) ? (tile_reg_acc(kind, tile) ? 1 : 512 / bn - 2) : 512 / bn);
 }
 // NVFP4 also stages 2 KB of scale factors per K atom and operand, so its host-streaming configuration uses
 // single-atom stages in a deeper ring to stay inside the 227 KB of shared memory.
-constexpr TileConfig kTileFp4Host = {64, 1, 12};
+constexpr TileConfig kTileFp4Host = {64, 1, 12, 4};
 constexpr TileConfig tile_config_of(int kind, int tile) { return (kind == 3 && tile == 3) ? kTileFp4Host : kTileConfigs[tile]; }
-constexpr int kStagesA = 4;
 constexpr int kTileDevice = 0;
 constexpr int kTileHost = 3;
+// Which configurations exist for which operand kind (0 bf16, 1 fp8, 2 int8, 3 nvfp4, 4 fp8 with UE8M0 scales).
+constexpr bool tile_supported(int kind, int tile) {
+  if (tile < 0 || tile >= kNumTileConfigs) return false;
+  if (kind_is_block_scaled(kind)) return tile == 0 || tile == 3 || tile == kTileDeviceDeepA;   // 128 or 64 columns per item
+  if (kind_is_sw_scaled(kind)) return tile != kTileDeviceDeepA;
+  return tile != kTileDeviceRegAcc;
+}
+inline const char* tile_support_text(int kind) {
+  return kind_is_block_scaled(kind) ? "hardware block-scaled kinds have tile_config 1, 4 and 7"
+         : kind_is_sw_scaled(kind) ? "fp8 and int8 have tile_config 1 .. 6" : "bf16 has tile_config 1 .. 4, 6 and 7";
+}
+// Configuration chosen when the caller does not force one.
+constexpr int default_tile(int kind, bool host_b) {
+  return host_b ? kTileHost : (kind_is_sw_scaled(kind) ? kTileDeviceRegAcc : kTileDevice);
+}
 
 #define AGB_LAUNCH_ARGS int tile, int grid, cudaStream_t stream, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &ms, const GemmParams &p
 // One instantiation set per dtype lives in its own translation unit (inst_*.cu).
 cudaError_t launch_bf16(AGB_LAUNCH_ARGS);
 cudaError_t launch_fp8(AGB_LAUNCH_ARGS);
 cudaError_t launch_int8(AGB_LAUNCH_ARGS);
-cudaError_t launch_fp4(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
-cudaError_t launch_fp8_ue8m0(AGB_LAUNCH_ARGS);   // tiles 0 and 3 only
+cudaError_t launch_fp4(AGB_LAUNCH_ARGS);   // tiles 0, 3 and 6 only
+cudaError_t launch_fp8_ue8m0(AGB_LAUNCH_ARGS);   // tiles 0, 3 and 6 only
 cudaError_t fp8_sf_to_blocked_ue8m0(const float* src, void* dst, long long groups, long long rows, long long kb, int rows_per_scale,
                                     cudaStream_t stream);
 cudaError_t fp4_sf_to_blocked(const void* src, void* dst, long long groups, long long rows, long long k16, cudaStream_t stream);
 long long fp4_sf_k4_padded_host(long long k16);
 long long fp8_sf_k4_padded_host(long long kb);
 
-template <Kind KIND, int BN, int KA, int SB, bool REG_ACC = false>
+template <Kind KIND, int BN, int KA, int SB, bool REG_ACC = false, int SA = 4>
 cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ms,
                        const GemmParams& p) {
-  using L = SmemLayout<BN, KA, kStagesA, SB, SfStage<KIND, KA>::a, SfStage<KIND, KA>::b>;
+  using L = SmemLayout<BN, KA, SA, SB, SfStage<KIND, KA>::a, SfStage<KIND, KA>::b>;
   static_assert(L::dyn_bytes <= 232448, "tile configuration does not fit in shared memory");
-  auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, kStagesA, SB, REG_ACC>;
+  auto kernel = mgrouped_gemm_kernel<KIND, BN, KA, SA, SB, REG_ACC>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -76,6 +99,10 @@ cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
     case 3: return launch_one<KIND, 64, 2, 8>(grid, stream, ma, mb, ms, p);
     case 4:
       if constexpr (KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 8, true>(grid, stream, ma, mb, ms, p);
+      else return cudaErrorInvalidValue;
+    case 5: return launch_one<KIND, 256, 1, 3, KindTraits<KIND>::sw_scale, 6>(grid, stream, ma, mb, ms, p);
+    case 6:
+      if constexpr (!KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 4, false, 8>(grid, stream, ma, mb, ms, p);
       else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }

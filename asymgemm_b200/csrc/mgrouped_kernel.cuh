@@ -19,14 +19,15 @@
 // Tile shape is chosen by where B lives. Streaming from the host, throughput drops once the rows being streamed at
 // the same time (CTAs x BN) spread over more than a few thousand 4 KB host pages (measured: 148 CTAs x 128 rows ->
 // 44.5 GB/s, 148 x 32 rows -> 51.4 GB/s of a 55.6 GB/s copy-engine peak), so host-resident B uses BN = 64 or 32 with
-// KA = several 128-byte K atoms per stage; device-resident B uses BN = 128, KA = 1 for tensor-core efficiency.
+// KA = several 128-byte K atoms per stage; device-resident B uses BN = 128 or 256 with KA = 1: there the bound is the
+// operand traffic from L2 into shared memory, and flops per operand byte grow with the tile.
 //
 // Four operand kinds share the body: BF16 and NVFP4 accumulate in TMEM in hardware (NVFP4 with its UE4M3 scale
 // factors copied into TMEM by tcgen05.cp); FP8 and INT8 produce one raw product per 128-wide K block that the drain warps
 // scale in fp32 (block scales are arbitrary fp32 numbers) and add to accumulators kept in TMEM, or in registers (REG_ACC).
 //
 // Warp roles: warp 0 = B producer (+ scratch spill), warp 1 = A producer, warp 2 = TMEM allocator + single-thread
-// tcgen05.mma issuer, warp 3 idle, warps 4-7 (and 8-11 for INT8 with REG_ACC) = TMEM drain.
+// tcgen05.mma issuer, warp 3 idle, warps 4-7 (and 8-11 where a second drain warpgroup pays, see drain_wgs_of) = TMEM drain.
 //
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
 // shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
@@ -295,10 +296,13 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
 // one tile tall anyway and the drain, not the host link, sets the pace.
 // Drain warpgroups. The software-scaled kinds use two (384 threads) wherever a tile is at least 64 columns wide: warps
 // 4-7 own the low half of the tile's columns, warps 8-11 the high half, and the two groups drain a raw slot side by
-// side (INT8 with REG_ACC: 272 -> 383 TFLOP/s on the 16-expert case). The exception is FP8 with REG_ACC, whose block
-// scale is one scalar per tile: it is bound by operand traffic, not by the drain, and measured slightly faster with one.
+// side (INT8 with REG_ACC: 272 -> 383 TFLOP/s on the 16-expert case). The exception is FP8 with REG_ACC on 128 columns,
+// whose block scale is one scalar per tile: it is bound by operand traffic, not by the drain, and measured slightly
+// faster with one. 256-column tiles always use two groups, whatever the kind (128 columns, and for REG_ACC 128
+// accumulator registers, per thread).
 template <Kind KIND, int BN, bool REG_ACC>
 __host__ __device__ constexpr int drain_wgs_of() {
+  if (BN == 256) return 2;
   return (KIND != Kind::FP8 && KIND != Kind::INT8) ? 1 : (REG_ACC ? (KIND == Kind::INT8 ? 2 : 1) : (BN >= 64 ? 2 : 1));
 }
 template <Kind KIND, int BN, bool REG_ACC>
@@ -311,12 +315,14 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   using T = KindTraits<KIND>;
   using L = SmemLayout<BN, KA, SA, SB, SfStage<KIND, KA>::a, SfStage<KIND, KA>::b>;
   static_assert(KIND != Kind::FP8_UE8M0 || (KA == 1 || KA == 2 || KA == 4), "a UE8M0 scale block spans four K atoms");
-  static_assert(BN == 32 || BN == 64 || BN == 128, "BN must be 32, 64 or 128");
+  static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "BN must be 32, 64, 128 or 256");
+  static_assert(!T::block_scaled || BN <= 128, "block-scaled kinds keep their scale factors in TMEM columns laid out for at most 128 weight rows");
   static_assert(!T::block_scaled || BN >= 64, "block-scaled kinds need BN >= 64");
   // TMEM plan: 512 / BN slots of BN columns. Hardware-accumulated kinds keep one output tile per slot; software-scaled
   // kinds keep scaled fp32 tiles in slots [0, CHUNK_TILES) and double-buffer the raw per-K-block product in the last two.
   constexpr int NUM_SLOTS = (TMEM_COLS - (T::block_scaled ? SF_TMEM_COLS : 0)) / BN;
   static_assert(!REG_ACC || T::sw_scale, "REG_ACC applies to the software-scaled kinds");
+  static_assert(!T::sw_scale || REG_ACC || NUM_SLOTS > 2, "software-scaled kinds need TMEM room for two raw slots and at least one accumulator tile");
   constexpr int RAW_SLOTS = REG_ACC ? NUM_SLOTS : 2;                 // raw product slots (software-scaled kinds)
   constexpr int CHUNK_TILES = T::sw_scale ? (REG_ACC ? 1 : NUM_SLOTS - 2) : NUM_SLOTS;
   constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
@@ -598,7 +604,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int kb = 0; kb < kb_count && ok; ++kb, ++rt) {
             float sb_scalar = 0.f;
             if constexpr (KIND == Kind::FP8) {
-              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + (n0 >> 7)) * p.sf_k + kb);
+              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k + kb);
             } else {
 #pragma unroll
               for (int j = 0; j < COLS / 32; ++j) {
@@ -615,35 +621,37 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t raw_addr = lane_addr + (RAW_SLOT0 + rs) * BN + col_base;
+            // columns per TMEM load: 128 accumulator registers per thread leave room for 16 staging registers, not 32
+            constexpr int LW = COLS >= 128 ? 16 : 32;
 #pragma unroll
-            for (int cc = 0; cc < COLS / 32; ++cc) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(raw_addr + cc * 32, r);
+            for (int cc = 0; cc < COLS / LW; ++cc) {
+              uint32_t r[LW];
+              tmem_ld_cols(raw_addr + cc * LW, r);
               tmem_wait_ld();
-              if (cc == COLS / 32 - 1) {  // this warp has read its part of the raw slot: hand it back before the arithmetic
+              if (cc == COLS / LW - 1) {  // this warp has read its part of the raw slot: hand it back before the arithmetic
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tm_empty[rs]);
               }
               if constexpr (KIND == Kind::INT8) {
                 if (p.raw_dump != nullptr && valid) {
-                  int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + cc * 32;
+                  int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + cc * LW;
 #pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (n0 + col_base + cc * 32 + j < p.n) dst[j] = static_cast<int>(r[j]);
+                  for (int j = 0; j < LW; ++j)
+                    if (n0 + col_base + cc * LW + j < p.n) dst[j] = static_cast<int>(r[j]);
                 }
               }
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
+              for (int j = 0; j < LW; ++j) {
                 float prod, scale;
                 if constexpr (KIND == Kind::INT8) {
                   prod = static_cast<float>(static_cast<int>(r[j]));
-                  scale = sa * sfb_buf[cc * 32 + j];
+                  scale = sa * sfb_buf[cc * LW + j];
                 } else {
                   prod = __uint_as_float(r[j]);
                   scale = sa * sb_scalar;
                 }
-                acc[cc * 32 + j] = fmaf(prod, scale, kb > 0 ? acc[cc * 32 + j] : 0.f);
+                acc[cc * LW + j] = fmaf(prod, scale, kb > 0 ? acc[cc * LW + j] : 0.f);
               }
             }
             if constexpr (KIND == Kind::INT8) __syncwarp();  // everyone is done with sfb_buf before the next block refills it
@@ -664,7 +672,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             // column scales of this K block
             float sb_scalar = 0.f;
             if constexpr (KIND == Kind::FP8) {
-              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + (n0 >> 7)) * p.sf_k + kb);
+              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k + kb);
             }
             for (int mt = 0; mt < mc && ok; ++mt, ++rt) {
               const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
@@ -728,6 +736,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
           }
         } else {
+          constexpr int COLS = BN / drain_wgs_of<KIND, BN, REG_ACC>();   // columns owned by this drain warpgroup
+          const int col_base = ((warp - 4) >> 2) * COLS;
           for (int mt = 0; mt < mc && ok; ++mt) {
             ok = wait_bar(&tm_full[mt], (slot_phase >> mt) & 1, wc, ST_TIMEOUT_TM_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -736,9 +746,9 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
             const bool valid = grow < row_end;
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = 0; cc < COLS / 32; ++cc) {
               uint32_t r[32];
-              tmem_ld_32x32b_x32(lane_addr + mt * BN + cc * 32, r);
+              tmem_ld_32x32b_x32(lane_addr + mt * BN + col_base + cc * 32, r);
               tmem_wait_ld();
               if constexpr (T::block_scaled) {
                 if (p.alpha != 1.f) {
@@ -746,7 +756,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
                 }
               }
-              if (valid) store_row32(p, grow, n0 + cc * 32, r);
+              if (valid) store_row32(p, grow, n0 + col_base + cc * 32, r);
             }
             tc_fence_before_sync();
             __syncwarp();

@@ -251,6 +251,7 @@ int launch_check() {
   return e == cudaSuccess ? AG_OK : agb_fail(AG_E_CUDA, cudaGetErrorString(e));
 }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+bool aligned_to(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 }  // namespace
 
 extern "C" {
@@ -258,6 +259,9 @@ extern "C" {
 int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, void* stream) {
   if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || cols % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
   if (rows == 0) return AG_OK;
+  // the narrow kernel reads 8 bytes of x and writes 4 bytes of q per lane (the wide one 16 and 8)
+  if (!aligned_to(x_bf16, 8) || !aligned_to(q, 4) || !aligned_to(sf, 4))
+    return agb_fail(AG_E_INVALID, "x must be 8-byte aligned, q and sf 4-byte aligned");
   const int bpr = static_cast<int>((cols + 127) / 128);
   if (cols % 8 == 0 && aligned16(x_bf16) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
     const int ppr = (bpr + 1) / 2;
@@ -275,6 +279,8 @@ int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int6
 int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales, void* stream) {
   if (!gate_up_bf16 || !q || !sf || rows < 0 || inter <= 0 || inter % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (inter must be a multiple of 4)");
   if (rows == 0) return AG_OK;
+  if (!aligned_to(gate_up_bf16, 8) || !aligned_to(q, 4) || !aligned_to(sf, 4))
+    return agb_fail(AG_E_INVALID, "gate_up must be 8-byte aligned, q and sf 4-byte aligned");
   const int bpr = static_cast<int>((inter + 127) / 128);
   if (inter % 8 == 0 && aligned16(gate_up_bf16) && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
     const int ppr = (bpr + 1) / 2;
@@ -301,8 +307,9 @@ int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int6
 
 int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                     int64_t cols, void* stream) {
-  if (!rows_bf16 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 8 != 0)
-    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 8)");
+  if (!rows_bf16 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 8 != 0 || !aligned16(rows_bf16) ||
+      !aligned16(y_bf16) || !aligned_to(pos, 8) || !aligned_to(weights, 4))
+    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 8; rows and y 16-byte aligned)");
   if (tokens == 0) return AG_OK;
   agb::combine_topk_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(rows_bf16), reinterpret_cast<const long long*>(pos), weights, static_cast<__nv_bfloat16*>(y_bf16),
@@ -311,7 +318,8 @@ int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weig
 }
 
 int ag_quant_rows_int8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, void* stream) {
-  if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0) return agb_fail(AG_E_INVALID, "bad arguments");
+  if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || !aligned_to(x_bf16, 2) || !aligned_to(sf, 4))
+    return agb_fail(AG_E_INVALID, "bad arguments (x must be 2-byte aligned, sf 4-byte aligned)");
   if (rows == 0) return AG_OK;
   agb::quant_rows_int8_kernel<0><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       x_bf16, static_cast<int8_t*>(q), sf, rows, static_cast<int>(cols), static_cast<int>((cols + 127) / 128));
@@ -319,7 +327,8 @@ int ag_quant_rows_int8(const void* x_bf16, void* q, float* sf, int64_t rows, int
 }
 
 int ag_silu_mul_quant_int8(const void* gate_up_f32, void* q, float* sf, int64_t rows, int64_t inter, void* stream) {
-  if (!gate_up_f32 || !q || !sf || rows < 0 || inter <= 0) return agb_fail(AG_E_INVALID, "bad arguments");
+  if (!gate_up_f32 || !q || !sf || rows < 0 || inter <= 0 || !aligned_to(gate_up_f32, 4) || !aligned_to(sf, 4))
+    return agb_fail(AG_E_INVALID, "bad arguments (gate_up and sf must be 4-byte aligned)");
   if (rows == 0) return AG_OK;
   agb::quant_rows_int8_kernel<1><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       gate_up_f32, static_cast<int8_t*>(q), sf, rows, static_cast<int>(inter), static_cast<int>((inter + 127) / 128));
@@ -328,8 +337,9 @@ int ag_silu_mul_quant_int8(const void* gate_up_f32, void* q, float* sf, int64_t 
 
 int ag_combine_topk_f32(const void* rows_f32, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                         int64_t cols, void* stream) {
-  if (!rows_f32 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 4 != 0)
-    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
+  if (!rows_f32 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 4 != 0 || !aligned16(rows_f32) ||
+      !aligned_to(y_bf16, 8) || !aligned_to(pos, 8) || !aligned_to(weights, 4))
+    return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4; rows 16-byte and y 8-byte aligned)");
   if (tokens == 0) return AG_OK;
   agb::combine_topk_f32_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float*>(rows_f32), reinterpret_cast<const long long*>(pos), weights, static_cast<__nv_bfloat16*>(y_bf16), top_k,

@@ -27,6 +27,7 @@
 
 // internal hooks exported by capi.cu
 int agb_run_desc(int kind, const ag_gemm_desc_t* desc);
+int agb_scratch_need(int kind, const ag_gemm_desc_t* desc, uint64_t* out);
 int agb_fail(int code, const char* message);
 
 namespace {
@@ -79,29 +80,17 @@ int ag_m_grouped_fp8_gemm_nt_static_scratch(const ag_gemm_desc_t* desc) {
   const uintptr_t aligned = (reinterpret_cast<uintptr_t>(base) + 1023) & ~static_cast<uintptr_t>(1023);
   const uint64_t usable = kStaticScratchBytes - (aligned - reinterpret_cast<uintptr_t>(base));
 
-  // Scratch this launch would use: one weight column (tile rows x padded K bytes) per CTA.
-  cudaPointerAttributes at;
-  bool host_b = false;
-  if (cudaPointerGetAttributes(&at, desc->b) == cudaSuccess) host_b = at.type == cudaMemoryTypeHost;
-  else cudaGetLastError();
-  int tile = desc->tile_config > 0 ? desc->tile_config - 1 : (host_b ? agb::kTileHost : agb::kTileDeviceRegAcc);
-  if (tile < 0 || tile >= agb::kNumTileConfigs) return agb_fail(AG_E_INVALID, "tile_config out of range");
-  const agb::TileConfig tc = agb::tile_config_of(1, tile);
-  const uint64_t atoms = (static_cast<uint64_t>(desc->k) + 127) / 128;
-  const uint64_t kpad = (atoms + tc.ka - 1) / tc.ka * tc.ka * 128;
-  const int64_t segments = desc->layout == AG_LAYOUT_MASKED ? desc->num_groups : desc->max_segments;
-  const int64_t items = segments * ((desc->n + tc.bn - 1) / tc.bn);
-  int64_t grid = desc->num_sms > 0 ? desc->num_sms : ag_get_num_sms();
-  if (items < grid) grid = items;
-  if (grid < 0) grid = 0;
-  const uint64_t need = static_cast<uint64_t>(grid) * tc.bn * kpad;
+  // Scratch this launch would use, from the same arithmetic as the launch itself: one weight column (tile rows x padded K
+  // bytes) per CTA when the weights stream from the host (or with no_split); nothing when device-resident weights are
+  // cut into one-chunk items, which never replay.
+  uint64_t need = 0;
+  if (int rc = agb_scratch_need(1, desc, &need)) return rc;
   if (need > usable) {
     char msg[320];
     snprintf(msg, sizeof(msg),
-             "this problem needs %llu bytes of scratch (%lld CTAs x %d rows x %llu bytes of K) but the built-in scratch holds %llu: "
+             "this problem needs %llu bytes of scratch (CTAs x tile rows x padded K bytes) but the built-in scratch holds %llu: "
              "lower num_sms, pick a narrower tile_config, or use ag_m_grouped_fp8_gemm_nt with caller-provided scratch",
-             static_cast<unsigned long long>(need), static_cast<long long>(grid), tc.bn, static_cast<unsigned long long>(kpad),
-             static_cast<unsigned long long>(usable));
+             static_cast<unsigned long long>(need), static_cast<unsigned long long>(usable));
     return agb_fail(AG_E_INVALID, msg);
   }
 
@@ -111,7 +100,6 @@ int ag_m_grouped_fp8_gemm_nt_static_scratch(const ag_gemm_desc_t* desc) {
   g.stage = nullptr;  // staging would create a stream and events on first use: this entry point reads b in the kernel
   g.stage_bytes = 0;
   g.stage_chunk_bytes = 0;
-  g.tile_config = tile + 1;
   return agb_run_desc(1, &g);
 }
 

@@ -451,13 +451,10 @@ class ExpertParallelMoE:
                 sfa = to_contiguous_layout(recv_extras[0], state)
                 return self.experts_forward(a_q, sfa, state, first, count)
 
-            cap = api.get_num_sms()
             sms = torch.cuda.get_device_properties(x.device).multi_processor_count
-            api.set_num_sms(max(8, (cap if cap > 0 else sms) - self.comm_sms))
-            try:
+            cap = api.get_num_sms()
+            with api.launch_sm_cap(max(8, (cap if 0 < cap < sms else sms) - self.comm_sms)):
                 return self.dispatcher.pipelined(x_q, (sfx,), topk_ids, topk_weights, self.pipeline_groups, group_forward)
-            finally:
-                api.set_num_sms(cap)
         state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)

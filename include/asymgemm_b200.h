@@ -77,7 +77,8 @@ typedef struct ag_gemm_desc {
   int32_t tile_config; /* 0 = choose from where b lives; 1.. = force tile configuration (tuning / tests):
                           1 = 128 columns per item (device-resident b), 2 = 32 columns x 512 B of K per stage
                           (host-resident b), 3 = 32 x 1024 B, 4 = 64 x 256 B, 5 = 128 columns with the scaled accumulators in registers
-                          (fp8 / int8 with device-resident b) */
+                          (fp8 / int8 with device-resident b), 6 = 256 columns per item (device-resident b; bf16, fp8, int8),
+                          7 = 128 columns with a deep activation ring (device-resident b; bf16 and the hardware-scaled kinds) */
   int32_t no_split;    /* device-resident b only: 1 = keep one item per (segment, n-tile) instead of splitting long segments into
                           accumulator-sized row chunks across CTAs (tests / tuning); ignored for host-resident b */
 
@@ -136,8 +137,11 @@ int ag_m_grouped_fp4_gemm_nt(const ag_gemm_desc_t* desc);
  * their own, loops that cannot afford a cudaMalloc (it synchronises the device and can fail when memory is nearly
  * full). The scratch that long segments use comes from a fixed 80 MiB array inside the library's device image
  * (ag_static_scratch_bytes); desc->scratch / scratch_bytes are ignored and desc->status MUST be given.
- * Limits: returns AG_E_INVALID with a message when CTAs x tile rows x padded K bytes exceeds the array (for FP8 with
- * weights on the host, tile_config 0 and all 148 SMs that is K <= 8704; tile_config 2 doubles it, a lower num_sms raises it);
+ * Limits: returns AG_E_INVALID with a message when the scratch the launch would use (ag_scratch_bytes_for: CTAs x tile
+ * rows x padded K bytes) exceeds the array. With weights on the host, tile_config 0 and all 148 SMs that is K <= 8704
+ * (tile_config 2 doubles it, a lower num_sms raises it). With weights in device memory the default launch cuts long
+ * segments into one-chunk items that never replay, needs no scratch and has no K limit; only no_split = 1 brings the
+ * limit back (K <= 4352 with 128-column items on 148 SMs).
  * every GPU that loads the library holds the array until the process exits; all calls share it, so calls that can
  * overlap on the GPU (other streams or threads) race -- serialise them. The array keeps the last call's contents and
  * needs no clearing. The first call on each device looks up the array's address (cudaGetSymbolAddress): make that
@@ -150,6 +154,14 @@ uint64_t ag_static_scratch_bytes(void);
  * (kind: 0 bf16, 1 fp8, 2 int8, 3 nvfp4). Reference counterpart: none (the reference accumulates bf16
  * partial sums in D instead, impls/sm100_fp8_asym_gemm_1d1d.cuh:648-659). */
 uint64_t ag_scratch_bytes(int32_t kind, int64_t n, int64_t k, int32_t num_sms);
+
+/* Exact scratch (bytes) the launch described by `desc` replays long segments from, by the arithmetic of the launch itself
+ * (tile configuration from where desc->b lives, grid size, K padded to whole weight stages); 0 when the launch has no use for
+ * scratch (device-resident b without no_split). A call whose scratch_bytes is smaller than this runs without replay: long
+ * segments then re-read their weight column from b once per accumulator chunk (same results; for host-resident b more
+ * trips over the link). kind as above, 4 = fp8 with UE8M0 scales. Only layout, m, n, k, num_groups, max_segments, b,
+ * num_sms, tile_config and no_split are read. Reference counterpart: none. */
+int ag_scratch_bytes_for(int32_t kind, const ag_gemm_desc_t* desc, uint64_t* bytes_out);
 
 /* Synchronises `stream`, copies the status word to *out and returns AG_OK or AG_E_DEVICE (with a decoded
  * message in ag_last_error). Replaces the reference's device-side trap (asym_gemm/include/asym_gemm/common/utils.cuh:24-40). */

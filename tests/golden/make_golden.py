@@ -95,7 +95,8 @@ def segments_table(rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of bytedance-iaas/AsymGEMM (its quantisers and test-side "
+                                                       "references are imported from there)")
     args = ap.parse_args()
     ref = Path(args.reference)
     M, numeric, fp4, int8 = _install_reference(ref)

@@ -102,6 +102,28 @@ def test_c_abi_rejects_bad_descriptors_without_a_gpu():
     assert lib.ag_fp4_sf_blocked_bytes(2, 130, 16) == 2 * 2 * 32 * 512  # 2 groups x 2 row tiles x K runs padded to 32
 
 
+def test_helper_kernels_reject_misaligned_pointers_without_launching():
+    """The row quantisers and the top-k combine use vector loads and stores; a pointer that is not aligned for them is
+    refused on the host (a launch would fault the context). No GPU is needed: the checks run before any CUDA call."""
+    lib = _lib.load()
+    base = 0x7F0000000000   # never dereferenced
+    ok = base
+    assert lib.ag_quant_rows_fp8(ok + 2, ok, ok, 4, 256, 0, None) == _lib.AG_E_INVALID      # x only 2-byte aligned
+    assert "aligned" in _lib.last_error()
+    assert lib.ag_quant_rows_fp8(ok, ok + 2, ok, 4, 256, 0, None) == _lib.AG_E_INVALID      # q only 2-byte aligned
+    assert lib.ag_silu_mul_quant_fp8(ok + 4, ok, ok, 4, 256, 0, None) == _lib.AG_E_INVALID  # gate_up only 4-byte aligned
+    assert lib.ag_silu_mul_quant_fp8(ok, ok + 1, ok, 4, 256, 0, None) == _lib.AG_E_INVALID
+    assert lib.ag_combine_topk(ok + 8, ok, ok, ok, 4, 2, 256, None) == _lib.AG_E_INVALID    # rows only 8-byte aligned
+    assert lib.ag_combine_topk(ok, ok, ok, ok + 8, 4, 2, 256, None) == _lib.AG_E_INVALID    # y only 8-byte aligned
+    assert lib.ag_combine_topk_f32(ok + 4, ok, ok, ok, 4, 2, 256, None) == _lib.AG_E_INVALID
+    assert lib.ag_combine_topk_f32(ok, ok, ok, ok + 4, 4, 2, 256, None) == _lib.AG_E_INVALID
+    assert lib.ag_move_rows(ok + 8, ok, None, None, 4, 256, None) == _lib.AG_E_INVALID
+    assert lib.ag_quant_rows_int8(ok + 1, ok, ok, 4, 256, None) == _lib.AG_E_INVALID
+    assert lib.ag_silu_mul_quant_int8(ok + 2, ok, ok, 4, 256, None) == _lib.AG_E_INVALID
+    # zero rows with aligned pointers: accepted, nothing launched
+    assert lib.ag_quant_rows_fp8(ok, ok, ok, 0, 256, 0, None) == _lib.AG_OK
+
+
 def test_weight_scale_cache_is_tied_to_the_tensor_object():
     """A new tensor that reuses a freed tensor's address must not be served the old tensor's cached copy."""
     from asymgemm_b200 import api
@@ -180,11 +202,11 @@ def test_torch_extension_loads_and_registers_the_launch_op():
     from asymgemm_b200 import _lib
     ops = _lib.torch_ops()
     schema = str(ops.m_grouped_gemm_nt.default._schema)
-    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema
+    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema and "int num_sms" in schema
     z = torch.zeros(4, 4)
     with pytest.raises(NotImplementedError):
         ops.m_grouped_gemm_nt(0, 0, z, None, z, None, z, None, None, 0, None, 4, 4, 4, 1, None,
-                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0)
+                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0, 0)
 
 
 def test_auto_weight_path_rule():
