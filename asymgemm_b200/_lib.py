@@ -84,6 +84,9 @@ EXPORTS = [
     "ag_release_weights",
     "ag_measure_host_link",
     "ag_measure_host_stream",
+    "ag_link_probe_create",
+    "ag_link_probe_run",
+    "ag_link_probe_destroy",
     "ag_selftest_wait_limit",
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
@@ -164,6 +167,12 @@ def load() -> ctypes.CDLL:
     lib.ag_release_weights.restype = c_int32
     lib.ag_measure_host_link.argtypes = [c_uint64, c_int32, POINTER(c_double)]
     lib.ag_measure_host_link.restype = c_int32
+    lib.ag_link_probe_create.argtypes = [c_int32, c_uint64, c_int32, c_int64, POINTER(c_void_p)]
+    lib.ag_link_probe_create.restype = c_int32
+    lib.ag_link_probe_run.argtypes = [c_void_p, c_double, POINTER(c_double)]
+    lib.ag_link_probe_run.restype = c_int32
+    lib.ag_link_probe_destroy.argtypes = [c_void_p]
+    lib.ag_link_probe_destroy.restype = c_int32
     lib.ag_gemm_desc_size.argtypes = []
     lib.ag_gemm_desc_size.restype = c_uint64
     if int(lib.ag_gemm_desc_size()) != ctypes.sizeof(GemmDesc):

@@ -278,17 +278,23 @@ class EPDispatcher:
             self._side = torch.cuda.Stream(device=device)
         return self._side
 
-    def combine(self, expert_out: torch.Tensor, state: DispatchState, topk_weights: torch.Tensor) -> torch.Tensor:
-        """expert_out [padded_rows, H] (contiguous layout) -> y [T, H] = sum_k w[t, k] * out(t, k), in fp32, as expert_out.dtype."""
+    def combine(self, expert_out: torch.Tensor, state: DispatchState, topk_weights: torch.Tensor, mark=None) -> torch.Tensor:
+        """expert_out [padded_rows, H] (contiguous layout) -> y [T, H] = sum_k w[t, k] * out(t, k), in fp32, as expert_out.dtype.
+        `mark(name)`, if given, is called between the return exchange and the weighted sum (phase timing)."""
         # inverse of the sort: pair p (token p // k, slot p % k) was sent as sorted row inv[p]
         inv = torch.empty_like(state.order)
         inv[state.order] = torch.arange(state.order.numel(), device=state.order.device)
         if self.world == 1:
             # the sorted rows never left this rank: read them straight out of the padded layout
-            return moe_ops.combine_topk(expert_out, state.dest_rows.index_select(0, inv), topk_weights, state.tokens, state.top_k)
+            pos = state.dest_rows.index_select(0, inv)
+            if mark is not None:
+                mark("return")
+            return moe_ops.combine_topk(expert_out, pos, topk_weights, state.tokens, state.top_k)
         back = moe_ops.move_rows(expert_out, state.dest_rows.numel(), src_rows=state.dest_rows)
         ret = torch.empty((state.tokens * state.top_k, back.shape[1]), dtype=back.dtype, device=back.device)
         self._all_to_all(ret, back, state.send_splits, state.recv_splits)
+        if mark is not None:
+            mark("return")
         return moe_ops.combine_topk(ret, inv, topk_weights, state.tokens, state.top_k)
 
 
@@ -366,6 +372,23 @@ def proportional_expert_ranges(rates: List[float], num_experts: int, tolerance: 
     return out
 
 
+def rebalance_expert_ranges(ranges: List[Tuple[int, int]], step_ms: List[float], tolerance: float = 0.06) -> List[Tuple[int, int]]:
+    """Expert ranges re-cut from what the ranks just measured: rank r took `step_ms[r]` for a step over its current range, so
+    its link moves (hi - lo) / step_ms[r] experts per millisecond under the load the job really produces (every rank
+    streaming, the host's memory system shared); the new ranges are proportional to those rates. A short calibration
+    before the job cannot see that load -- on one 8-GPU host it read 47 GB/s for links that then ran at 29 GB/s.
+    Returns `ranges` itself when the slowest and the fastest rank are within `tolerance` of each other. The caller moves
+    the weights of experts that change owner (once, outside any timed region) and may repeat the step."""
+    if len(ranges) != len(step_ms) or not ranges:
+        raise RuntimeError("one step time per rank is needed")
+    if min(step_ms) <= 0:
+        return list(ranges)
+    if max(step_ms) / min(step_ms) <= 1.0 + tolerance:
+        return list(ranges)
+    rates = [(hi - lo) / ms for (lo, hi), ms in zip(ranges, step_ms)]
+    return proportional_expert_ranges(rates, ranges[-1][1], tolerance=0.0)
+
+
 def gpu_numa_node(device_index: int) -> int:
     """NUMA node of the GPU's PCIe root, or -1 when the platform does not say (single-node VMs)."""
     try:
@@ -407,6 +430,12 @@ class ExpertParallelMoE:
         # staged weight path only: weights whose first chunks are copied while this layer's results travel home (the next
         # layer's gate+up weights in a model; this layer's own when it is called in a loop). None = no prefetch.
         self.prefetch_next: Optional[torch.Tensor] = None
+        # Measurement and test hooks, off by default. `phase_events`: a list that every unpipelined forward() appends
+        # (phase name, CUDA event) pairs to, recorded on the caller's stream where one phase ends. `keep_intermediates`:
+        # the last experts_forward() leaves its operands and results in `self.intermediates`.
+        self.phase_events: Optional[list] = None
+        self.keep_intermediates = False
+        self.intermediates: Optional[dict] = None
         epr = self.dispatcher.experts_per_rank
         if tuple(w13[0].shape) != (epr, 2 * inter, hidden) or tuple(w2[0].shape) != (epr, hidden, inter):
             raise RuntimeError("weight shapes do not match (experts_per_rank, 2*inter, hidden) / (experts_per_rank, hidden, inter)")
@@ -422,6 +451,12 @@ class ExpertParallelMoE:
             hit = self._weight_views[(first, count)] = ((self.w13[0][sl], self.w13[1][sl]), (self.w2[0][sl], self.w2[1][sl]))
         return hit
 
+    def _mark(self, name: str) -> None:
+        if self.phase_events is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.append((name, ev))
+
     def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState, first: int = 0,
                         count: Optional[int] = None) -> torch.Tensor:
         """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]. `first` / `count`: the local
@@ -436,13 +471,20 @@ class ExpertParallelMoE:
             return d2
         hw = self.ue8m0_scales
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
+        self._mark("gemm_gate_up")
         a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw)
+        self._mark("silu_mul_requant")
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
+        self._mark("gemm_down")
+        if self.keep_intermediates:
+            self.intermediates = dict(a_q=a_q, sfa=sfa, d1=d1, a2=a2, s2=s2, d2=d2, state=state, first=first)
         return d2
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
+        self._mark("start")
         x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous(), pow2_scales=self.ue8m0_scales)
+        self._mark("quantise")
         if self.pipeline_groups > 1 and self.dispatcher.world > 1:
             from . import api
 
@@ -456,10 +498,14 @@ class ExpertParallelMoE:
             with api.launch_sm_cap(max(8, (cap if 0 < cap < sms else sms) - self.comm_sms)):
                 return self.dispatcher.pipelined(x_q, (sfx,), topk_ids, topk_weights, self.pipeline_groups, group_forward)
         state, recv_q, (recv_s,) = self.dispatcher.dispatch(x_q, topk_ids, (sfx,))
+        self._mark("plan_dispatch")
         a_q = to_contiguous_layout(recv_q, state)
         sfa = to_contiguous_layout(recv_s, state)
+        self._mark("layout")
         out = self.experts_forward(a_q, sfa, state)
         if self.prefetch_next is not None and out.is_cuda:
             from . import api
             api.prefetch_weights(self.prefetch_next, out.device)
-        return self.dispatcher.combine(out, state, topk_weights)
+        y = self.dispatcher.combine(out, state, topk_weights, self._mark if self.phase_events is not None else None)
+        self._mark("combine")
+        return y

@@ -7,13 +7,18 @@ host-link peak.
 One step = one grouped GEMM over one batch of synthetic, seeded input (the shapes of the benchmark configurations named in WORKLOADS; no
 dataset or checkpoint is involved). The default workload is the DeepSeek-V3-shaped FP8 gate+up GEMM: 256 experts,
 K=7168, N=4096, 16384 tokens x top-8 with Zipf(0.8) expert popularity, B (7.5 GB) in pinned host memory.
-With N > 1 ranks the experts (and the rows routed to them) are split across ranks in contiguous ranges -- evenly when the
-ranks' host links measure within 10 % of each other with all of them streaming at once, otherwise in proportion to those
-rates (--even-shards forces the even split); every rank streams its own shard over its own host link and there is no
-collective on the data path, so total work is fixed ("strong").
+With N > 1 ranks the experts (and the rows routed to them) are split across ranks in contiguous ranges: first in proportion
+to each rank's host-link rate measured with all ranks streaming at once for a sustained interval, then re-cut from the
+ranks' own step times after the warm-up steps (closed loop; --even-shards forces the even split). Every rank streams its
+own shard over its own host link and there is no collective on the data path of the headline number, so total work is
+fixed ("strong"). When the job has fewer ranks than the machine has GPUs, the GPUs are chosen by measurement
+(asymgemm_b200/linkprobe.py; --device-map identity keeps rank r on GPU r).
 
 Prints ONE JSON line on rank 0. `value` times the kernel with activations already in HBM; `e2e` times the public
-operator call with host buffers (pinned A in, D out) inside the timed region.
+operator call with host buffers (pinned A in, D out) inside the timed region. The same line carries `ep_layer` -- the
+expert-parallel FP8 MoE layer (two grouped GEMMs, NCCL all-to-all dispatch and combine) timed in the same run at the same
+N, with a per-phase breakdown and a parity figure against a dense fp32 restatement -- and, on one GPU, `device_resident`:
+the grouped GEMM with the weights in HBM, against the tensor roofline.
 """
 from __future__ import annotations
 
@@ -43,8 +48,9 @@ WORKLOADS = {
     "c5_moe_fp8": dict(kind="moe", experts=256, hidden=7168, inter=2048, tokens=65536, top_k=8),
 }
 ELEM_BYTES = {"fp8": 1.0, "bf16": 2.0, "int8": 1.0, "fp4": 0.5}
-# DRAM bytes (read + write) per padded row of A/D of the FP8 7168x4096 kernel, from one ncu capture of a 16-expert case
-# (profiles/mgrouped_fp8_host_streamed_16experts.md): traffic grows with the rows of the launch, not with the weights.
+# DRAM bytes (read + write) per padded row of A/D, from one ncu capture of a cut-down case of each workload with the
+# default tile configuration (dram__bytes_read.sum + dram__bytes_write.sum over the padded rows of that launch): HBM
+# traffic grows with the rows of the launch, not with the weights, which never touch HBM.
 NCU_DRAM_BYTES_PER_ROW = {"c3_fp8": 18.4e3}
 
 
@@ -57,7 +63,10 @@ def rows_per_expert(cfg, seed=0):
 
 
 def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, huge_pages=False, expert_range=None, ue8m0=False):
-    """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host."""
+    """Seeded synthetic operands for this rank's expert shard. B is quantised on the GPU and moved to pinned host.
+    Every expert's weights and rows come from a generator keyed by the expert's global index, so an expert holds the same
+    numbers whichever rank owns it (ranges are re-cut between warm-up and the timed steps)."""
+    from asymgemm_b200.testing.moe_reference import expert_generator
     from asymgemm_b200.utils import (build_contiguous_layout, per_block_cast_to_fp8, per_channel_cast_to_int8,
                                      per_token_cast_to_fp8, per_token_cast_to_int8)
     kind, k, n = cfg["kind"], cfg["k"], cfg["n"]
@@ -68,14 +77,13 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     counts = counts[lo:hi]
     g = len(counts)
     offsets, experts, list_size, m_total, segs = build_contiguous_layout(counts, device=device)
-    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
     valid = sum(c for c in counts)
 
     a_dtype = {"fp8": torch.float8_e4m3fn, "bf16": torch.bfloat16, "int8": torch.int8}[kind]
     a = torch.zeros((m_total, k), dtype=a_dtype, device=device)
     sfa = None if kind == "bf16" else torch.zeros((m_total, (k + 127) // 128), dtype=torch.float32, device=device)
     for e, start, rows in segs:
-        x = torch.randn((rows, k), device=device, generator=gen)
+        x = torch.randn((rows, k), device=device, generator=expert_generator(device, seed, lo + e, 1))
         if kind == "fp8":
             q, s = per_token_cast_to_fp8(x, use_ue8m0=ue8m0)
             a[start:start + rows], sfa[start:start + rows] = q, s
@@ -96,7 +104,7 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     elif kind == "int8":
         sfb = torch.empty((g, n, k // 128), dtype=torch.float32, device=device)
     for e in range(g):
-        w = torch.randn((n, k), device=device, generator=gen) * 0.02
+        w = torch.randn((n, k), device=device, generator=expert_generator(device, seed, lo + e, 0)) * 0.02
         if kind == "fp8":
             q, s = per_block_cast_to_fp8(w, use_ue8m0=ue8m0)
             sfb[e] = s
@@ -112,42 +120,49 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
     d = torch.empty((m_total, n), dtype=torch.bfloat16, device=device)
     active = sum(1 for c in counts if c > 0)
     return dict(kind=kind, a=a, sfa=sfa, b=b_host, sfb=sfb, d=d, offsets=offsets, experts=experts, list_size=list_size,
-                m_total=m_total, valid_rows=valid, segs=segs, g=g, n=n, k=k,
+                m_total=m_total, valid_rows=valid, segs=segs, g=g, n=n, k=k, expert_lo=lo,
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * ELEM_BYTES[kind])
 
 
-def build_moe(cfg, rank, world, device, group, seed=0, expert_ranges=None, ue8m0=False, pipeline_groups=1):
+MOE_SEED = 5
+
+
+def build_moe(cfg, rank, world, device, group, seed=MOE_SEED, expert_ranges=None, ue8m0=False, pipeline_groups=1):
     """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
-    GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing."""
+    GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing. Expert e's
+    weights come from a generator keyed by e, so any rank can rebuild any expert for the parity check."""
     from asymgemm_b200 import ep
-    from asymgemm_b200.utils import per_block_cast_to_fp8
+    from asymgemm_b200.testing.moe_reference import expert_generator, expert_weights
     e_total, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
-    epr = e_total // world if expert_ranges is None else expert_ranges[rank][1] - expert_ranges[rank][0]
-    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    if expert_ranges is None:
+        per = e_total // world
+        expert_ranges = [(r * per, (r + 1) * per if r < world - 1 else e_total) for r in range(world)]
+    lo, hi = expert_ranges[rank]
+    epr = hi - lo
     node = ep.gpu_numa_node(device.index)
     w13 = ep.pinned_empty((epr, 2 * i, h), torch.float8_e4m3fn, node)
     w2 = ep.pinned_empty((epr, h, i), torch.float8_e4m3fn, node)
     s13 = torch.empty((epr, 2 * i // 128, h // 128), dtype=torch.float32, device=device)
     s2 = torch.empty((epr, h // 128, i // 128), dtype=torch.float32, device=device)
     for e in range(epr):
-        q, s = per_block_cast_to_fp8(torch.randn((2 * i, h), device=device, generator=gen) * 0.02, use_ue8m0=ue8m0)
-        w13[e].copy_(q, non_blocking=True)
-        s13[e] = s
-        q, s = per_block_cast_to_fp8(torch.randn((h, i), device=device, generator=gen) * 0.02, use_ue8m0=ue8m0)
-        w2[e].copy_(q, non_blocking=True)
-        s2[e] = s
+        q13, sc13, q2, sc2 = expert_weights(seed, lo + e, h, i, device, use_ue8m0=ue8m0)
+        w13[e].copy_(q13, non_blocking=True)
+        s13[e] = sc13
+        w2[e].copy_(q2, non_blocking=True)
+        s2[e] = sc2
     torch.cuda.synchronize(device)
     layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges, ue8m0_scales=ue8m0,
                                  pipeline_groups=pipeline_groups)
     t_local = cfg["tokens"] // world
+    gen = expert_generator(device, seed, 100000 + rank, 3)      # this rank's tokens and router logits
     x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
     logits = torch.randn((t_local, e_total), device=device, generator=gen)
     topk_w, topk_ids = torch.topk(torch.softmax(logits, dim=-1), cfg["top_k"], dim=-1)
     topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
     rows = t_local * cfg["top_k"]
-    return dict(kind="moe", layer=layer, x=x, ids=topk_ids, w=topk_w, numa_node=node,
+    return dict(kind="moe", layer=layer, x=x, ids=topk_ids, w=topk_w, numa_node=node, seed=seed, ue8m0=ue8m0,
                 flops=float(rows) * 2.0 * (2 * i * h + h * i), host_bytes=float(epr) * (2 * i * h + h * i),
-                nvlink_bytes=float(rows) * (h + h // 128 * 4 + 2 * h))
+                nvlink_bytes=float(rows) * (h + h // 128 * 4 + 2 * h) * (world - 1) / world if world > 1 else 0.0)
 
 
 def build_masked_fp4(cfg, rank, world, device, seed=0):
@@ -175,8 +190,10 @@ def build_masked_fp4(cfg, rank, world, device, seed=0):
     active = sum(1 for c in counts if c > 0)
     return dict(kind="fp4", a=a, sfa=sfa, b=b, sfb=sfb, d=torch.empty((g, stride, n), dtype=torch.bfloat16, device=device),
                 masked_m=torch.tensor(counts, dtype=torch.int32, device=device), counts=counts, g=g, n=n, k=k, m_total=g * stride,
-                # the weight scales are re-laid out once and then stay on the device, so only the packed values stream per call
-                flops=2.0 * n * k * valid, host_bytes=active * n * k * 0.5, segs=None)
+                # the weight scales are re-laid out once and then stay on the device, so only the packed values stream per call;
+                # host_bytes_with_scales is the figure that counts the (host-resident) scale bytes of the API tensors as well
+                flops=2.0 * n * k * valid, host_bytes=active * n * k * 0.5, host_bytes_with_scales=active * n * (k * 0.5 + k / 16.0),
+                segs=None)
 
 
 def run_op(w, a=None, sfa=None, d=None):
@@ -341,6 +358,270 @@ def _cpu_reference_fp4(w, threads, max_experts):
     return flops / dt / 1e12, f"{len(ops)} experts of this workload, torch CPU bf16 `a[:m] @ w.t()` per expert", "port", threads
 
 
+def pick_device(args, local_rank, world):
+    """GPU this rank runs on. With as many ranks as visible GPUs (or one rank) rank r uses GPU r. With fewer ranks than GPUs
+    the set of GPUs is chosen by measurement -- GPUs of one machine share host bridges, so which GPUs stream together
+    decides the host-link rate more than anything else: local rank 0 runs asymgemm_b200/linkprobe.py in a child process
+    (its CUDA contexts on the other GPUs die with it) and hands the map to the other ranks through a file named after
+    the launcher's pid. Returns (device index, record for the JSON line or None)."""
+    visible = torch.cuda.device_count()
+    if world <= 1 or world >= visible or args.device_map == "identity":
+        return local_rank, None
+    path = Path("/tmp") / f"asymgemm_b200_devmap_{os.getppid()}_{os.environ.get('MASTER_PORT', '0')}.json"
+    if local_rank == 0:
+        info = None
+        try:
+            res = subprocess.run([sys.executable, str(ROOT / "asymgemm_b200" / "linkprobe.py"), "--choose", str(world), "--visible", str(visible)],
+                                 capture_output=True, text=True, timeout=180)
+            if res.returncode == 0:
+                info = json.loads(res.stdout.strip().splitlines()[-1])
+            else:
+                info = {"devices": list(range(world)), "why": "link probe failed: " + res.stderr.strip()[-200:]}
+        except Exception as e:  # noqa: BLE001 -- any failure of the probe falls back to the identity map, and says so
+            info = {"devices": list(range(world)), "why": f"link probe failed: {type(e).__name__}: {e}"}
+        tmp = path.with_suffix(".tmp")
+        tmp.write_text(json.dumps(info))
+        os.replace(tmp, path)
+    else:
+        t0 = time.time()
+        while not path.exists():
+            if time.time() - t0 > 240:
+                raise RuntimeError("timed out waiting for local rank 0's device map")
+            time.sleep(0.05)
+        info = json.loads(path.read_text())
+    return int(info["devices"][local_rank]), (info, path)
+
+
+class RankLinks:
+    """This rank's host-link figures, each measured with a barrier between set-up and the streaming interval so that
+    "all ranks at once" really overlaps: copy-engine rate alone and together, and the SM-issued TMA read rate together."""
+
+    def __init__(self, lib, _lib, row_bytes, barrier, rank, world):
+        self.lib, self._lib = lib, _lib
+        ce, tma = _lib.c_void_p(), _lib.c_void_p()
+        _lib.check(lib.ag_link_probe_create(-1, 512 << 20, 0, 0, ce))
+        _lib.check(lib.ag_link_probe_create(-1, 512 << 20, 1, row_bytes, tma))
+        rate = _lib.c_double(0.0)
+        self.alone = 0.0
+        for r in range(world):          # one rank at a time, the others idle
+            barrier()
+            if r == rank:
+                _lib.check(lib.ag_link_probe_run(ce, 0.25, rate))
+                self.alone = rate.value
+        barrier()
+        _lib.check(lib.ag_link_probe_run(ce, 0.3, rate))
+        self.together = rate.value
+        barrier()
+        _lib.check(lib.ag_link_probe_run(tma, 0.3, rate))
+        self.tma_together = rate.value
+        barrier()
+        lib.ag_link_probe_destroy(ce)
+        lib.ag_link_probe_destroy(tma)
+
+
+def hbm_traffic_model(w, tile_bn=64, chunk_tiles=6, ka=2):
+    """HBM bytes of one launch of the host-streamed kernel, from this run's own segment table: A and its scales read once,
+    D written once, plus the scratch copy of every (segment, column tile) longer than one accumulator chunk (written once,
+    read once per further chunk). A rows are read by every column tile of their segment; tiles that run together share
+    them in L2, which is why the measured figure sits between this model and one more pass over A."""
+    if w.get("segs") is None:
+        return None
+    k_bytes = w["a"].shape[1] * w["a"].element_size()
+    kpad = (k_bytes + 128 * ka - 1) // (128 * ka) * (128 * ka)
+    n_tiles = (w["n"] + tile_bn - 1) // tile_bn
+    spill = replay = 0
+    for _, _, rows in w["segs"]:
+        chunks = ((rows + 127) // 128 + chunk_tiles - 1) // chunk_tiles
+        if chunks > 1:
+            spill += n_tiles * tile_bn * kpad
+            replay += n_tiles * tile_bn * kpad * (chunks - 1)
+    a = w["a"].numel() * w["a"].element_size() + (w["sfa"].numel() * 4 if w["sfa"] is not None else 0)
+    d = w["valid_rows"] * w["n"] * w["d"].element_size()
+    return {"a_and_scales_gb": round(a / 1e9, 3), "d_gb": round(d / 1e9, 3), "scratch_write_gb": round(spill / 1e9, 3),
+            "scratch_replay_gb": round(replay / 1e9, 3), "total_gb": round((a + d + spill + replay) / 1e9, 3)}
+
+
+def timed(fn, steps, barrier):
+    """ms per call of fn over `steps` calls, CUDA events on the current stream, barrier + synchronize on both sides."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def measure_device_resident(device, peaks, steps=20):
+    """The grouped GEMM with the weights resident in HBM (the tensor-bound regime) on cut-down twins of the FP8 and BF16
+    configurations: 32 experts with the routing density of the full configs, inputs larger than L2. For every kind the
+    automatic tile and the wide / deep-ring device tiles are timed and the best is reported with all figures beside it."""
+    import asymgemm_b200 as ag
+    out = {"note": "weights resident in HBM; 32-expert cuts (tokens cut in proportion) of the named configs; peak = bf16_tflops of "
+                   "MEASURED_PEAKS.json (x2 for 8-bit operands), of measured" if peaks else
+                   "weights resident in HBM; peak = 1590 TFLOP/s bf16 (x2 for 8-bit), of fallback"}
+    bf16_peak = peaks.get("bf16_tflops", 1590.0)
+    cases = [("fp8", "c3_fp8", False, (0, 6), 2.0), ("fp8_ue8m0", "c3_fp8", True, (0, 7), 2.0), ("bf16", "c2_bf16", False, (0, 6, 7), 1.0)]
+    for name, wl, ue, tiles, mult in cases:
+        cfg = dict(WORKLOADS[wl])
+        cfg["tokens"] = max(1, cfg["tokens"] * 32 // cfg["experts"])
+        cfg["experts"] = 32
+        w = build_workload(cfg, 0, 1, device, weights_on_device=True, ue8m0=ue)
+        ag.set_fp8_scale_mode("ue8m0" if ue else "fp32")
+        best = None
+        per_tile = {}
+        for t in tiles:
+            ag.set_tile_config(t)
+            for _ in range(3):
+                run_op(w)
+            ms = timed(lambda: run_op(w), steps, lambda: torch.cuda.synchronize(device))
+            ag.check_status()
+            tf = w["flops"] / (ms * 1e-3) / 1e12
+            per_tile["auto" if t == 0 else f"tile_config_{t}"] = round(tf, 1)
+            if best is None or tf > best[0]:
+                best = (tf, t, ms)
+        ag.set_tile_config(0)
+        ag.set_fp8_scale_mode("fp32")
+        peak = mult * bf16_peak
+        out[name] = {"tflops": round(best[0], 1), "ms_per_step": round(best[2], 4), "tile_config": best[1], "peak_tflops": round(peak, 1),
+                     "frac": round(best[0] / peak, 4), "by_tile_config": per_tile,
+                     "workload": f"{wl} cut to 32 experts: K={cfg['k']}, N={cfg['n']}, {w['valid_rows']} rows"}
+        del w
+        torch.cuda.empty_cache()
+    return out
+
+
+def cpu_moe_baseline(cfg, threads):
+    """The reference's CPU implementation of the whole MoE layer on a bounded twin of the workload (experts / 8, tokens
+    / 16): its INT8 bucket `moe_expert_forward_batch` (csrc/cpu/module.cpp:257-479, compiled from the reference's source into
+    oracle/_ref) and, beside it, the torch CPU bf16 per-expert loop (asym_gemm/training/frozen_linear.py:986-1008
+    semantics) on the same rows. Returns the record for the JSON line."""
+    import numpy as np
+    from oracle import oracle as O
+    from oracle import ref_cpu_moe as RM
+    h, i = cfg["hidden"], cfg["inter"]
+    experts = max(1, cfg["experts"] // 8)
+    rows_total = max(experts, cfg["tokens"] // 8 * cfg["top_k"])
+    rng = np.random.default_rng(0)
+    rows = np.full(experts, rows_total // experts, dtype=np.int64)
+    off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+    flops = float(off[-1]) * 2.0 * 3 * h * i
+    block = rng.standard_normal((min(int(off[-1]), 2048), h), dtype=np.float32)     # N(0,1) rows, repeated: values do not change the timing
+    x = np.tile(block, (-(-int(off[-1]) // block.shape[0]), 1))[: int(off[-1])]
+    sample = (f"{experts} experts x {int(rows[0])} rows of this layer (hidden {h}, inter {i}): experts / 8 and tokens / 8 of the "
+              "workload, balanced routing")
+    rec = {"unit": "TFLOP/s", "cores": threads, "sample": sample}
+    torch.set_num_threads(threads)
+    if RM.available():
+        one = rng.integers(-127, 128, size=(i, h), dtype=np.int8)            # one random expert, repeated (1.4 GB of draws otherwise)
+        sc = lambda *shape: np.full(shape, 0.02 / 127, dtype=np.float32)
+        gate, up = np.ascontiguousarray(np.broadcast_to(one, (experts, i, h))), np.ascontiguousarray(np.broadcast_to(one[::-1], (experts, i, h)))
+        down = np.ascontiguousarray(np.broadcast_to(one.reshape(h, i), (experts, h, i)))
+        x_bits = O.f32_to_bf16_bits(x)
+        out = np.zeros((int(off[-1]), h), dtype=np.float32)
+        rt = RM.runtime(0)
+        ids = np.arange(experts, dtype=np.int64)
+        RM.moe_expert_forward_batch(x_bits[: int(off[1])], off[:2], ids[:1], gate, sc(experts, i), up, sc(experts, i), down, sc(experts, h), rt,
+                                    out[: int(off[1])])          # warm the pool
+        t0 = time.perf_counter()
+        RM.moe_expert_forward_batch(x_bits, off, ids, gate, sc(experts, i), up, sc(experts, i), down, sc(experts, h), rt, out)
+        dt = time.perf_counter() - t0
+        rec.update({"value": round(flops / dt / 1e12, 4), "kind": "reference", "seconds": round(dt, 2), "cores": int(rt.threads() if callable(rt.threads) else rt.threads),
+                    "what": f"reference moe_expert_forward_batch (INT8 weights, bf16 activations, {RM.caps().get('int8_rm_backend')})"})
+        del gate, up, down, out, x_bits
+    # torch CPU bf16 loop on the same rows
+    xt = torch.from_numpy(x).to(torch.bfloat16)
+    w13 = (torch.randn((2 * i, h)) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn((h, i)) * 0.02).to(torch.bfloat16)
+    (xt[:64] @ w13.t())
+    t0 = time.perf_counter()
+    for e in range(experts):
+        hh = xt[off[e]:off[e + 1]] @ w13.t()
+        act = (torch.nn.functional.silu(hh[:, :i].float()) * hh[:, i:].float()).to(torch.bfloat16)
+        act @ w2.t()
+    dt = time.perf_counter() - t0
+    rec["torch_bf16_loop"] = {"value": round(flops / dt / 1e12, 4), "unit": "TFLOP/s", "kind": "port", "cores": threads, "seconds": round(dt, 2)}
+    if "value" not in rec:
+        rec.update({"value": rec["torch_bf16_loop"]["value"], "kind": "port", "what": "torch CPU bf16 per-expert loop"})
+    return rec
+
+
+def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone_sum, steps):
+    """The expert-parallel FP8 MoE layer at this N: ms per step (max over ranks), TFLOP/s, weight GB/s (aggregate and per
+    rank), per-phase CUDA-event breakdown of an unpipelined step, bytes crossing NVLink, and the parity of a sample of this
+    rank's tokens against the dense fp32 restatement (outside the timed region)."""
+    import asymgemm_b200 as ag
+    import torch.distributed as dist
+    from asymgemm_b200.testing import calc_diff, max_rel_err
+    from asymgemm_b200.testing.moe_reference import dense_moe_reference, expert_weights
+    ue = args.fp8_scales == "ue8m0"
+    w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=ue, pipeline_groups=args.pipeline_groups)
+    layer = w["layer"]
+    step = lambda: layer.forward(w["x"], w["ids"], w["w"])
+    for _ in range(2):
+        y = step()
+    ag.check_status()
+    ms = timed(step, steps, barrier)
+    ag.check_status()
+    # per-phase breakdown: two more steps with events at the phase boundaries (unpipelined path only)
+    phases = None
+    if not (args.pipeline_groups > 1 and world > 1):
+        acc = {}
+        for _ in range(2):
+            layer.phase_events = []
+            step()
+            torch.cuda.synchronize(device)
+            ev = layer.phase_events
+            for (_, a), (name, b) in zip(ev[:-1], ev[1:]):
+                acc[name] = acc.get(name, 0.0) + a.elapsed_time(b) / 2
+        layer.phase_events = None
+        phases = {k: round(v, 3) for k, v in acc.items()}
+    # parity of a sample of this rank's tokens (their experts may live on any rank: weights are rebuilt from the seed)
+    sample = min(args.parity_tokens, w["x"].shape[0])
+    h, i = cfg["hidden"], cfg["inter"]
+    ref = dense_moe_reference(w["x"][:sample], w["ids"][:sample], w["w"][:sample],
+                              lambda e: expert_weights(w["seed"], e, h, i, device, use_ue8m0=ue), i, use_ue8m0=ue)
+    got = y[:sample].float()
+    stats = torch.tensor([ms, w["flops"], w["host_bytes"], w["host_bytes"] / (ms * 1e-3) / 1e9, max_rel_err(got, ref), calc_diff(got, ref),
+                          w["nvlink_bytes"]], dtype=torch.float64, device=device)
+    if world > 1:
+        mx, sm, mn = stats.clone(), stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        if phases is not None:
+            keys = sorted(phases)
+            pt = torch.tensor([phases[k] for k in keys], dtype=torch.float64, device=device)
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+            phases = {k: round(v, 3) for k, v in zip(keys, pt.tolist())}
+    else:
+        mx = sm = mn = stats
+    ms_all = mx[0].item()
+    rec = {
+        "workload": (f"FP8 MoE layer, {cfg['experts']} experts over {world} rank(s), gate+up K={h} N={2 * i}, SiLU*mul, down K={i} N={h}, "
+                     f"{cfg['tokens']} tokens x top-{cfg['top_k']} (softmax of N(0,1) logits), weights in pinned host memory per rank"
+                     + (", NCCL all-to-all(v) dispatch and combine" if world > 1 else ", one rank: no exchange")),
+        "ms_per_step": round(ms_all, 3), "steps": steps,
+        "tflops": round(sm[1].item() / (ms_all * 1e-3) / 1e12, 2),
+        "weight_gbs": round(sm[2].item() / (ms_all * 1e-3) / 1e9, 2),
+        "per_rank_weight_gbs_min_max": [round(mn[3].item(), 2), round(mx[3].item(), 2)],
+        "frac_of_link_peak_sum": round(sm[2].item() / (ms_all * 1e-3) / 1e9 / link_alone_sum, 4) if link_alone_sum > 0 else None,
+        "phase_ms_max_over_ranks": phases,
+        "nvlink_gb_per_step": round(sm[6].item() / 1e9, 3),
+        "parity_tokens_per_rank": sample, "parity_max_rel": float(f"{mx[4].item():.3e}"), "parity_calc_diff": float(f"{mx[5].item():.3e}"),
+        "parity_against": "dense fp32 restatement of the layer on dequantised operands (asymgemm_b200/testing/moe_reference.py), "
+                          "worst rank; tolerance of the FP8 path: max-rel <= 2e-2",
+        "experts_per_rank": [hi - lo for lo, hi in ranges] if ranges is not None else [cfg["experts"] // world] * world,
+        "gemm_launches_per_step": 2 * (args.pipeline_groups if world > 1 else 1),
+    }
+    if args.pipeline_groups > 1 and world > 1:
+        rec["pipeline_groups"] = args.pipeline_groups
+    del w, layer, y
+    torch.cuda.empty_cache()
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -353,7 +634,7 @@ def main():
                     help="override the token count of the workload (decode-sized batches leave experts without rows: the in-kernel "
                          "stream skips those, the staged path copies them all); 0 = the named config")
     ap.add_argument("--pipeline-groups", type=int, default=1,
-                    help="c5_moe_fp8 on several GPUs: run the layer in this many rounds over groups of each rank's experts so that "
+                    help="MoE layer on several GPUs: run the layer in this many rounds over groups of each rank's experts so that "
                          "the token exchanges overlap the GEMMs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weights", default="host", choices=["host", "device", "staged"],
@@ -371,7 +652,14 @@ def main():
     ap.add_argument("--cache-experts", type=int, default=0,
                     help="keep this many of the most popular experts resident in HBM (HotExpertCache); the rest stream from the host")
     ap.add_argument("--even-shards", action="store_true",
-                    help="N > 1: give every rank the same number of experts even when the host links are measured unequal")
+                    help="N > 1: give every rank the same number of experts (no link calibration, no re-sharding)")
+    ap.add_argument("--device-map", default="auto", choices=["auto", "identity"],
+                    help="auto (default): with fewer ranks than visible GPUs, choose the GPUs by measuring their host links together; "
+                         "identity: rank r on GPU r")
+    ap.add_argument("--no-ep-layer", action="store_true", help="skip the `ep_layer` record (the expert-parallel MoE layer at this N)")
+    ap.add_argument("--ep-tokens", type=int, default=0, help="token count of the `ep_layer` record (default: the 65536 of the named config)")
+    ap.add_argument("--parity-tokens", type=int, default=256, help="tokens per rank checked against the dense restatement in `ep_layer`")
+    ap.add_argument("--no-device-resident", action="store_true", help="skip the `device_resident` record (one GPU only)")
     ap.add_argument("--huge-pages", action="store_true", help="back the pinned weights with transparent huge pages (mmap + madvise + cudaHostRegister)")
     ap.add_argument("--tile", type=int, default=0, help="force a tile configuration (0 = automatic)")
     ap.add_argument("--sms", type=int, default=0, help="cap the number of CTAs (0 = all SMs)")
@@ -402,45 +690,64 @@ def main():
             return 0
         return reference_arm(args, cfg, config)
 
-    device = torch.device("cuda", local_rank)
+    dev_index, devmap = pick_device(args, local_rank, world)
+    device = torch.device("cuda", dev_index)
     torch.cuda.set_device(device)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     import asymgemm_b200 as ag
     from asymgemm_b200 import _lib
+    from asymgemm_b200.ep import proportional_expert_ranges, rebalance_expert_ranges
 
+    if devmap is not None:
+        info, path = devmap
+        config["device_map"] = {"rank_to_gpu": info["devices"], "all_gpus_at_once_gbs": info.get("all_at_once_gbs"),
+                                "candidates": info.get("candidates"), "why": info.get("why")}
     moe = cfg["kind"] == "moe"
     on_dev = args.weights == "device"
     lib = _lib.load()
-    expert_range = None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def gather(value):
+        t = torch.zeros(world, dtype=torch.float64, device=device)
+        t[rank] = value
+        if world > 1:
+            dist.all_reduce(t)
+        return t.tolist()
+
+    # measured host-link figures (sustained, mean): copy engine alone / all ranks at once, TMA reads all ranks at once
+    row_bytes = max(128, int(cfg["hidden"] if moe else cfg["k"] * ELEM_BYTES[cfg["kind"]]) // 128 * 128)
+    links = RankLinks(lib, _lib, row_bytes, barrier, rank, world)
+    link_peak, link_peak_together, stream_ceiling = links.alone, links.together, links.tma_together
+    tma_rates = gather(links.tma_together)
+
     ranges = None
-    if world > 1 and cfg["kind"] != "fp4" and not on_dev and not args.even_shards:
-        # Shard sizes follow each rank's host-link rate measured with every rank streaming at once (copy-only TMA kernel).
-        from asymgemm_b200.ep import proportional_expert_ranges
-        rate = _lib.c_double(0.0)
-        row_b = max(128, int(cfg["hidden"] if moe else cfg["k"] * ELEM_BYTES[cfg["kind"]]) // 128 * 128)
-        dist.barrier()
-        _lib.check(lib.ag_measure_host_stream(1 << 30, row_b, 64, 2, 0, 2, rate))
-        rates = torch.zeros(world, dtype=torch.float64, device=device)
-        rates[rank] = rate.value
-        dist.all_reduce(rates)
-        ranges = proportional_expert_ranges(rates.tolist(), cfg["experts"])
-        expert_range = ranges[rank]
-        config["experts_per_rank"] = [hi - lo for lo, hi in ranges]
-        config["sharding"] = ("contiguous expert ranges sized by each rank's host-link rate measured with all ranks streaming at once "
-                              f"({[round(x, 1) for x in rates.tolist()]} GB/s); equal when the rates are within 10 %")
-    if moe:
-        w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=args.fp8_scales == "ue8m0",
-                      pipeline_groups=args.pipeline_groups)
-        if args.pipeline_groups > 1 and world > 1:
-            config["pipeline"] = (f"{args.pipeline_groups} rounds over groups of each rank's experts; exchanges on a second stream "
-                                  "overlap the GEMMs")
-    elif cfg["kind"] == "fp4":
-        w = build_masked_fp4(cfg, rank, world, device)
-    else:
-        w = build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages, expert_range=expert_range,
-                           ue8m0=args.fp8_scales == "ue8m0")
+    shard = world > 1 and cfg["kind"] != "fp4" and not on_dev and not args.even_shards
+    if shard:
+        ranges = proportional_expert_ranges(tma_rates, cfg["experts"])
+        config["sharding"] = {"how": "contiguous expert ranges; first cut in proportion to each rank's TMA read rate of pinned memory measured "
+                                     "with all ranks streaming at once (mean over 0.3 s; equal when within 10 %), then re-cut from the "
+                                     "ranks' own step times after the warm-up steps",
+                              "calibration_gbs": [round(x, 1) for x in tma_rates], "first_cut": [hi - lo for lo, hi in ranges]}
+
+    def build(rng):
+        if moe:
+            return build_moe(cfg, rank, world, device, None, expert_ranges=rng, ue8m0=args.fp8_scales == "ue8m0",
+                             pipeline_groups=args.pipeline_groups)
+        if cfg["kind"] == "fp4":
+            return build_masked_fp4(cfg, rank, world, device)
+        return build_workload(cfg, rank, world, device, weights_on_device=on_dev, huge_pages=args.huge_pages,
+                              expert_range=rng[rank] if rng is not None else None, ue8m0=args.fp8_scales == "ue8m0")
+
+    w = build(ranges)
+    if moe and args.pipeline_groups > 1 and world > 1:
+        config["pipeline"] = (f"{args.pipeline_groups} rounds over groups of each rank's experts; exchanges on a second stream "
+                              "overlap the GEMMs")
     if args.cache_experts > 0 and cfg["kind"] in ("fp8", "bf16") and not on_dev:
         from asymgemm_b200.expert_cache import HotExpertCache
         cache = HotExpertCache(w["b"], w["sfb"], args.cache_experts, device)
@@ -471,35 +778,40 @@ def main():
     if args.sms:
         ag.set_num_sms(args.sms)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(device)
+    def warm(wk, n):
+        """n untimed steps; returns this rank's mean ms per step over all but the first."""
+        ts = []
+        for _ in range(n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a.record()
+            run_op(wk)
+            b.record()
+            torch.cuda.synchronize(device)
+            ts.append(a.elapsed_time(b))
+        ag.check_status()
+        return sum(ts[1:]) / max(1, len(ts) - 1) if len(ts) > 1 else ts[0]
 
-    # measured host-link peak (copy engine, pinned -> device): each rank alone (the others idle), then all ranks at once
-    peak = _lib.c_double(0.0)
-    link_peak = 0.0
-    for r in range(world):
-        barrier()
-        if r == rank:
-            _lib.check(lib.ag_measure_host_link(1 << 30, 3, peak))
-            link_peak = peak.value
-    barrier()
-    _lib.check(lib.ag_measure_host_link(1 << 30, 3, peak))
-    link_peak_together = peak.value
-    barrier()
-    # copy-only TMA stream with the weight producer's access pattern, all ranks at once (reference for SM-issued reads)
-    row_bytes = int((cfg["hidden"] if moe else cfg["k"] * ELEM_BYTES[cfg["kind"]]))
-    row_bytes = max(128, row_bytes // 128 * 128)
-    _lib.check(lib.ag_measure_host_stream(1 << 30, row_bytes, 64, 2, 0, 2, peak))
-    stream_ceiling = peak.value
-    barrier()
+    my_ms = warm(w, args.warmup)
+    # closed loop: re-cut the expert ranges from what the ranks measured on real steps, rebuild, warm up again
+    if shard:
+        history = []
+        for _ in range(2):
+            step_ms = gather(my_ms)
+            new = rebalance_expert_ranges(ranges, step_ms)
+            history.append({"experts_per_rank": [hi - lo for lo, hi in ranges], "ms_per_rank": [round(x, 2) for x in step_ms]})
+            if new == ranges:
+                break
+            ranges = new
+            del w
+            torch.cuda.empty_cache()
+            w = build(ranges)
+            my_ms = warm(w, args.warmup)
+        config["sharding"]["closed_loop"] = history
+        config["experts_per_rank"] = [hi - lo for lo, hi in ranges]
 
-    for _ in range(args.warmup):
-        run_op(w)
-    ag.check_status()
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dev_index)
     if rank == 0:
         sampler.start()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -561,7 +873,7 @@ def main():
     e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(2, min(args.steps, 4))
+    e2e_steps = max(2, min(args.steps, 10))
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -579,16 +891,10 @@ def main():
         ag.set_weight_path("staged", chunk_bytes=args.stage_mb << 20)
         for _ in range(2):
             run_op(w)
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(args.steps):
-            run_op(w)
-        s1.record()
-        barrier()
-        alt_ms = s0.elapsed_time(s1) / args.steps
+        alt_ms = timed(lambda: run_op(w), args.steps, barrier)
         e2e_step()
         barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s0.record()
         for _ in range(e2e_steps):
             e2e_step()
@@ -624,16 +930,48 @@ def main():
         link_peak_sum = link_peak_min = link_peak
         together_sum = together_min = link_peak_together
 
+    # what the default line carries beside the headline: the expert-parallel layer at this N, the device-resident regime
+    h2d = int(a_host.numel() * a_host.element_size() + (sfa_host.numel() * sfa_host.element_size() if sfa_host is not None else 0))
+    d2h = int(d_host.numel() * d_host.element_size())
+    rank0_w = {k: w.get(k) for k in ("host_bytes", "flops", "m_total", "valid_rows", "n", "host_bytes_with_scales")}
+    traffic_model = hbm_traffic_model(w) if not moe and cfg["kind"] != "fp4" and args.weights == "host" and args.tile == 0 else None
+    launches = args.steps * gemm_launches_per_step(w, args)
+    extras = {}
+    default_line = args.workload == "c3_fp8" and args.weights == "host" and not args.cache_experts
+    cpu_sample = None
+    if world == 1 and not args.no_cpu_baseline and not moe:
+        cpu_sample = cpu_reference_sample(cfg, w, os.cpu_count() or 1, max_experts=8)
+    numa = w.get("numa_node")
+    del w, a_host, d_host, a_dev
+    if not moe:
+        del d_bufs, d_dev, sfa_host, sfa_dev
+    torch.cuda.empty_cache()
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    if default_line and not args.no_ep_layer:
+        ep_cfg = dict(WORKLOADS["c5_moe_fp8"])
+        if args.experts and args.experts < ep_cfg["experts"]:
+            ep_cfg["tokens"] = max(world, ep_cfg["tokens"] * args.experts // ep_cfg["experts"])
+            ep_cfg["experts"] = args.experts
+        if args.ep_tokens > 0:
+            ep_cfg["tokens"] = args.ep_tokens
+        ep_ranges = None
+        if ranges is not None and ranges[-1][1] == ep_cfg["experts"]:
+            ep_ranges = ranges            # the layer's weights have the same bytes per expert ratio on every rank: same cut
+        extras["ep_layer"] = measure_ep_layer(args, ep_cfg, rank, world, device, barrier, ep_ranges, link_peak_sum, steps=max(2, min(args.steps, 5)))
+        if world == 1 and not args.no_cpu_baseline and rank == 0:
+            extras["ep_layer"]["cpu_baseline"] = cpu_moe_baseline(ep_cfg, os.cpu_count() or 1)
+    if default_line and world == 1 and not args.no_device_resident:
+        extras["device_resident"] = measure_device_resident(device, peaks)
+
     if rank == 0:
         tflops = flops / (ms_step * 1e-3) / 1e12
         host_gbs = host_bytes / (ms_step * 1e-3) / 1e9
         # roofline of the one kernel in the step, on this rank's launch (rank 0) -- bound by the host link
-        ach = w["host_bytes"] / (kernel_ms * 1e-3) / 1e9
-        peaks = {}
-        try:
-            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
-        except Exception:
-            pass
+        ach = rank0_w["host_bytes"] / (kernel_ms * 1e-3) / 1e9
         tensor_peak = {"fp8": 2.0, "int8": 2.0, "bf16": 1.0, "moe": 2.0, "fp4": 4.0}[cfg["kind"]] * peaks.get("bf16_tflops", 1590.0)
         line = {
             "metric": "grouped-GEMM TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)",
@@ -649,30 +987,39 @@ def main():
                           "frac_of_peak_all_ranks_at_once": round(host_gbs / together_sum, 4),
                           "tma_copy_only_all_ranks_at_once_gbs_sum": round(ceil_sum, 2), "tma_copy_only_per_gpu_min_gbs": round(ceil_min, 2),
                           "per_rank_weight_gbs_min_max": [round(rank_gbs_min, 2), round(rank_gbs_max, 2)],
-                          "peak_how": "cudaMemcpyAsync pinned->device, 1 GiB, best of 3, measured in this run: peak_gbs_sum adds each "
-                                      "rank's rate measured while the others idle, peak_all_ranks_at_once adds the rates measured "
-                                      "with every rank copying at the same time; tma_copy_only is a copy-only TMA kernel with the weight "
-                                      "producer's access pattern on every SM, all ranks at once (a reference, not a bound). The step ends when the slowest rank ends, so "
-                                      "with even sharding weight_gbs <= n_gpus x the slowest rank's link rate"},
+                          "peak_how": "cudaMemcpyAsync pinned->device, 512 MiB buffer, mean over a sustained 0.25-0.3 s of copies, measured in "
+                                      "this run with a barrier between set-up and streaming: peak_gbs_sum adds each rank's rate measured "
+                                      "while the others idle, peak_all_ranks_at_once adds the rates measured with every rank copying at "
+                                      "the same time; tma_copy_only is a copy-only TMA kernel with the weight producer's access pattern "
+                                      "on every SM, all ranks at once (a reference, not a bound). The step ends when the slowest rank "
+                                      "ends, so weight_gbs <= sum over ranks of (its experts' bytes / the slowest rank's time)"},
             "roofline": {"bound": "host_link", "achieved": round(ach, 2), "peak": round(link_peak, 2), "unit": "GB/s",
                          "frac": round(ach / link_peak, 4),
-                         "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload] * w["m_total"] / 1e9, 3)
-                                     if args.workload in NCU_DRAM_BYTES_PER_ROW and not moe else None),
-                         "traffic_unit": "GB of HBM traffic per launch, scaled by rows from an ncu capture of a smaller case",
-                         "algorithmic_gb": round(w["host_bytes"] / 1e9, 3),
+                         "frac_of_peak_all_ranks_at_once": round(ach / link_peak_together, 4) if link_peak_together > 0 else None,
+                         "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload] * rank0_w["m_total"] / 1e9, 3)
+                                     if args.workload in NCU_DRAM_BYTES_PER_ROW and not moe and args.weights == "host" else None),
+                         "traffic_unit": "GB of HBM traffic per launch: ncu dram bytes per padded row of a cut-down capture of this workload "
+                                         "x the padded rows of this launch (traffic grows with rows, not with the weights)",
+                         "traffic_model": traffic_model,
+                         "algorithmic_gb": round(rank0_w["host_bytes"] / 1e9, 3),
                          "note": "algorithmic bytes = each active expert's weights once (N*K*bytes); the kernel is bound by the PCIe "
-                                 "host link, not HBM or tensor throughput: peak is the copy-engine rate measured in this run",
-                         "tensor_frac_of_measured": round(w["flops"] / (kernel_ms * 1e-3) / 1e12 / tensor_peak, 5)},
-            "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
-                    "h2d_bytes_per_step": int(a_host.numel() * a_host.element_size()
-                                              + (sfa_host.numel() * sfa_host.element_size() if sfa_host is not None else 0)),
-                    "d2h_bytes_per_step": int(d_host.numel() * d_host.element_size()),
+                                 "host link, not HBM or tensor throughput: peak is the copy-engine rate of this rank's link measured "
+                                 "alone in this run (frac_of_peak_all_ranks_at_once: against its rate with every rank copying); "
+                                 "traffic_model is computed from this run's segment table",
+                         "tensor_frac_of_measured": round(rank0_w["flops"] / (kernel_ms * 1e-3) / 1e12 / tensor_peak, 5)},
+            "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "weights are read from pinned host memory inside the kernel in both timings"},
-            "gpu_launches": args.steps * gemm_launches_per_step(w, args),
+            "gpu_launches": launches,
             "clocks": clocks,
         }
+        if rank0_w.get("host_bytes_with_scales"):
+            line["host_link"]["weight_gbs_counting_scale_bytes"] = round(rank0_w["host_bytes_with_scales"] / (ms_step * 1e-3) / 1e9, 2)
+            line["host_link"]["scale_bytes_note"] = ("weight_gbs counts the packed values, which cross the link every call; the weight scales "
+                                                     "(K/16 bytes per row) are re-laid out once and then stay in HBM, so they are not per-call "
+                                                     "traffic; the second figure counts them as the per-call definition of the config does")
         if on_dev and not moe:
-            tf = w["flops"] / (kernel_ms * 1e-3) / 1e12
+            tf = rank0_w["flops"] / (kernel_ms * 1e-3) / 1e12
             line["roofline"] = {"bound": "tensor", "achieved": round(tf, 2), "peak": round(tensor_peak, 1), "unit": "TFLOP/s",
                                 "frac": round(tf / tensor_peak, 4), "traffic": None,
                                 "note": "weights resident in HBM: bound by the tensor pipe; peak = MEASURED_PEAKS.json bf16_tflops"
@@ -694,13 +1041,22 @@ def main():
             line["e2e"]["note"] = "weights are copied from pinned host memory by the copy engine inside both timings"
         if moe:
             line["metric"] = "MoE-layer TFLOPS (with host->GPU weight GB/s vs measured PCIe peak)"
-            line["config"]["numa_node_of_weights"] = w["numa_node"]
-            line["roofline"]["note"] += "; the step holds two grouped-GEMM launches plus torch glue kernels and two NCCL all-to-alls, achieved is over the whole step"
-        if world == 1 and not args.no_cpu_baseline and not moe:
-            threads = os.cpu_count() or 1
-            v, sample, kind, cores = cpu_reference_sample(cfg, w, threads, max_experts=8)
+            line["config"]["numa_node_of_weights"] = numa
+            line["roofline"]["note"] += "; the step holds two grouped-GEMM launches plus helper kernels and two NCCL all-to-alls, achieved is over the whole step"
+            if world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_moe_baseline(cfg, os.cpu_count() or 1)
+        if cpu_sample is not None:
+            v, sample, kind, cores = cpu_sample
             line["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
+        line.update(extras)
+        if "ep_layer" in extras:
+            line["gpu_launches"] += extras["ep_layer"]["gemm_launches_per_step"] * (extras["ep_layer"]["steps"] + 4)
         print(json.dumps(line))
+        if devmap is not None:
+            try:
+                devmap[1].unlink()
+            except OSError:
+                pass
     if world > 1:
         dist.destroy_process_group()
     return 0

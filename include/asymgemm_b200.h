@@ -254,6 +254,18 @@ int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
 int ag_measure_host_stream(uint64_t bytes, int64_t row_bytes, int32_t box_rows, int32_t boxes_per_stage, int32_t num_ctas,
                            int32_t reps, double* gbps_out);
 
+/* Sustained host-link measurement in three steps, so that several GPUs can be timed while they really stream at the same
+ * time. ag_link_probe_create (slow and unevenly long: allocates and touches `bytes` of pinned memory, the device side and
+ * one untimed pass) for `device` (-1 = the current one); then a barrier of the caller's between the ranks or threads that
+ * measure together; then ag_link_probe_run streams for at least `min_seconds` and reports the MEAN GB/s over the whole
+ * run (not the best pass); ag_link_probe_destroy frees everything. mode 0 = copy engine (cudaMemcpyAsync pinned -> device),
+ * mode 1 = SM-issued TMA reads with the weight producer's access pattern (rows of `row_bytes`, a multiple of 128).
+ * A probe may be run repeatedly. Reference counterpart: none. */
+typedef struct ag_link_probe ag_link_probe_t;
+int ag_link_probe_create(int32_t device, uint64_t bytes, int32_t mode, int64_t row_bytes, ag_link_probe_t** out);
+int ag_link_probe_run(ag_link_probe_t* probe, double min_seconds, double* gbps_mean);
+int ag_link_probe_destroy(ag_link_probe_t* probe);
+
 /* sizeof(ag_gemm_desc_t) as this library was compiled: lets a binding written in another language (ctypes, cgo, JNI)
  * check its mirror of the struct before the first call. */
 uint64_t ag_gemm_desc_size(void);

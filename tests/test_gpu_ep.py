@@ -97,6 +97,58 @@ def test_moe_layer_single_rank():
     assert err <= 3e-2, f"max-rel {err:.3e}"
 
 
+def test_moe_layer_stages_meet_the_gemm_tolerance_on_their_own_inputs():
+    """The FP8 tolerance of this path (max-rel <= 2e-2 against the fp32 dequantised reference) is stated per GEMM. The layer
+    chains two of them with a requantisation in between, where a one-ulp difference in a bf16 intermediate can move an FP8
+    code of the next stage's input; so the end-to-end figure of the tests above is held to 3e-2, and this test holds every
+    stage to the stated tolerance on the operands the layer itself produced: gate+up GEMM and down GEMM against the CPU
+    oracle, the activation + requantisation against the quantiser applied to the layer's own gate+up output."""
+    import numpy as np
+    from asymgemm_b200 import ep
+    from asymgemm_b200.utils import per_token_cast_to_fp8
+    from oracle import oracle
+    from tests import helpers as H
+    device = torch.device("cuda", 0)
+    num_experts, hidden, inter, tokens, top_k = 8, 512, 256, 300, 2
+    w13, s13, w2, s2 = _make_weights(num_experts, hidden, inter, device)
+    layer = ep.ExpertParallelMoE(num_experts, hidden, inter, (w13.contiguous().pin_memory(), s13.contiguous().to(device)),
+                                 (w2.contiguous().pin_memory(), s2.contiguous().to(device)))
+    layer.keep_intermediates = True
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn((tokens, hidden), generator=gen).to(torch.bfloat16).to(device)
+    wts, ids = torch.topk(torch.softmax(torch.randn((tokens, num_experts), generator=gen), -1), top_k, dim=-1)
+    layer.forward(x, ids.to(device), (wts / wts.sum(-1, keepdim=True)).to(device))
+    torch.cuda.synchronize()
+    it = layer.intermediates
+    state = it["state"]
+    segments = oracle.contiguous_segments(state.offsets.cpu().tolist(), state.experts.cpu().tolist(), None, state.padded_rows)
+    valid = np.zeros(state.padded_rows, dtype=bool)
+    rows_per_expert = state.rows_per_expert.cpu().tolist()
+    for e, r0, _ in segments:
+        valid[r0:r0 + rows_per_expert[e]] = True
+    # stage 1: gate+up GEMM on the layer's quantised tokens
+    ref1 = oracle.gemm_fp8(H.np_bits(it["a_q"]), it["sfa"].cpu().numpy(), H.np_bits(w13), s13.numpy(), segments)
+    got1 = it["d1"].float().cpu().numpy()
+    assert oracle.max_rel(got1[valid], ref1[valid]) <= 2e-2
+    # stage 2: bf16(silu(gate) * up) of the layer's own d1, quantised 1x128: scales agree to fp32 rounding, codes differ only
+    # where the device's expf and torch's exp round a bf16 activation differently
+    d1 = it["d1"].float()
+    g, u = d1[:, :inter], d1[:, inter:]
+    act = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16).float()
+    q_ref, sf_ref = per_token_cast_to_fp8(act, use_ue8m0=False)
+    vmask = torch.from_numpy(valid).to(device)
+    assert ((it["s2"] - sf_ref).abs()[vmask] <= 1e-2 * sf_ref[vmask]).all()
+    assert (it["a2"].view(torch.uint8)[vmask] != q_ref.view(torch.uint8)[vmask]).float().mean() < 1e-2
+    deq = it["a2"].float() * it["s2"].repeat_interleave(128, 1)[:, :inter]
+    amax = act.view(act.shape[0], -1, 128).abs().amax(dim=2).repeat_interleave(128, 1)
+    assert ((deq - act).abs()[vmask] <= (amax * 0.0625 + 1e-6)[vmask]).all()      # within half an e4m3 step of the block maximum
+    # stage 3: down GEMM on the layer's own requantised activations
+    ref2 = oracle.gemm_fp8(H.np_bits(it["a2"]), it["s2"].cpu().numpy(), H.np_bits(w2), s2.numpy(), segments)
+    got2 = it["d2"].float().cpu().numpy()
+    assert oracle.max_rel(got2[valid], ref2[valid]) <= 2e-2
+    assert oracle.calc_diff(got2[valid], ref2[valid]) <= 1e-3
+
+
 def test_moe_layer_single_rank_staged_weights():
     import asymgemm_b200 as ag
     err = _case(0, 1, torch.device("cuda", 0), weight_path="staged")

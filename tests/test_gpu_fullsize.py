@@ -26,10 +26,13 @@ def _dequant_b(w, e, n0, n1):
     return b
 
 
-@pytest.mark.parametrize("name,experts", [("c3_fp8", 64), ("c2_bf16", 0), ("c1_int8", 0)])
+@pytest.mark.parametrize("name,experts", [("c3_fp8", 0), ("c2_bf16", 0), ("c2b_bf16", 0), ("c1_int8", 0)])
 def test_full_size_properties(name, experts):
+    """Every benchmark configuration of the plain grouped GEMM at its full size: all 256 experts of the FP8 case (7.5 GB of
+    weights in pinned memory), both BF16 GEMMs (K = 2048 and the K = 768 one, whose K is not a multiple of the 512-byte
+    stage) and the INT8 case."""
     cfg = dict(bench.WORKLOADS[name])
-    if experts:  # the 256-expert FP8 case keeps its shapes and routing law but a quarter of the experts (1.9 GB of weights)
+    if experts:
         cfg["tokens"] = cfg["tokens"] * experts // cfg["experts"]
         cfg["experts"] = experts
     w = bench.build_workload(cfg, 0, 1, torch.device("cuda", 0))
@@ -87,4 +90,47 @@ def test_full_size_nvfp4_masked_properties():
         ref = a @ b.t()
         err = (w["d"][e, :rows, n0:n0 + 128].float() - ref).abs().max() / ref.abs().max().clamp_min(1e-9)
         worst = max(worst, float(err))
+    assert worst <= 2e-2, f"max-rel {worst:.3e}"
+
+
+def test_full_size_moe_down_projection_on_requantised_activations():
+    """The down GEMM of the FP8 MoE layer at its full shape (K = 2048, N = 7168) on activations produced the way the layer
+    produces them: a bf16 gate|up tensor through the fused SiLU*mul + 1x128 requantisation kernel. 32 experts with the
+    layer's 2048 rows per expert on average (Zipf routing makes them ragged); sampled blocks against torch fp32 on the
+    dequantised operands, run-to-run bit identity."""
+    from asymgemm_b200 import moe_ops
+    from asymgemm_b200.utils import build_contiguous_layout, per_block_cast_to_fp8
+    dev = torch.device("cuda", 0)
+    experts, inter, hidden = 32, 2048, 7168
+    counts = bench.rows_per_expert(dict(experts=experts, tokens=8192, top_k=8, zipf=0.8), seed=3)
+    offsets, expert_ids, list_size, m_total, segs = build_contiguous_layout(counts, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(4)
+    gate_up = torch.zeros((m_total, 2 * inter), dtype=torch.bfloat16, device=dev)
+    for _, start, rows in segs:
+        gate_up[start:start + rows] = (torch.randn((rows, 2 * inter), device=dev, generator=gen) * 1.5).to(torch.bfloat16)
+    a2, s2 = moe_ops.silu_mul_quant_fp8(gate_up, inter)
+    w2 = torch.empty((experts, hidden, inter), dtype=torch.float8_e4m3fn).pin_memory()
+    sf2 = torch.empty((experts, hidden // 128, inter // 128), dtype=torch.float32, device=dev)
+    for e in range(experts):
+        q, s = per_block_cast_to_fp8(torch.randn((hidden, inter), device=dev, generator=gen) * 0.02, use_ue8m0=False)
+        w2[e].copy_(q, non_blocking=True)
+        sf2[e] = s
+    torch.cuda.synchronize()
+    d = torch.full((m_total, hidden), float("nan"), dtype=torch.bfloat16, device=dev)
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), (w2, sf2), d, offsets, expert_ids, None)
+    ag.check_status()
+    d1 = d.clone()
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), (w2, sf2), d, offsets, expert_ids, None)
+    ag.check_status()
+    assert torch.equal(d1.view(torch.int16), d.view(torch.int16)), "two runs differ"
+    cpu_gen = torch.Generator().manual_seed(0)
+    worst = 0.0
+    for e, start, rows in segs:
+        seg = d[start:start + rows].float()
+        assert torch.isfinite(seg).all()
+        n0 = int(torch.randint(0, hidden // 128, (1,), generator=cpu_gen)) * 128
+        a = a2[start:start + rows].float() * s2[start:start + rows].repeat_interleave(128, 1)
+        b = w2[e, n0:n0 + 128].to(dev).float() * sf2[e, n0 // 128].repeat_interleave(128).unsqueeze(0)
+        ref = a @ b.t()
+        worst = max(worst, float((seg[:, n0:n0 + 128] - ref).abs().max() / ref.abs().max().clamp_min(1e-9)))
     assert worst <= 2e-2, f"max-rel {worst:.3e}"

@@ -13,7 +13,7 @@ from tests.test_gpu_parity import _check, _run_contiguous, _run_masked
 pytestmark = pytest.mark.gpu
 
 K_STEP = {"bf16": 8, "fp8": 16, "int8": 128, "fp4": 32}
-TILES = {"bf16": [0, 1, 2, 3, 4], "fp8": [0, 1, 2, 3, 4, 5], "int8": [0, 1, 2, 3, 4, 5], "fp4": [0, 1, 4]}
+TILES = {"bf16": [0, 1, 2, 3, 4, 6, 7], "fp8": [0, 1, 2, 3, 4, 5, 6], "int8": [0, 1, 2, 3, 4, 5, 6], "fp4": [0, 1, 4, 7]}
 
 
 def _random_case(rng: random.Random):
@@ -77,7 +77,7 @@ def test_random_case_fp8_hardware_scaled(seed):
     masked = rng.random() < 0.4
     groups = rng.randint(1, 5)
     n, k = 8 * rng.randint(1, 60), 16 * rng.randint(1, 64)
-    tile = rng.choice([0, 1, 4])
+    tile = rng.choice([0, 1, 4, 7])
     host = rng.random() < 0.6
     counts = [rng.choice([0, rng.randint(1, 400), rng.randint(1, 400), rng.randint(1800, 2600)]) for _ in range(groups)]
     if sum(counts) == 0:

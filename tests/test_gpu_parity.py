@@ -67,6 +67,10 @@ def _skip_unsupported(kind, tile):
         pytest.skip("NVFP4 has 64- and 128-column tile configurations only")
     if tile == 5 and kind not in ("fp8", "int8"):
         pytest.skip("register accumulators exist for the software-scaled kinds only")
+    if tile == 6 and kind == "fp4":
+        pytest.skip("256-column items exist for bf16, fp8 and int8")
+    if tile == 7 and kind in ("fp8", "int8"):
+        pytest.skip("the deep activation ring exists for bf16 and the hardware-scaled kinds")
 
 
 @pytest.mark.parametrize("kind", KINDS)
@@ -89,7 +93,7 @@ def tile(request):
 
 
 @pytest.mark.parametrize("kind", KINDS)
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5], indirect=True)
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6, 7], indirect=True)
 @pytest.mark.parametrize("b_on_host", [True, False])
 def test_contiguous_ragged_multi_tile(kind, tile, b_on_host):
     """Ragged row counts, empty experts, segments longer than one accumulator chunk in every tile configuration
@@ -126,7 +130,7 @@ def test_contiguous_no_scratch_matches(kind, tile):
 
 
 @pytest.mark.parametrize("kind", KINDS)
-@pytest.mark.parametrize("tile", [0, 1, 3, 5], indirect=True)
+@pytest.mark.parametrize("tile", [0, 1, 3, 5, 6, 7], indirect=True)
 def test_masked(kind, tile):
     """Masked layout incl. an empty group and a full group (reference case: tests/m_grouped/...:320-342)."""
     _skip_unsupported(kind, tile)
@@ -332,7 +336,7 @@ def test_two_streams_do_not_share_replay_scratch():
         _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
 
 
-@pytest.mark.parametrize("tile", [0, 1, 4], indirect=True)
+@pytest.mark.parametrize("tile", [0, 1, 4, 7], indirect=True)
 @pytest.mark.parametrize("b_on_host", [True, False])
 def test_fp8_hardware_ue8m0_scaling_contiguous(tile, b_on_host):
     """FP8 with the block scales applied by the tensor core (UE8M0): exact for power-of-two scales, so it must agree with

@@ -183,6 +183,39 @@ def test_proportional_expert_ranges():
         pr([1.0, 1.0, 1.0], 2)
 
 
+def test_rebalance_expert_ranges_from_step_times():
+    """Closed loop of the sharding: ranks that took longer per step hand experts to ranks that took less."""
+    from asymgemm_b200.ep import rebalance_expert_ranges as rb
+    even = [(0, 64), (64, 128), (128, 192), (192, 256)]
+    assert rb(even, [38.0, 38.5, 37.9, 38.2]) == even                    # within tolerance: untouched
+    new = rb(even, [64.0, 64.0, 38.0, 38.0])                              # two ranks on a shared, slower host bridge
+    sizes = [hi - lo for lo, hi in new]
+    assert sum(sizes) == 256 and new[0][0] == 0 and new[-1][1] == 256 and all(new[i][1] == new[i + 1][0] for i in range(3))
+    assert sizes[0] < 64 < sizes[2] and abs(sizes[0] - sizes[1]) <= 1 and abs(sizes[2] - sizes[3]) <= 1
+    # predicted step times with the measured rates (experts per ms) are balanced to within one expert
+    rates = [64 / 64.0, 64 / 64.0, 64 / 38.0, 64 / 38.0]
+    t = [n / r for n, r in zip(sizes, rates)]
+    assert max(t) - min(t) <= 1.0 / min(rates) + 1e-9
+    # a second round on the new cut with times that now agree changes nothing
+    assert rb(new, t) == new
+    with pytest.raises(RuntimeError):
+        rb(even, [1.0, 2.0])
+
+
+def test_link_probe_candidate_sets():
+    """Choice of GPUs from concurrent link rates: groups by rate, and candidate sets that spread over the groups."""
+    from asymgemm_b200 import linkprobe as lp
+    rates = [23.1, 22.8, 23.4, 23.0, 35.2, 34.8, 35.0, 34.5]             # two host bridges, one more loaded
+    assert lp.rate_groups(rates) == [[4, 5, 6, 7], [0, 1, 2, 3]]
+    assert lp.rate_groups([50.0, 50.5, 49.8]) == [[0, 1, 2]]
+    sets = lp.candidate_sets(rates, 4)
+    assert [0, 1, 2, 3] == sets[0] and [4, 5, 6, 7] in sets and [0, 1, 4, 5] in sets and [0, 2, 4, 6] in sets
+    assert all(len(s) == 4 and len(set(s)) == 4 for s in sets)
+    assert lp.candidate_sets(rates, 8) == [list(range(8))]
+    assert lp.candidate_sets([50.0] * 8, 2)[0] == [0, 1]
+    assert lp.choose_devices(8, 8)["devices"] == list(range(8))         # nothing to choose: no probe, no GPU needed
+
+
 def test_hot_expert_cache_table_split():
     from asymgemm_b200.expert_cache import HotExpertCache
     c = HotExpertCache.__new__(HotExpertCache)
