@@ -64,18 +64,47 @@ def build_torch_ops(force: bool = False) -> Path:
     from torch.utils import cpp_extension as ce
     cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
     tmp = TORCH_OPS_PATH.with_suffix(".so.tmp")
-    cmd = [os.environ.get("CXX") or shutil.which("g++") or "g++", "-O2", "-std=c++17", "-fPIC", "-shared", str(TORCH_OPS_SRC),
-           "-o", str(tmp), f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
-    for inc in ce.include_paths() + [str(Path(cuda_home) / "include")]:
-        cmd += ["-isystem", inc]
-    for lib in ce.library_paths():
-        cmd += ["-L", lib]
-    cmd += ["-L", str(LIB_DIR), "-lasymgemm_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-Wl,-rpath,$ORIGIN"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"building the torch extension failed:\n{res.stdout}\n{res.stderr}")
+    # Host compilers to try, the system one first. The extension throws c10::Error across its boundary and formats
+    # messages with iostreams, so it must share the process's libstdc++: a toolchain whose default link pulls in a static
+    # libstdc++ (a private copy with its own, never initialised, locale) builds a library that crashes on its first
+    # error message. The result is checked, and the next candidate is tried when libstdc++.so is not among its dependencies.
+    cands = []
+    for c in (os.environ.get("ASYMGEMM_CXX"), shutil.which("g++"), "/usr/bin/g++", os.environ.get("CXX")):
+        if c and c not in cands and (Path(c).exists() or shutil.which(c)):
+            cands.append(c)
+    if not cands:
+        raise RuntimeError("no host C++ compiler found (set ASYMGEMM_CXX)")
+    last = ""
+    for cxx in cands:
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", str(TORCH_OPS_SRC),
+               "-o", str(tmp), f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+        for inc in ce.include_paths() + [str(Path(cuda_home) / "include")]:
+            cmd += ["-isystem", inc]
+        for lib in ce.library_paths():
+            cmd += ["-L", lib]
+        cmd += ["-L", str(LIB_DIR), "-lasymgemm_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-Wl,-rpath,$ORIGIN"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            last = f"{cxx}: building the torch extension failed:\n{res.stdout}\n{res.stderr}"
+            continue
+        if b"libstdc++.so" not in _needed_libraries(tmp):
+            last = f"{cxx} linked libstdc++ statically into the torch extension"
+            continue
+        break
+    else:
+        raise RuntimeError(last)
     os.replace(tmp, TORCH_OPS_PATH)
     return TORCH_OPS_PATH
+
+
+def _needed_libraries(path: Path) -> bytes:
+    """The DT_NEEDED lines of a shared library as readelf prints them. Without readelf the check cannot be made and the
+    library is accepted as built."""
+    readelf = shutil.which("readelf")
+    if readelf is None:
+        return b"libstdc++.so (unchecked: readelf not found)"
+    res = subprocess.run([readelf, "-d", str(path)], capture_output=True)
+    return b"\n".join(ln for ln in res.stdout.splitlines() if b"NEEDED" in ln)
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:

@@ -77,17 +77,21 @@ void m_grouped_gemm_nt(int64_t kind, int64_t layout, const at::Tensor& a, const 
     desc.stage_chunk_bytes = static_cast<uint64_t>(stage_chunk_bytes > 0 ? stage_chunk_bytes : 0);
   }
 
-  const c10::cuda::CUDAGuard guard(a.device());
-  desc.stream = c10::cuda::getCurrentCUDAStream(a.device().index()).stream();
   int rc = AG_E_INVALID;
-  switch (kind) {
-    case 0: rc = ag_m_grouped_bf16_gemm_nt(&desc); break;
-    case 1: rc = ag_m_grouped_fp8_gemm_nt(&desc); break;
-    case 2: rc = ag_m_grouped_int8_gemm_nt(&desc); break;
-    case 3: rc = ag_m_grouped_fp4_gemm_nt(&desc); break;
-    case 4: rc = ag_m_grouped_fp8_ue8m0_gemm_nt(&desc); break;
-    default: TORCH_CHECK(false, "asymgemm_b200: unknown kind ", kind);
+  {
+    // device guard and launch in a scope of their own: a failure is raised after the guard has been released
+    const c10::cuda::CUDAGuard guard(a.device());
+    desc.stream = c10::cuda::getCurrentCUDAStream(a.device().index()).stream();
+    switch (kind) {
+      case 0: rc = ag_m_grouped_bf16_gemm_nt(&desc); break;
+      case 1: rc = ag_m_grouped_fp8_gemm_nt(&desc); break;
+      case 2: rc = ag_m_grouped_int8_gemm_nt(&desc); break;
+      case 3: rc = ag_m_grouped_fp4_gemm_nt(&desc); break;
+      case 4: rc = ag_m_grouped_fp8_ue8m0_gemm_nt(&desc); break;
+      default: rc = AG_E_UNSUPPORTED; break;
+    }
   }
+  TORCH_CHECK(rc != AG_E_UNSUPPORTED || (kind >= 0 && kind <= 4), "asymgemm_b200: unknown kind ", kind);
   TORCH_CHECK(rc == AG_OK, "asymgemm_b200: ", ag_last_error(), " (code ", rc, ")");
 }
 

@@ -348,6 +348,8 @@ def test_fp8_hardware_ue8m0_scaling_contiguous(tile, b_on_host):
     d_sw = torch.full_like(d_hw, float("nan"))
     args = ((c["a"], c["sfa"]), (c["b"], c["sfb"]))
     ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d_hw, c["offsets"], c["experts"], c["list_size"], ue8m0_scales=True)
+    if tile == 7:   # the deep-ring configuration exists for the hardware-scaled kinds only: the exact path runs its default
+        ag.set_tile_config(0)
     ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d_sw, c["offsets"], c["experts"], c["list_size"], ue8m0_scales=False)
     torch.cuda.synchronize()
     _check("fp8", d_hw.float().cpu().numpy(), c["ref"], c["segments"])
@@ -355,6 +357,28 @@ def test_fp8_hardware_ue8m0_scaling_contiguous(tile, b_on_host):
     a, b = d_hw.float().cpu().numpy()[mask], d_sw.float().cpu().numpy()[mask]
     assert oracle.max_rel(a, b) <= 2 ** -7          # at most one bf16 ulp apart anywhere
     assert (a != b).mean() < 0.05
+
+
+def test_c_abi_error_surfaces_as_runtime_error_through_the_operator():
+    """A descriptor the library refuses (a tile configuration that does not exist for the operand kind) comes back as the
+    RuntimeError the reference API raises, with the library's message, and leaves the context usable."""
+    c = H.make_contiguous_case("fp8", [130, 64], 128, 512, seed=63)
+    d = torch.zeros((c["m_total"], 128), dtype=torch.bfloat16, device="cuda")
+    args = ((c["a"], c["sfa"]), (c["b"], c["sfb"]))
+    ag.set_tile_config(7)
+    try:
+        with pytest.raises(RuntimeError, match="tile_config 7 does not exist"):
+            ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d, c["offsets"], c["experts"], c["list_size"])
+        ag.set_tile_config(5)
+        with pytest.raises(RuntimeError, match="tile_config 5 does not exist"):
+            ag.m_grouped_bf16_asym_gemm_nt_contiguous(c["a"].view(torch.uint8)[:, :256].contiguous().view(torch.bfloat16),
+                                                      c["b"].view(torch.uint8)[:, :, :256].contiguous().pin_memory().view(torch.bfloat16),
+                                                      d, c["offsets"], c["experts"], c["list_size"])
+    finally:
+        ag.set_tile_config(0)
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d, c["offsets"], c["experts"], c["list_size"])
+    torch.cuda.synchronize()
+    _check("fp8", d.float().cpu().numpy(), c["ref"], c["segments"])
 
 
 def test_fp8_hardware_ue8m0_scaling_masked_and_mode_switch():
