@@ -5,10 +5,11 @@ links it runs on -- and on multi-GPU hosts the links are not independent: GPUs b
 ceiling (on one 8-GPU machine four GPUs shared ~116 GB/s while each reached 55 GB/s alone). When a job uses fewer ranks
 than the machine has GPUs, the set of GPUs matters more than anything the kernel does.
 
-`probe(devices, ...)` measures the given GPUs streaming at the same time (one host thread per GPU, all behind one
-barrier, copy engine, mean over the run). `choose_devices(n, ...)` measures all visible GPUs together, builds a few
-candidate sets of n GPUs (the first n, the n fastest, one spread over the groups that the rates fall into) and keeps
-the candidate whose own concurrent measurement has the highest sum.
+`LinkProbes(devices).run(...)` measures the given GPUs streaming at the same time (one host thread per GPU, all behind one
+barrier, copy engine, mean over the run). `choose_devices(n, ...)` first checks whether the default GPUs 0..n-1 slow each
+other down; only if they do, it measures all visible GPUs together, builds a few candidate sets of n GPUs (the first n,
+the n fastest, one spread over the groups that the rates fall into, one strided over the device order) and keeps the
+candidate whose own concurrent measurement has the highest sum.
 
 The module only needs ctypes and the C library (ag_link_probe_* in include/asymgemm_b200.h); run as a script
 (`python asymgemm_b200/linkprobe.py --choose N`) it prints one JSON object and does not import torch, which is how a
@@ -133,11 +134,29 @@ def candidate_sets(rates: Sequence[float], n: int) -> List[List[int]]:
     return uniq
 
 
-def choose_devices(n: int, visible: int, seconds: float = 0.3, nbytes: int = 256 << 20, margin: float = 0.05) -> dict:
-    """Which `n` of the `visible` GPUs to run on. Returns {"devices": [...], "all_at_once_gbs": [...], "candidates": [...]}.
-    The first n GPUs stay the choice unless another candidate measured more than `margin` above them."""
+def choose_devices(n: int, visible: int, seconds: float = 0.2, nbytes: int = 128 << 20, margin: float = 0.05,
+                   contention: float = 0.9) -> dict:
+    """Which `n` of the `visible` GPUs to run on. Returns {"devices": [...], "why": ..., and what was measured}.
+
+    Two stages, so that GPUs the job will not use are touched only when it pays. First the default set (GPUs 0..n-1)
+    alone: each link by itself, then all n at once. If together they keep at least `contention` of the sum of their
+    stand-alone rates, they do not get in each other's way and stay the choice; no other GPU is touched. Otherwise all
+    visible GPUs are measured at once, candidate sets are built from the groups their rates fall into, each candidate
+    is measured streaming at once, and the best one wins if it beats the default set by more than `margin`."""
     if n >= visible:
-        return {"devices": list(range(visible))[:n], "all_at_once_gbs": None, "candidates": [], "why": "every visible GPU is used"}
+        return {"devices": list(range(visible))[:n], "why": "every visible GPU is used"}
+    first = list(range(n))
+    probes = LinkProbes(first, nbytes)
+    try:
+        alone = [probes.run([d], seconds / 2)[0] for d in first]
+        together = probes.run(first, seconds)
+    finally:
+        probes.close()
+    rec = {"first_gpus_alone_gbs": [round(x, 2) for x in alone], "first_gpus_at_once_gbs": [round(x, 2) for x in together]}
+    if sum(together) >= contention * sum(alone):
+        rec.update({"devices": first, "why": f"the first {n} GPUs keep {sum(together) / sum(alone):.2f} of their stand-alone host-link rates "
+                                            "when they stream at once: no other GPU was measured"})
+        return rec
     probes = LinkProbes(range(visible), nbytes)
     try:
         all_rates = probes.run(None, seconds)
@@ -148,18 +167,20 @@ def choose_devices(n: int, visible: int, seconds: float = 0.3, nbytes: int = 256
     finally:
         probes.close()
     best = max(cands, key=lambda c: c["sum_gbs"])
-    first = cands[0]
-    pick = best if best["sum_gbs"] > (1.0 + margin) * first["sum_gbs"] else first
-    return {"devices": pick["devices"], "all_at_once_gbs": [round(x, 2) for x in all_rates], "candidates": cands,
-            "why": "measured: candidate sets of GPUs streaming at once over their host links (copy engine, mean over "
-                   f"{seconds} s each); the first {n} GPUs are kept unless another set is more than {int(margin * 100)} % faster"}
+    pick = best if best["sum_gbs"] > (1.0 + margin) * cands[0]["sum_gbs"] else cands[0]
+    rec.update({"devices": pick["devices"], "all_gpus_at_once_gbs": [round(x, 2) for x in all_rates], "candidates": cands,
+                "why": f"the first {n} GPUs keep only {sum(together) / sum(alone):.2f} of their stand-alone host-link rates when they stream "
+                       "at once (a shared host bridge), so candidate sets of GPUs were measured streaming at once (copy engine, mean "
+                       f"over {seconds} s each) before any rank started; the chosen set is the fastest one. The measurement used the copy "
+                       "engines of all visible GPUs for about a second; everything after it runs on the chosen GPUs only"})
+    return rec
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--choose", type=int, default=0, help="print the choice of this many GPUs")
     ap.add_argument("--visible", type=int, default=0, help="GPUs visible to the process (default: ask the driver via nvidia-smi -L)")
-    ap.add_argument("--seconds", type=float, default=0.3)
+    ap.add_argument("--seconds", type=float, default=0.2)
     args = ap.parse_args(argv)
     visible = args.visible
     if visible <= 0:

@@ -702,8 +702,7 @@ def main():
 
     if devmap is not None:
         info, path = devmap
-        config["device_map"] = {"rank_to_gpu": info["devices"], "all_gpus_at_once_gbs": info.get("all_at_once_gbs"),
-                                "candidates": info.get("candidates"), "why": info.get("why")}
+        config["device_map"] = {"rank_to_gpu": info["devices"], **{k: v for k, v in info.items() if k != "devices"}}
     moe = cfg["kind"] == "moe"
     on_dev = args.weights == "device"
     lib = _lib.load()
