@@ -143,7 +143,7 @@ int plan_launch(int kind, const ag_gemm_desc_t* g, bool host_b, LaunchPlan* out)
   if (int rc = device_sm_count(&sms)) return rc;
   const int cap = g->num_sms > 0 ? g->num_sms : g_num_sms.load();
   const int grid_cap = cap > 0 && cap < sms ? cap : sms;
-  pl.tile = g->tile_config > 0 ? g->tile_config - 1 : agb::default_tile(kind, host_b);
+  pl.tile = g->tile_config > 0 ? g->tile_config - 1 : agb::default_tile(kind, host_b, g->n);
   AG_REQUIRE(pl.tile >= 0 && pl.tile < agb::kNumTileConfigs, "tile_config must be 0 (auto) .. %d", agb::kNumTileConfigs);
   AG_REQUIRE(agb::tile_supported(kind, pl.tile), "tile_config %d does not exist for this operand kind (%s)", pl.tile + 1,
              agb::tile_support_text(kind));

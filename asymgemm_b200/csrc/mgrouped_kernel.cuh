@@ -33,6 +33,9 @@
 // shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
 #pragma once
 #include <cuda_bf16.h>
+
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace agb {
@@ -307,7 +310,6 @@ __host__ __device__ constexpr int drain_wgs_of() {
 }
 template <Kind KIND, int BN, bool REG_ACC>
 __host__ __device__ constexpr int num_threads_of() { return 128 + 128 * drain_wgs_of<KIND, BN, REG_ACC>(); }
-
 template <Kind KIND, int BN, int KA, int SA, int SB, bool REG_ACC = false>
 __global__ void __launch_bounds__(num_threads_of<KIND, BN, REG_ACC>(), 1)
 mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -377,6 +379,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int kb_count = p.kb_count;                       // 128-byte K atoms
   const int ks_count = (kb_count + KA - 1) / KA;         // B stages along K
 
+  if (warp < 4) {
   if (warp == 0) {
     // ===================================================================== B producer (+ scratch spill)
     if (lane == 0) {
@@ -576,7 +579,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         wait_bar(done_bar, 0, wc, ST_TIMEOUT_DRAIN, false);
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
     // ===================================================================== TMEM drain (epilogue)
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
     const int row_in_tile = q * 32 + lane;
@@ -600,12 +604,46 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const long long grow = static_cast<long long>(it.row0) + m0 * BM + row_in_tile;
           const bool valid = grow < row_end;
           float acc[COLS];
+#pragma unroll
+          for (int j = 0; j < COLS; ++j) acc[j] = 0.f;
           float* sfb_buf = sfb_smem + (warp - 4) * COLS;     // private to this warp
+          // scales of a K block are fetched one block ahead, so that their latency never sits in front of the arithmetic
+          const float* sfa_row = p.sfa + grow * p.sf_k;
+          const float* sfb_blk = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k;   // FP8 only
+          float sa_next = valid ? __ldg(sfa_row) : 0.f;
+          float sb_next = KIND == Kind::FP8 ? __ldg(sfb_blk) : 0.f;
+          // one 32-column piece of the raw product, scaled and added into the accumulators
+          auto accumulate = [&](auto& r, auto c0_tag, float sa, float sb_scalar, int kb) {
+            constexpr int W = sizeof(r) / sizeof(r[0]);
+            constexpr int c0 = decltype(c0_tag)::value;
+            if constexpr (KIND == Kind::INT8) {
+              if (p.raw_dump != nullptr && valid) {
+                int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + c0;
+#pragma unroll
+                for (int j = 0; j < W; ++j)
+                  if (n0 + col_base + c0 + j < p.n) dst[j] = static_cast<int>(r[j]);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < W; ++j) {
+              float prod, scale;
+              if constexpr (KIND == Kind::INT8) {
+                prod = static_cast<float>(static_cast<int>(r[j]));
+                scale = sa * sfb_buf[c0 + j];
+              } else {
+                prod = __uint_as_float(r[j]);
+                scale = sa * sb_scalar;
+              }
+              acc[c0 + j] = fmaf(prod, scale, acc[c0 + j]);
+            }
+          };
           for (int kb = 0; kb < kb_count && ok; ++kb, ++rt) {
-            float sb_scalar = 0.f;
-            if constexpr (KIND == Kind::FP8) {
-              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k + kb);
-            } else {
+            const float sa = sa_next, sb_scalar = sb_next;
+            if (kb + 1 < kb_count) {
+              sa_next = valid ? __ldg(sfa_row + kb + 1) : 0.f;
+              if constexpr (KIND == Kind::FP8) sb_next = __ldg(sfb_blk + kb + 1);
+            }
+            if constexpr (KIND == Kind::INT8) {
 #pragma unroll
               for (int j = 0; j < COLS / 32; ++j) {
                 const int col = n0 + col_base + j * 32 + lane;
@@ -614,45 +652,36 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               }
               __syncwarp();
             }
-            const float sa = valid ? __ldg(p.sfa + grow * p.sf_k + kb) : 0.f;
             const uint32_t rs = rt % RAW_SLOTS;
             ok = wait_bar(&tm_full[rs], (rt / RAW_SLOTS) & 1, wc, ST_TIMEOUT_TM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t raw_addr = lane_addr + (RAW_SLOT0 + rs) * BN + col_base;
-            // columns per TMEM load: 128 accumulator registers per thread leave room for 16 staging registers, not 32
-            constexpr int LW = COLS >= 128 ? 16 : 32;
-#pragma unroll
-            for (int cc = 0; cc < COLS / LW; ++cc) {
-              uint32_t r[LW];
-              tmem_ld_cols(raw_addr + cc * LW, r);
-              tmem_wait_ld();
-              if (cc == COLS / LW - 1) {  // this warp has read its part of the raw slot: hand it back before the arithmetic
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tm_empty[rs]);
+            auto release_slot = [&]() {   // this warp has read its part of the raw slot: hand it back before the arithmetic
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tm_empty[rs]);
+            };
+            {
+              // columns per TMEM load: 128 accumulator registers per thread leave room for 16 staging registers, not 32
+              constexpr int LW = COLS >= 128 ? 16 : 32;
+              auto piece = [&](auto cc_tag) {
+                constexpr int cc = decltype(cc_tag)::value;
+                uint32_t r[LW];
+                tmem_ld_cols(raw_addr + cc * LW, r);
+                tmem_wait_ld();
+                if (cc == COLS / LW - 1) release_slot();
+                accumulate(r, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, kb);
+              };
+              piece(std::integral_constant<int, 0>{});
+              if constexpr (COLS / LW > 1) piece(std::integral_constant<int, 1>{});
+              if constexpr (COLS / LW > 2) { piece(std::integral_constant<int, 2>{}); piece(std::integral_constant<int, 3>{}); }
+              if constexpr (COLS / LW > 4) {
+                piece(std::integral_constant<int, 4>{}); piece(std::integral_constant<int, 5>{});
+                piece(std::integral_constant<int, 6>{}); piece(std::integral_constant<int, 7>{});
               }
-              if constexpr (KIND == Kind::INT8) {
-                if (p.raw_dump != nullptr && valid) {
-                  int* dst = p.raw_dump + (static_cast<long long>(kb) * p.rows_total + grow) * p.n + n0 + col_base + cc * LW;
-#pragma unroll
-                  for (int j = 0; j < LW; ++j)
-                    if (n0 + col_base + cc * LW + j < p.n) dst[j] = static_cast<int>(r[j]);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < LW; ++j) {
-                float prod, scale;
-                if constexpr (KIND == Kind::INT8) {
-                  prod = static_cast<float>(static_cast<int>(r[j]));
-                  scale = sa * sfb_buf[cc * LW + j];
-                } else {
-                  prod = __uint_as_float(r[j]);
-                  scale = sa * sb_scalar;
-                }
-                acc[cc * LW + j] = fmaf(prod, scale, kb > 0 ? acc[cc * LW + j] : 0.f);
-              }
+              static_assert(COLS / LW <= 8, "pieces are written out up to eight");
             }
             if constexpr (KIND == Kind::INT8) __syncwarp();  // everyone is done with sfb_buf before the next block refills it
           }
@@ -745,22 +774,26 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             tc_fence_after_sync();
             const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
             const bool valid = grow < row_end;
-#pragma unroll 1
-            for (int cc = 0; cc < COLS / 32; ++cc) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(lane_addr + mt * BN + col_base + cc * 32, r);
-              tmem_wait_ld();
-              if constexpr (T::block_scaled) {
-                if (p.alpha != 1.f) {
+            // Read this warp's whole share of the accumulator into registers (at most 128 columns), hand the TMEM slot back,
+            // and only then convert and store: the MMA warp can start the next tile on this slot while the stores run.
+            uint32_t r[COLS / 32][32];
 #pragma unroll
-                  for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
-                }
-              }
-              if (valid) store_row32(p, grow, n0 + col_base + cc * 32, r);
-            }
+            for (int cc = 0; cc < COLS / 32; ++cc) tmem_ld_32x32b_x32(lane_addr + mt * BN + col_base + cc * 32, r[cc]);
+#pragma unroll
+            for (int cc = 0; cc < COLS / 32; ++cc) tmem_wait_ld_into(r[cc]);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tm_empty[mt]);
+#pragma unroll
+            for (int cc = 0; cc < COLS / 32; ++cc) {
+              if constexpr (T::block_scaled) {
+                if (p.alpha != 1.f) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) r[cc][j] = __float_as_uint(__uint_as_float(r[cc][j]) * p.alpha);
+                }
+              }
+              if (valid) store_row32(p, grow, n0 + col_base + cc * 32, r[cc]);
+            }
           }
           slot_phase ^= (1u << mc) - 1u;
         }

@@ -162,6 +162,16 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// tcgen05.wait::ld for loads into `r`, with the registers tied to the wait: the compiler sees every later read of r[i]
+// as depending on a statement that follows the wait, so it cannot schedule such a read ahead of it. Needed where
+// arithmetic on one buffer is interleaved with loads in flight into another.
+template <int W>
+__device__ __forceinline__ void tmem_wait_ld_into(uint32_t (&r)[W]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < W; ++i) asm volatile("" : "+r"(r[i])::"memory");
+}
+
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------- tcgen05 MMA (single-thread issue)
