@@ -61,6 +61,17 @@ class GemmDesc(Structure):
     ]
 
 
+EP_MAX_RANKS = 16
+EP_BAD_EXPERT, EP_OVERFLOW = 64, 65
+
+
+class EpPeers(Structure):
+    """Mirror of ``ag_ep_peers_t``: every rank's four exchange buffers as this process can address them."""
+
+    _fields_ = [("a", c_void_p * EP_MAX_RANKS), ("sfa", c_void_p * EP_MAX_RANKS), ("meta", c_void_p * EP_MAX_RANKS),
+                ("ret", c_void_p * EP_MAX_RANKS)]
+
+
 EXPORTS = [
     "ag_m_grouped_bf16_gemm_nt",
     "ag_m_grouped_fp8_gemm_nt",
@@ -90,6 +101,15 @@ EXPORTS = [
     "ag_selftest_wait_limit",
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
+    "ag_silu_mul_quant_fp8_upto",
+    "ag_peer_alloc",
+    "ag_peer_open",
+    "ag_peer_close",
+    "ag_peer_free",
+    "ag_ep_histogram",
+    "ag_ep_plan",
+    "ag_ep_dispatch",
+    "ag_ep_return",
     "ag_move_rows",
     "ag_combine_topk",
     "ag_quant_rows_int8",
@@ -145,6 +165,26 @@ def load() -> ctypes.CDLL:
     lib.ag_quant_rows_fp8.restype = c_int32
     lib.ag_silu_mul_quant_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     lib.ag_silu_mul_quant_fp8.restype = c_int32
+    lib.ag_silu_mul_quant_fp8_upto.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p]
+    lib.ag_silu_mul_quant_fp8_upto.restype = c_int32
+    lib.ag_peer_alloc.argtypes = [c_uint64, POINTER(c_void_p), c_void_p]
+    lib.ag_peer_alloc.restype = c_int32
+    lib.ag_peer_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    lib.ag_peer_open.restype = c_int32
+    lib.ag_peer_close.argtypes = [c_void_p]
+    lib.ag_peer_close.restype = c_int32
+    lib.ag_peer_free.argtypes = [c_void_p]
+    lib.ag_peer_free.restype = c_int32
+    lib.ag_ep_histogram.argtypes = [c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p]
+    lib.ag_ep_histogram.restype = c_int32
+    lib.ag_ep_plan.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                               c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.ag_ep_plan.restype = c_int32
+    lib.ag_ep_dispatch.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_void_p, c_int32, c_int32, c_void_p,
+                                   c_void_p, c_int64, POINTER(EpPeers), c_void_p]
+    lib.ag_ep_dispatch.restype = c_int32
+    lib.ag_ep_return.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, POINTER(EpPeers), c_void_p]
+    lib.ag_ep_return.restype = c_int32
     lib.ag_move_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]
     lib.ag_move_rows.restype = c_int32
     lib.ag_combine_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p]

@@ -21,7 +21,7 @@ TORCH_OPS_PATH = LIB_DIR / "libasymgemm_b200_torch.so"
 TORCH_OPS_SRC = CSRC / "torch_ops.cpp"
 OBJ_DIR = CSRC / "build"
 
-SOURCES = ["capi.cu", "inst_bf16.cu", "inst_fp8.cu", "inst_int8.cu", "inst_fp4.cu", "inst_fp8_ue8m0.cu", "sf_layout.cu", "no_alloc.cu", "selftest.cu", "moe_glue.cu", "hostlink.cu"]
+SOURCES = ["capi.cu", "inst_bf16.cu", "inst_fp8.cu", "inst_int8.cu", "inst_fp4.cu", "inst_fp8_ue8m0.cu", "sf_layout.cu", "no_alloc.cu", "selftest.cu", "moe_glue.cu", "hostlink.cu", "ep_peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -383,6 +383,8 @@ const char* status_text(int code) {
     case agb::ST_TIMEOUT_DRAIN: return "timed out draining copies in flight";
     case agb::ST_BAD_EXPERT: return "an expert id in `experts` is >= num_groups";
     case agb::ST_TIMEOUT_PROBE: return "wait-limit self test expired (expected)";
+    case AG_EP_BAD_EXPERT: return "the routing names an expert id outside [0, num_experts)";
+    case AG_EP_OVERFLOW: return "a rank's experts received more rows than its exchange buffers hold";
     default: return "unknown status";
   }
 }

@@ -44,12 +44,13 @@ __device__ __forceinline__ float ceil_pow2(float x) {
 template <int MODE>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                          float* __restrict__ sf, long long rows, int cols, int blocks_per_row,
-                                                         int pow2_scales) {
+                                                         int pow2_scales, const int* __restrict__ rows_limit) {
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = rows * blocks_per_row;
   if (warp_global >= total) return;
   const long long row = warp_global / blocks_per_row;
+  if (rows_limit != nullptr && row >= *rows_limit) return;   // rows past the count the device holds are not touched
   const int blk = static_cast<int>(warp_global - row * blocks_per_row);
   const int c0 = blk * 128 + lane * 4;
   float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -103,11 +104,12 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
 template <int MODE>
 __global__ void __launch_bounds__(256) quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                               float* __restrict__ sf, long long rows, int cols, int blocks_per_row,
-                                                              int pairs_per_row, int pow2_scales) {
+                                                              int pairs_per_row, int pow2_scales, const int* __restrict__ rows_limit) {
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= rows * pairs_per_row) return;
   const long long row = warp_global / pairs_per_row;
+  if (rows_limit != nullptr && row >= *rows_limit) return;
   const int pair = static_cast<int>(warp_global - row * pairs_per_row);
   const int blk = pair * 2 + (lane >> 4);
   const int c0 = blk * 128 + (lane & 15) * 8;
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(256) combine_topk_kernel(const __nv_bfloat16* 
   for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < top_k; ++j) {
-      const long long r = pos[t * top_k + j];
+      const long long r = pos != nullptr ? pos[t * top_k + j] : t * top_k + j;
       const float wt = w[t * top_k + j];
       const uint4 v = *reinterpret_cast<const uint4*>(rows + r * cols + c);
       const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -267,16 +269,17 @@ int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int6
     const int ppr = (bpr + 1) / 2;
     const long long wide = rows * ppr;
     agb::quant_rows_wide_kernel<0><<<static_cast<unsigned>((wide + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, ppr, pow2_scales);
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, ppr, pow2_scales, nullptr);
     return launch_check();
   }
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<0><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales);
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales, nullptr);
   return launch_check();
 }
 
-int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales, void* stream) {
+int ag_silu_mul_quant_fp8_upto(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales,
+                               const int32_t* rows_used, void* stream) {
   if (!gate_up_bf16 || !q || !sf || rows < 0 || inter <= 0 || inter % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (inter must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   if (!aligned_to(gate_up_bf16, 8) || !aligned_to(q, 4) || !aligned_to(sf, 4))
@@ -286,13 +289,17 @@ int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t 
     const int ppr = (bpr + 1) / 2;
     const long long wide = rows * ppr;
     agb::quant_rows_wide_kernel<1><<<static_cast<unsigned>((wide + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, ppr, pow2_scales);
+        static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, ppr, pow2_scales, rows_used);
     return launch_check();
   }
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<1><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, pow2_scales);
+      static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(inter), bpr, pow2_scales, rows_used);
   return launch_check();
+}
+
+int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales, void* stream) {
+  return ag_silu_mul_quant_fp8_upto(gate_up_bf16, q, sf, rows, inter, pow2_scales, nullptr, stream);
 }
 
 int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes, void* stream) {
@@ -307,7 +314,7 @@ int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int6
 
 int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                     int64_t cols, void* stream) {
-  if (!rows_bf16 || !pos || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 8 != 0 || !aligned16(rows_bf16) ||
+  if (!rows_bf16 || !weights || !y_bf16 || tokens < 0 || top_k <= 0 || cols <= 0 || cols % 8 != 0 || !aligned16(rows_bf16) ||
       !aligned16(y_bf16) || !aligned_to(pos, 8) || !aligned_to(weights, 4))
     return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 8; rows and y 16-byte aligned)");
   if (tokens == 0) return AG_OK;

@@ -412,14 +412,23 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
                  expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False, pipeline_groups: int = 1,
-                 comm_sms: int = 24):
+                 comm_sms: int = 24, exchange: str = "nccl", max_tokens: Optional[int] = None, top_k: Optional[int] = None):
         """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
         (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly.
         Whether the kernel reads the pinned weights itself or the copy engine stages them is the operators' setting
         (`asymgemm_b200.set_weight_path`). `pipeline_groups` > 1 (several ranks only): the layer runs in that many
         rounds over groups of each rank's experts so that the token exchanges overlap the GEMMs
         (`EPDispatcher.pipelined`); the persistent GEMMs then leave `comm_sms` SMs free for the exchange kernels --
-        they are bound by the host link, not by SMs."""
+        they are bound by the host link, not by SMs.
+        `exchange`: "nccl" (default) sorts the (token, slot) pairs, gathers rows into send buffers and exchanges them with
+        all-to-all(v), reading the split sizes back on the host; "peer" routes, lays out and exchanges with this library's
+        own kernels, which store rows straight into the owner rank's buffers over NVLink (`ep_peer.PeerExchange`; needs
+        `max_tokens`, the most tokens one rank brings to a step, and `top_k`; the ranks must be processes of one node).
+        Both give the same output bit for bit."""
+        if exchange not in ("nccl", "peer"):
+            raise RuntimeError("exchange must be 'nccl' or 'peer'")
+        self.exchange = exchange
+        self.peer = None
         self.pipeline_groups = max(1, int(pipeline_groups))
         self.comm_sms = max(0, int(comm_sms))
         self.dispatcher = EPDispatcher(num_experts, group, expert_ranges)
@@ -439,6 +448,13 @@ class ExpertParallelMoE:
         epr = self.dispatcher.experts_per_rank
         if tuple(w13[0].shape) != (epr, 2 * inter, hidden) or tuple(w2[0].shape) != (epr, hidden, inter):
             raise RuntimeError("weight shapes do not match (experts_per_rank, 2*inter, hidden) / (experts_per_rank, hidden, inter)")
+        if exchange == "peer":
+            from .ep_peer import PeerExchange
+            if not max_tokens or not top_k:
+                raise RuntimeError("exchange='peer' needs max_tokens and top_k")
+            dev = w13[1].device if w13[1].is_cuda else torch.device("cuda", torch.cuda.current_device())
+            self.peer = PeerExchange(num_experts, hidden, (hidden + 127) // 128, hidden * 2, int(top_k), int(max_tokens),
+                                     self.dispatcher.expert_ranges, dev, group)
 
     def _weights_of(self, first: int, count: int):
         """(w13, w2) of the local experts [first, first + count): views made once, because the operators cache prepared
@@ -458,9 +474,11 @@ class ExpertParallelMoE:
             self.phase_events.append((name, ev))
 
     def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState, first: int = 0,
-                        count: Optional[int] = None) -> torch.Tensor:
+                        count: Optional[int] = None, rows_used: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]. `first` / `count`: the local
-        experts `state` describes (expert id 0 of its segment table = local expert `first`); default: all of them."""
+        experts `state` describes (expert id 0 of its segment table = local expert `first`); default: all of them.
+        `rows_used`: device int32 holding how many rows of the layout are in use when only the device knows (the
+        activation kernel then leaves the rest of the buffer alone)."""
         from . import api
         w13, w2 = self._weights_of(first, self.dispatcher.experts_per_rank if count is None else count)
         m = state.padded_rows
@@ -472,7 +490,7 @@ class ExpertParallelMoE:
         hw = self.ue8m0_scales
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
         self._mark("gemm_gate_up")
-        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw)
+        a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw, rows_used=rows_used)
         self._mark("silu_mul_requant")
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
         self._mark("gemm_down")
@@ -480,11 +498,32 @@ class ExpertParallelMoE:
             self.intermediates = dict(a_q=a_q, sfa=sfa, d1=d1, a2=a2, s2=s2, d2=d2, state=state, first=first)
         return d2
 
+    def _forward_peer(self, x_q: torch.Tensor, sfx: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """The layer with the peer-memory exchange: rows land in the owner's padded layout directly, the GEMMs run over the
+        whole buffer with the device-built segment table, results go home the same way. No host synchronisation."""
+        from . import api
+        px = self.peer
+        tokens, top_k = topk_ids.shape
+        px.route(topk_ids, api._status_word(x_q.device))
+        px.dispatch(x_q.view(torch.uint8), sfx)
+        self._mark("plan_dispatch")
+        a_q = px.a.view(torch.float8_e4m3fn).view(px.cap_rows, self.hidden)
+        state = DispatchState(None, [], [], None, None, px.cap_rows, px.offsets, px.experts, tokens, top_k)
+        self._mark("layout")
+        out = self.experts_forward(a_q, px.sfa, state, rows_used=px.rows_used[:1])
+        px.send_back(out)
+        self._mark("return")
+        y = moe_ops.combine_topk(px.ret.view(torch.bfloat16).view(px.pairs_cap, self.hidden), None, topk_weights, tokens, top_k)
+        self._mark("combine")
+        return y
+
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x bf16 [T, hidden] (this rank's tokens), topk_ids int64 [T, k], topk_weights [T, k] -> bf16 [T, hidden]."""
         self._mark("start")
         x_q, sfx = moe_ops.quant_rows_fp8(x.contiguous(), pow2_scales=self.ue8m0_scales)
         self._mark("quantise")
+        if self.peer is not None:
+            return self._forward_peer(x_q, sfx, topk_ids, topk_weights)
         if self.pipeline_groups > 1 and self.dispatcher.world > 1:
             from . import api
 

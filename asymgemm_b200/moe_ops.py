@@ -30,8 +30,10 @@ def quant_rows_fp8(x: torch.Tensor, pow2_scales: bool = False) -> Tuple[torch.Te
     return q, sf
 
 
-def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int, pow2_scales: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [rows, 2*inter] -> bf16(silu(gate) * up) quantised to (e4m3 [rows, inter], fp32 [rows, ceil(inter/128)])."""
+def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int, pow2_scales: bool = False,
+                       rows_used: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, 2*inter] -> bf16(silu(gate) * up) quantised to (e4m3 [rows, inter], fp32 [rows, ceil(inter/128)]).
+    `rows_used`: device int32 tensor; rows from that count on are neither read nor written."""
     if not (gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.dim() == 2 and gate_up.is_contiguous()
             and gate_up.shape[1] == 2 * inter):
         raise RuntimeError("silu_mul_quant_fp8 wants a contiguous bf16 CUDA tensor [rows, 2*inter]")
@@ -39,7 +41,8 @@ def silu_mul_quant_fp8(gate_up: torch.Tensor, inter: int, pow2_scales: bool = Fa
     q = torch.empty((rows, inter), dtype=torch.float8_e4m3fn, device=gate_up.device)
     sf = torch.empty((rows, (inter + 127) // 128), dtype=torch.float32, device=gate_up.device)
     with torch.cuda.device(gate_up.device):
-        _lib.check(_lib.load().ag_silu_mul_quant_fp8(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, inter, int(pow2_scales), _stream(gate_up)))
+        _lib.check(_lib.load().ag_silu_mul_quant_fp8_upto(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, inter, int(pow2_scales),
+                                                          rows_used.data_ptr() if rows_used is not None else None, _stream(gate_up)))
     return q, sf
 
 
@@ -114,14 +117,14 @@ def move_rows_into(out: torch.Tensor, src: torch.Tensor, dst_rows: torch.Tensor)
 
 
 def combine_topk(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, tokens: int, top_k: int) -> torch.Tensor:
-    """y[t] = sum_j weights[t, j] * rows[pos[t*top_k + j]] (fp32 accumulation), as rows.dtype."""
+    """y[t] = sum_j weights[t, j] * rows[pos[t*top_k + j]] (fp32 accumulation), as rows.dtype; pos None = t*top_k + j."""
     cols = rows.shape[1]
     if rows.is_cuda and rows.dtype == torch.bfloat16 and cols % 8 == 0 and rows.is_contiguous():
         y = torch.empty((tokens, cols), dtype=torch.bfloat16, device=rows.device)
         w = weights.to(torch.float32).contiguous()
         with torch.cuda.device(rows.device):
-            _lib.check(_lib.load().ag_combine_topk(rows.data_ptr(), pos.data_ptr(), w.data_ptr(), y.data_ptr(), tokens, top_k, cols,
-                                                   _stream(rows)))
+            _lib.check(_lib.load().ag_combine_topk(rows.data_ptr(), pos.data_ptr() if pos is not None else None, w.data_ptr(), y.data_ptr(),
+                                                   tokens, top_k, cols, _stream(rows)))
         return y
     if rows.is_cuda and rows.dtype == torch.float32 and cols % 4 == 0 and rows.is_contiguous():
         y = torch.empty((tokens, cols), dtype=torch.bfloat16, device=rows.device)
@@ -130,5 +133,5 @@ def combine_topk(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, t
             _lib.check(_lib.load().ag_combine_topk_f32(rows.data_ptr(), pos.data_ptr(), w.data_ptr(), y.data_ptr(), tokens, top_k, cols,
                                                        _stream(rows)))
         return y
-    picked = rows.index_select(0, pos).view(tokens, top_k, cols).float()
+    picked = (rows.index_select(0, pos) if pos is not None else rows[: tokens * top_k]).view(tokens, top_k, cols).float()
     return (picked * weights.unsqueeze(-1).float()).sum(dim=1).to(rows.dtype)

@@ -554,17 +554,42 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
     rank's tokens against the dense fp32 restatement (outside the timed region)."""
     import asymgemm_b200 as ag
     import torch.distributed as dist
+    from asymgemm_b200 import ep
     from asymgemm_b200.testing import calc_diff, max_rel_err
     from asymgemm_b200.testing.moe_reference import dense_moe_reference, expert_weights
     ue = args.fp8_scales == "ue8m0"
     w = build_moe(cfg, rank, world, device, None, expert_ranges=ranges, ue8m0=ue, pipeline_groups=args.pipeline_groups)
     layer = w["layer"]
-    step = lambda: layer.forward(w["x"], w["ids"], w["w"])
-    for _ in range(2):
-        y = step()
-    ag.check_status()
-    ms = timed(step, steps, barrier)
-    ag.check_status()
+    nccl_ms = peer_ms = None
+    chosen = "nccl"
+    if args.exchange in ("nccl", "both"):
+        step = lambda: layer.forward(w["x"], w["ids"], w["w"])
+        for _ in range(2):
+            y = step()
+        ag.check_status()
+        nccl_ms = timed(step, steps, barrier)
+        ag.check_status()
+    if args.exchange in ("peer", "both") and args.pipeline_groups <= 1:
+        peer_layer = ep.ExpertParallelMoE(cfg["experts"], cfg["hidden"], cfg["inter"], layer.w13, layer.w2, None, ranges, ue8m0_scales=ue,
+                                          exchange="peer", max_tokens=w["x"].shape[0], top_k=cfg["top_k"])
+        pstep = lambda: peer_layer.forward(w["x"], w["ids"], w["w"])
+        for _ in range(2):
+            y_peer = pstep()
+        ag.check_status()
+        peer_ms = timed(pstep, steps, barrier)
+        ag.check_status()
+        differs = 0.0 if nccl_ms is None or torch.equal(y_peer, y) else 1.0
+        # the faster exchange (by the slowest rank's time) is the one the record describes
+        both = torch.tensor([nccl_ms if nccl_ms is not None else 1e30, peer_ms, differs], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(both, op=dist.ReduceOp.MAX)
+        if both[1].item() <= both[0].item():
+            chosen, step, y = "peer", pstep, y_peer
+        nccl_all, peer_all = (both[0].item() if nccl_ms is not None else None), both[1].item()
+        same = (both[2].item() == 0.0) if nccl_ms is not None else None
+    ms = peer_ms if chosen == "peer" else nccl_ms
+    if chosen == "peer":
+        layer = peer_layer
     # per-phase breakdown: two more steps with events at the phase boundaries (unpipelined path only)
     phases = None
     if not (args.pipeline_groups > 1 and world > 1):
@@ -615,9 +640,17 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
                           "worst rank; tolerance of the FP8 path: max-rel <= 2e-2",
         "experts_per_rank": [hi - lo for lo, hi in ranges] if ranges is not None else [cfg["experts"] // world] * world,
         "gemm_launches_per_step": 2 * (args.pipeline_groups if world > 1 else 1),
+        "exchange": {"nccl": "sort + gather + NCCL all-to-all(v), split sizes read back on the host",
+                     "peer": "this library's kernels: histogram, plan, rows stored into the owner's layout over NVLink peer memory, results "
+                             "stored back the same way; no host synchronisation"}[chosen],
     }
+    if peer_ms is not None:
+        rec["exchange_ms_per_step"] = {"nccl": round(nccl_all, 3) if nccl_all is not None else None, "peer": round(peer_all, 3),
+                                       "outputs_bit_equal": same}
     if args.pipeline_groups > 1 and world > 1:
         rec["pipeline_groups"] = args.pipeline_groups
+    if peer_ms is not None:
+        peer_layer.peer.close()
     del w, layer, y
     torch.cuda.empty_cache()
     return rec
@@ -657,6 +690,9 @@ def main():
     ap.add_argument("--device-map", default="auto", choices=["auto", "identity"],
                     help="auto (default): with fewer ranks than visible GPUs, choose the GPUs by measuring their host links together; "
                          "identity: rank r on GPU r")
+    ap.add_argument("--exchange", default="both", choices=["nccl", "peer", "both"],
+                    help="token exchange of the MoE layer: nccl (sort + all-to-all(v)), peer (this library's kernels storing rows into the "
+                         "owner's buffers over NVLink), both (default: `ep_layer` times the two and reports the faster as its headline)")
     ap.add_argument("--no-ep-layer", action="store_true", help="skip the `ep_layer` record (the expert-parallel MoE layer at this N)")
     ap.add_argument("--ep-tokens", type=int, default=0, help="token count of the `ep_layer` record (default: the 65536 of the named config)")
     ap.add_argument("--parity-tokens", type=int, default=256, help="tokens per rank checked against the dense restatement in `ep_layer`")

@@ -227,7 +227,14 @@ int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t 
 int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes,
                  void* stream);
 
-/* y[t] = sum_j weights[t, j] * rows[pos[t * top_k + j]] accumulated in fp32, rounded once to bf16. cols % 8 == 0. */
+/* As ag_silu_mul_quant_fp8 over a buffer of `rows` rows of which only the first *rows_used (a device int32, read by the
+ * kernel) hold data: rows past that count are neither read nor written. For layouts whose size only the device knows
+ * (the peer-memory exchange below). rows_used == NULL: all rows. */
+int ag_silu_mul_quant_fp8_upto(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales,
+                               const int32_t* rows_used, void* stream);
+
+/* y[t] = sum_j weights[t, j] * rows[pos[t * top_k + j]] accumulated in fp32, rounded once to bf16. cols % 8 == 0.
+ * pos == NULL reads rows[t * top_k + j]. */
 int ag_combine_topk(const void* rows_bf16, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                     int64_t cols, void* stream);
 
@@ -240,6 +247,54 @@ int ag_silu_mul_quant_int8(const void* gate_up_f32, void* q, float* sf, int64_t 
 /* ag_combine_topk for fp32 rows (cols % 4 == 0); the result is rounded once to bf16. */
 int ag_combine_topk_f32(const void* rows_f32, const int64_t* pos, const float* weights, void* y_bf16, int64_t tokens, int32_t top_k,
                         int64_t cols, void* stream);
+
+/* ---- expert-parallel token exchange over peer memory (NVLink / NVSwitch), for the ranks of one node ----
+ * The routing, the layout and both exchanges of an MoE layer as kernels that write rows straight into the owner rank's
+ * buffers with ordinary stores through peer-mapped pointers; no kernel loads from a peer, none waits for another GPU, and
+ * no split size ever reaches the host. The caller issues a small collective on the same stream between the steps
+ * (all-gather of the histograms; one after dispatch and one after return, so that every rank's stores have landed before
+ * they are read). Every rank allocates the same four buffers with ag_peer_alloc, exchanges the 64-byte handles, and opens
+ * the others' with ag_peer_open. The reference's callers do these steps with torch sort / bincount / index kernels and NCCL
+ * all_gather + reduce_scatter (asym_gemm/unified_moe/runtime.py:1422-1476, asym_gemm/training/ep_vanilla.py:173-282). */
+#define AG_EP_MAX_RANKS 16
+#define AG_EP_BAD_EXPERT 64 /* status word: an expert id outside [0, num_experts) in the routing */
+#define AG_EP_OVERFLOW 65   /* status word: a rank's experts received more rows than its buffers hold */
+typedef struct ag_ep_peers {
+  void* a[AG_EP_MAX_RANKS];    /* per rank: [cap_rows, row_bytes] rows in that rank's padded contiguous layout */
+  void* sfa[AG_EP_MAX_RANKS];  /* per rank: [cap_rows, sf_per_row] fp32 scales of those rows */
+  void* meta[AG_EP_MAX_RANKS]; /* per rank: [cap_rows] int64 return address of each row: (source rank << 32) | pair, -1 = none */
+  void* ret[AG_EP_MAX_RANKS];  /* per rank: [tokens * top_k, ret_row_bytes] results by (token, slot) pair of that rank */
+} ag_ep_peers_t;
+
+/* Device memory that other processes of the node can map: cudaMalloc + an IPC handle (64 bytes) to send to them;
+ * ag_peer_open maps a handle received from another rank (enabling peer access on first use), ag_peer_close unmaps it,
+ * ag_peer_free releases one's own. Called once when a layer is built, never per step. */
+int ag_peer_alloc(uint64_t bytes, void** ptr, unsigned char* handle64);
+int ag_peer_open(const unsigned char* handle64, void** ptr);
+int ag_peer_close(void* ptr);
+int ag_peer_free(void* ptr);
+
+/* counts[e] = (token, slot) pairs of ids [pairs] (int64) routed to expert e; counts is zeroed first. */
+int ag_ep_histogram(const int64_t* ids, int64_t pairs, int32_t num_experts, int32_t* counts, int32_t* status, void* stream);
+
+/* From every rank's histogram counts_all [world, num_experts] and the ownership table range_lo [world + 1] (rank r owns
+ * experts [range_lo[r], range_lo[r + 1])): where this rank's rows for each expert start on the owner (send_base [E]), zeroed
+ * slot counters (cursors [E]), this rank's own segment table for the grouped GEMM (offsets [2 * epr_cap] = (start, start +
+ * valid rows) per local expert, each expert's start a multiple of 128; experts [epr_cap + 1] ending in -1), rows_used [2] =
+ * {rows of the padded layout in use, valid rows}, and -1 in my_meta for this rank's padding rows. One small block. */
+int ag_ep_plan(const int32_t* counts_all, const int32_t* range_lo, int32_t world, int32_t rank, int32_t num_experts, int64_t cap_rows,
+               int32_t* send_base, int32_t* cursors, int32_t* offsets, int32_t* experts, int32_t epr_cap, int32_t* rows_used, int64_t* my_meta,
+               int32_t* status, void* stream);
+
+/* Every (token, slot) pair of this rank: the token's row x_q [tokens, row_bytes] and scales sfx [tokens, sf_per_row] are
+ * stored into the next free row of the pair's expert on the owner rank, with the pair's return address beside it. */
+int ag_ep_dispatch(const void* x_q, const float* sfx, const int64_t* ids, int64_t tokens, int32_t top_k, int64_t row_bytes, int32_t sf_per_row,
+                   const int32_t* range_lo, int32_t world, int32_t rank, const int32_t* send_base, int32_t* cursors, int64_t cap_rows,
+                   const ag_ep_peers_t* peers, void* stream);
+
+/* Every valid row of this rank's result `out` [cap_rows, row_bytes] is stored into its pair's slot of the source rank's `ret`. */
+int ag_ep_return(const void* out, const int64_t* my_meta, const int32_t* rows_used, int64_t cap_rows, int64_t row_bytes, int32_t world,
+                 const ag_ep_peers_t* peers, void* stream);
 
 /* Failure-detection self test: launches a one-CTA kernel whose only barrier wait can never be satisfied. After
  * `timeout_ms` (1..2000) the wait gives up, the kernel stores (0 << 8) | 9 ("wait-limit self test expired") in *status

@@ -70,6 +70,17 @@ def _case(rank, world, device, weight_path="stream"):
             piped = ep.ExpertParallelMoE(num_experts, hidden, inter, layer.w13, layer.w2, pipeline_groups=groups)
             assert torch.equal(piped.forward(x, ids, wts), y), f"pipeline_groups={groups}"
             assert torch.equal(piped.forward(x, ids, wts), y), f"pipeline_groups={groups}, second call"
+    # routing, layout and both exchanges by this library's own kernels over peer memory: the same output bit for bit, also
+    # on a second call, which finds the previous call's rows, return addresses and results in the buffers
+    peer = ep.ExpertParallelMoE(num_experts, hidden, inter, layer.w13, layer.w2, exchange="peer",
+                                max_tokens=300 + 17 * (world - 1), top_k=top_k)
+    try:
+        assert torch.equal(peer.forward(x, ids, wts), y), "peer exchange"
+        assert torch.equal(peer.forward(x[:250].contiguous(), ids[:250].contiguous(), wts[:250].contiguous()), layer.forward(
+            x[:250].contiguous(), ids[:250].contiguous(), wts[:250].contiguous())), "peer exchange, fewer tokens"
+        assert torch.equal(peer.forward(x, ids, wts), y), "peer exchange, third call"
+    finally:
+        peer.peer.close()
     if weight_path == "staged":
         # the copy engine moves the same bytes the kernel would read: same result, also when the staging buffers are reused
         import asymgemm_b200 as ag
