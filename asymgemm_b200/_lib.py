@@ -22,6 +22,7 @@ LAYOUT_CONTIGUOUS = 0
 LAYOUT_MASKED = 1
 D_BF16 = 0
 D_FP32 = 1
+EPILOGUE_NONE, EPILOGUE_SILU_MUL = 0, 1
 
 KIND_BF16, KIND_FP8, KIND_INT8, KIND_NVFP4, KIND_FP8_UE8M0 = 0, 1, 2, 3, 4
 
@@ -58,6 +59,7 @@ class GemmDesc(Structure):
         ("stage", c_void_p),
         ("stage_bytes", c_uint64),
         ("stage_chunk_bytes", c_uint64),
+        ("epilogue", c_int32),
     ]
 
 
@@ -102,6 +104,7 @@ EXPORTS = [
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
     "ag_silu_mul_quant_fp8_upto",
+    "ag_quant_rows_fp8_upto",
     "ag_peer_alloc",
     "ag_peer_open",
     "ag_peer_close",
@@ -165,6 +168,8 @@ def load() -> ctypes.CDLL:
     lib.ag_quant_rows_fp8.restype = c_int32
     lib.ag_silu_mul_quant_fp8.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     lib.ag_silu_mul_quant_fp8.restype = c_int32
+    lib.ag_quant_rows_fp8_upto.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p]
+    lib.ag_quant_rows_fp8_upto.restype = c_int32
     lib.ag_silu_mul_quant_fp8_upto.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p]
     lib.ag_silu_mul_quant_fp8_upto.restype = c_int32
     lib.ag_peer_alloc.argtypes = [c_uint64, POINTER(c_void_p), c_void_p]

@@ -253,19 +253,20 @@ def _check_b_residency(b: torch.Tensor) -> None:
     _require(b.is_cuda or b.is_pinned(), "b must be a CUDA tensor or pinned host memory (b.is_cuda() or b.is_pinned())")
 
 
-def _common_checks(a, b, d, masked: bool, k_div: int = 1):
+def _common_checks(a, b, d, masked: bool, k_div: int = 1, d_col_div: int = 1):
+    """`d_col_div` = 2: d has half the columns of the product (fused SiLU*mul epilogue)."""
     if masked:
         _require(a.dim() == 3 and b.dim() == 3 and d.dim() == 3, "masked layout wants a [G,M,K], b [G,N,K], d [G,M,N]")
         g, m, k = a.shape
         g_, n, k_ = b.shape
         g__, m_, n_ = d.shape
-        _require(g == g_ == g__ and m == m_ and n == n_ and k == k_, "shape mismatch between a, b and d")
+        _require(g == g_ == g__ and m == m_ and n == n_ * d_col_div and k == k_, "shape mismatch between a, b and d")
     else:
         _require(a.dim() == 2 and b.dim() == 3 and d.dim() == 2, "contiguous layout wants a [M,K], b [G,N,K], d [M,N]")
         m, k = a.shape
         g, n, k_ = b.shape
         m_, n_ = d.shape
-        _require(m == m_ and n == n_ and k == k_, "shape mismatch between a, b and d")
+        _require(m == m_ and n == n_ * d_col_div and k == k_, "shape mismatch between a, b and d")
     _require(n > 0 and k > 0 and g > 0, "n, k and num_groups must be positive")
     _require(a.is_cuda, "a must be a CUDA tensor")
     _require(d.is_cuda or d.is_pinned(), "d must be a CUDA tensor (or, as an extension, pinned host memory the kernel writes directly)")
@@ -317,7 +318,7 @@ def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> Tuple[torch.
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
             masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0,
-            rows_hint: Optional[int] = None) -> None:
+            rows_hint: Optional[int] = None, epilogue: int = 0) -> None:
     """Every operator ends here: one call of the torch extension's op, which fills the C descriptor from the tensors and
     launches on the current stream of a's device (csrc/torch_ops.cpp). `rows_hint`: rows the call is expected to
     multiply (masked layout: expected_m * groups; contiguous: m), for the "auto" weight path."""
@@ -328,7 +329,7 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
     with torch.cuda.device(dev):
         op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
            _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage, slot_bytes,
-           getattr(_call_caps, "num_sms", 0))
+           getattr(_call_caps, "num_sms", 0), epilogue)
 
 
 def _check_index_tensors(offsets, experts, g):
@@ -403,18 +404,30 @@ def _fp8_use_hw(ue8m0_scales: Optional[bool]) -> bool:
 def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor], d,
                                           offsets, experts, list_size=None,
                                           recipe: Optional[Tuple[int, int, int]] = None, compiled_dims: str = "nk",
-                                          disable_ue8m0_cast: bool = False, *, ue8m0_scales: Optional[bool] = None) -> None:
+                                          disable_ue8m0_cast: bool = False, *, ue8m0_scales: Optional[bool] = None,
+                                          epilogue: Optional[str] = None) -> None:
     """FP8 E4M3 with 1x128 (A) and 128x128 (B) fp32 scales, bf16 out (csrc/apis/gemm.hpp:81-157).
 
     ``ue8m0_scales`` (extension): True = apply the scales in the tensor core as power-of-two factors (the reference's
     SM100 numerics; segments must be 128-row aligned), False = exact fp32 in the drain, None = `set_fp8_scale_mode`.
+    ``epilogue="silu_mul"`` (extension, exact-scale mode only): the gate+up GEMM of an MoE layer with its activation fused
+    into the drain: `b` holds gate and up rows interleaved in groups of 16 (`ep.interleave_gate_up`), `d` is bf16
+    [M, N/2] = bf16(silu(gate) * up) -- the bits the unfused GEMM plus the activation kernel produce.
     """
-    g, m, n, k = _common_checks(a[0], b[0], d, masked=False)
+    _require(epilogue in (None, "silu_mul"), "epilogue must be None or 'silu_mul'")
+    fused = epilogue == "silu_mul"
+    g, m, n, k = _common_checks(a[0], b[0], d, masked=False, d_col_div=2 if fused else 1)
     _check_index_tensors(offsets, experts, g)
     sfa, sfb = _fp8_scales(a, b, g, (m,), n, k, recipe)
     if m == 0:
         return
     segs = _list_size_to_segments(list_size, offsets, experts)
+    if fused:
+        _require(not _fp8_use_hw(ue8m0_scales), "the fused SiLU*mul epilogue exists for the exact fp32-scale mode only")
+        _require(n % 256 == 0 and d.dtype == torch.bfloat16, "the fused SiLU*mul epilogue needs n % 256 == 0 and a bf16 d")
+        _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
+                offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, epilogue=_lib.EPILOGUE_SILU_MUL)
+        return
     if _fp8_use_hw(ue8m0_scales):
         kb, dev = (k + 127) // 128, a[0].device
         sfa_b = _fp8_blocked_ue8m0(sfa, 1, m, kb, 1, dev, cache=False)

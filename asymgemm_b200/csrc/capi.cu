@@ -191,6 +191,12 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   if (masked) AG_REQUIRE(g->masked_m != nullptr, "masked layout needs masked_m");
   else AG_REQUIRE(g->offsets != nullptr && g->experts != nullptr, "contiguous layout needs offsets and experts");
   if (kind >= 1) AG_REQUIRE(g->sfa != nullptr && g->sfb != nullptr, "quantised kinds need sfa and sfb");
+  AG_REQUIRE(g->epilogue == AG_EPILOGUE_NONE || g->epilogue == AG_EPILOGUE_SILU_MUL, "unknown epilogue %d", g->epilogue);
+  if (g->epilogue == AG_EPILOGUE_SILU_MUL) {
+    AG_REQUIRE(kind == 1, "the fused SiLU*mul epilogue exists for fp8 with fp32 scales only");
+    AG_REQUIRE(g->n % 256 == 0, "the fused SiLU*mul epilogue needs n to be a multiple of 256 (got %lld)", static_cast<long long>(g->n));
+    AG_REQUIRE(g->d_dtype == AG_D_BF16, "the fused SiLU*mul epilogue writes bf16");
+  }
 
   const uint64_t kbytes = k_bytes_of(kind, g->k);
   AG_REQUIRE(kbytes % 16 == 0, "K must make rows a multiple of 16 bytes (row bytes %llu)", static_cast<unsigned long long>(kbytes));
@@ -247,6 +253,8 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   p.b_streaming = res == RES_HOST_MAPPED;
   p.alpha = g->alpha == 0.f ? 1.f : g->alpha;
   p.split_rows = plan.split_rows;
+  p.epilogue = g->epilogue;
+  p.d_cols = g->epilogue == AG_EPILOGUE_SILU_MUL ? static_cast<int>(g->n / 2) : static_cast<int>(g->n);
 
   // Replay from scratch needs the whole amount; with less (or none) long segments re-read their weight column from b.
   p.use_scratch = (g->scratch != nullptr && need > 0 && g->scratch_bytes >= need) ? 1 : 0;

@@ -84,6 +84,10 @@ struct GemmParams {
   int expert_lo;           // this launch serves the experts [expert_lo, expert_lo + expert_n) only (a staged chunk of the
   int expert_n;            // weights): segments of other experts are skipped, and B holds just these experts' rows
   float alpha;             // NVFP4 global scale (product of the two tensor-level scales), 1.0 otherwise
+  int epilogue;            // FP8 only. 1 = the weight rows hold gate and up columns interleaved in groups of 16 (rows 32q..32q+15 =
+                           // gate columns 16q.., rows 32q+16..32q+31 = the same up columns) and the drain writes bf16(silu(gate) * up)
+                           // into d [rows, n / 2] instead of the raw product
+  int d_cols;              // row length of d in elements: n, or n / 2 with the fused activation
 };
 
 struct Item {
@@ -269,7 +273,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Store 32 consecutive output columns of one row. `vals` are fp32 bit patterns.
 __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow, int col0, const uint32_t (&vals)[32]) {
   if (p.d_fp32) {
-    float* dst = reinterpret_cast<float*>(p.d) + grow * p.n + col0;
+    float* dst = reinterpret_cast<float*>(p.d) + grow * p.d_cols + col0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (col0 + j * 4 < p.n) {
@@ -278,7 +282,7 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
       }
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.n + col0;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.d_cols + col0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (col0 + j * 8 < p.n) {
@@ -291,6 +295,31 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
       }
     }
   }
+}
+
+// Fused activation of an FP8 gate+up product: `vals` are the fp32 results of 32 consecutive (interleaved) weight rows, 16 gate
+// columns followed by the 16 up columns of the same index. Each is rounded to bf16 exactly as the unfused operator would have
+// written it, then act = bf16(silu(gate) * up) with silu(g) = g / (1 + exp(-g)) in fp32 -- the arithmetic of the separate
+// activation kernel and of the reference's CPU bucket (csrc/cpu/module.cpp:337-347), so fused and unfused agree bit for bit.
+// Writes 16 bf16 values at d[grow, col0 / 2 ..].
+__device__ __forceinline__ void store_silu_mul16(const GemmParams& p, long long grow, int col0, const uint32_t (&vals)[32]) {
+  if (col0 >= p.n) return;
+  uint32_t packed[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float act[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vals[2 * j + h])));
+      const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vals[16 + 2 * j + h])));
+      const float sg = g / (1.0f + expf(-g));
+      act[h] = sg * u;
+    }
+    packed[j] = pack_bf16(act[0], act[1]);
+  }
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.d_cols + (col0 >> 1);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
 }
 
 // REG_ACC (software-scaled kinds only): the scaled fp32 accumulators of ONE 128-row tile live in the drain warps'
@@ -609,11 +638,18 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           float* sfb_buf = sfb_smem + (warp - 4) * COLS;     // private to this warp
           // scales of a K block are fetched one block ahead, so that their latency never sits in front of the arithmetic
           const float* sfa_row = p.sfa + grow * p.sf_k;
-          const float* sfb_blk = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k;   // FP8 only
+          // FP8 only: the 128x128 weight block of this warpgroup's columns. With the fused activation the columns are
+          // interleaved gate / up rows of the weight, which lie in two different blocks (see GemmParams::epilogue).
+          const bool fused = KIND == Kind::FP8 && p.epilogue != 0;
+          const int blk_g = fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7;
+          const int blk_u = fused ? ((p.n >> 1) + ((n0 + col_base) >> 1)) >> 7 : blk_g;
+          const float* sfb_blk = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_g) * p.sf_k;
+          const float* sfb_blk_u = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_u) * p.sf_k;
           float sa_next = valid ? __ldg(sfa_row) : 0.f;
           float sb_next = KIND == Kind::FP8 ? __ldg(sfb_blk) : 0.f;
+          float sbu_next = KIND == Kind::FP8 ? __ldg(sfb_blk_u) : 0.f;
           // one 32-column piece of the raw product, scaled and added into the accumulators
-          auto accumulate = [&](auto& r, auto c0_tag, float sa, float sb_scalar, int kb) {
+          auto accumulate = [&](auto& r, auto c0_tag, float sa, float sb_scalar, float sb_up, int kb) {
             constexpr int W = sizeof(r) / sizeof(r[0]);
             constexpr int c0 = decltype(c0_tag)::value;
             if constexpr (KIND == Kind::INT8) {
@@ -632,16 +668,19 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 scale = sa * sfb_buf[c0 + j];
               } else {
                 prod = __uint_as_float(r[j]);
-                scale = sa * sb_scalar;
+                scale = sa * (((c0 + j) & 16) ? sb_up : sb_scalar);   // columns 16..31 of every 32 are up rows when fused
               }
               acc[c0 + j] = fmaf(prod, scale, acc[c0 + j]);
             }
           };
           for (int kb = 0; kb < kb_count && ok; ++kb, ++rt) {
-            const float sa = sa_next, sb_scalar = sb_next;
+            const float sa = sa_next, sb_scalar = sb_next, sb_up = sbu_next;
             if (kb + 1 < kb_count) {
               sa_next = valid ? __ldg(sfa_row + kb + 1) : 0.f;
-              if constexpr (KIND == Kind::FP8) sb_next = __ldg(sfb_blk + kb + 1);
+              if constexpr (KIND == Kind::FP8) {
+                sb_next = __ldg(sfb_blk + kb + 1);
+                sbu_next = __ldg(sfb_blk_u + kb + 1);
+              }
             }
             if constexpr (KIND == Kind::INT8) {
 #pragma unroll
@@ -672,7 +711,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 tmem_ld_cols(raw_addr + cc * LW, r);
                 tmem_wait_ld();
                 if (cc == COLS / LW - 1) release_slot();
-                accumulate(r, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, kb);
+                accumulate(r, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, sb_up, kb);
               };
               piece(std::integral_constant<int, 0>{});
               if constexpr (COLS / LW > 1) piece(std::integral_constant<int, 1>{});
@@ -691,7 +730,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               uint32_t v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[cc * 32 + j]);
-              store_row32(p, grow, n0 + col_base + cc * 32, v);
+              if (fused) store_silu_mul16(p, grow, n0 + col_base + cc * 32, v);
+              else store_row32(p, grow, n0 + col_base + cc * 32, v);
             }
           }
         } else if constexpr (T::sw_scale) {
@@ -699,9 +739,13 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const int col_base = ((warp - 4) >> 2) * COLS;
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             // column scales of this K block
-            float sb_scalar = 0.f;
+            float sb_scalar = 0.f, sb_up = 0.f;
+            const bool fused = KIND == Kind::FP8 && p.epilogue != 0;
             if constexpr (KIND == Kind::FP8) {
-              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + ((n0 + col_base) >> 7)) * p.sf_k + kb);
+              const int blk_g = fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7;
+              const int blk_u = fused ? ((p.n >> 1) + ((n0 + col_base) >> 1)) >> 7 : blk_g;
+              sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_g) * p.sf_k + kb);
+              sb_up = fused ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_u) * p.sf_k + kb) : sb_scalar;
             }
             for (int mt = 0; mt < mc && ok; ++mt, ++rt) {
               const long long grow = static_cast<long long>(it.row0) + (m0 + mt) * BM + row_in_tile;
@@ -747,13 +791,16 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     scale = sa * sfb_buf[cc * 32 + j];
                   } else {
                     prod = __uint_as_float(r[j]);
-                    scale = sa * sb_scalar;
+                    scale = sa * ((j & 16) ? sb_up : sb_scalar);
                   }
                   const float prev = kb > 0 ? __uint_as_float(a[j]) : 0.f;
                   a[j] = __float_as_uint(fmaf(prod, scale, prev));
                 }
                 if (last) {
-                  if (valid) store_row32(p, grow, n0 + col_base + cc * 32, a);
+                  if (valid) {
+                    if (fused) store_silu_mul16(p, grow, n0 + col_base + cc * 32, a);
+                    else store_row32(p, grow, n0 + col_base + cc * 32, a);
+                  }
                 } else {
                   tmem_st_32x32b_x32(acc_addr + cc * 32, a);
                 }

@@ -258,7 +258,8 @@ bool aligned_to(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t
 
 extern "C" {
 
-int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, void* stream) {
+int ag_quant_rows_fp8_upto(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, const int32_t* rows_used,
+                           void* stream) {
   if (!x_bf16 || !q || !sf || rows < 0 || cols <= 0 || cols % 4 != 0) return agb_fail(AG_E_INVALID, "bad arguments (cols must be a multiple of 4)");
   if (rows == 0) return AG_OK;
   // the narrow kernel reads 8 bytes of x and writes 4 bytes of q per lane (the wide one 16 and 8)
@@ -269,13 +270,17 @@ int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int6
     const int ppr = (bpr + 1) / 2;
     const long long wide = rows * ppr;
     agb::quant_rows_wide_kernel<0><<<static_cast<unsigned>((wide + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, ppr, pow2_scales, nullptr);
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, ppr, pow2_scales, rows_used);
     return launch_check();
   }
   const long long warps = rows * bpr;
   agb::quant_rows_kernel<0><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales, nullptr);
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), sf, rows, static_cast<int>(cols), bpr, pow2_scales, rows_used);
   return launch_check();
+}
+
+int ag_quant_rows_fp8(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, void* stream) {
+  return ag_quant_rows_fp8_upto(x_bf16, q, sf, rows, cols, pow2_scales, nullptr, stream);
 }
 
 int ag_silu_mul_quant_fp8_upto(const void* gate_up_bf16, void* q, float* sf, int64_t rows, int64_t inter, int32_t pow2_scales,

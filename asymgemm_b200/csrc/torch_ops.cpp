@@ -28,7 +28,7 @@ void m_grouped_gemm_nt(int64_t kind, int64_t layout, const at::Tensor& a, const 
                        int64_t max_segments, const OptTensor& masked_m, int64_t m, int64_t n, int64_t k, int64_t num_groups,
                        const OptTensor& scratch, const at::Tensor& status, int64_t timeout_ms, const OptTensor& raw_dump,
                        double alpha, int64_t tile_config, int64_t no_split, const OptTensor& stage, int64_t stage_chunk_bytes,
-                       int64_t num_sms) {
+                       int64_t num_sms, int64_t epilogue) {
   TORCH_CHECK(a.is_cuda(), "a must be a CUDA tensor");
   TORCH_CHECK(b.is_cuda() || b.is_pinned(), "b must be a CUDA tensor or pinned host memory (b.is_cuda() or b.is_pinned())");
   TORCH_CHECK(d.is_cuda() || d.is_pinned(), "d must be a CUDA tensor or pinned host memory");
@@ -64,6 +64,7 @@ void m_grouped_gemm_nt(int64_t kind, int64_t layout, const at::Tensor& a, const 
     desc.scratch_bytes = static_cast<uint64_t>(scratch->numel()) * scratch->element_size();
   }
   desc.status = static_cast<int32_t*>(status.data_ptr());
+  desc.epilogue = static_cast<int32_t>(epilogue);
   desc.num_sms = static_cast<int32_t>(num_sms > 0 ? num_sms : 0);   // 0: every SM, or the process-wide cap
   desc.timeout_ms = static_cast<uint32_t>(timeout_ms);
   desc.raw_dump = static_cast<int32_t*>(ptr_of(raw_dump));
@@ -102,7 +103,7 @@ TORCH_LIBRARY(asymgemm_b200, m) {
       "m_grouped_gemm_nt(int kind, int layout, Tensor a, Tensor? sfa, Tensor b, Tensor? sfb, Tensor(a!) d, Tensor? offsets, "
       "Tensor? experts, int max_segments, Tensor? masked_m, int m, int n, int k, int num_groups, Tensor? scratch, "
       "Tensor status, int timeout_ms, Tensor? raw_dump, float alpha, int tile_config, int no_split, Tensor? stage, int stage_chunk_bytes, "
-      "int num_sms) -> ()");
+      "int num_sms, int epilogue) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(asymgemm_b200, CUDA, m) { m.impl("m_grouped_gemm_nt", &m_grouped_gemm_nt); }

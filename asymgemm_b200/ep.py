@@ -389,6 +389,25 @@ def rebalance_expert_ranges(ranges: List[Tuple[int, int]], step_ms: List[float],
     return proportional_expert_ranges(rates, ranges[-1][1], tolerance=0.0)
 
 
+def gate_up_interleave_index(inter: int, device=None) -> torch.Tensor:
+    """Row permutation for the fused SiLU*mul epilogue: row r of the interleaved weight is row index[r] of the usual
+    [gate; up] tensor [2*inter, hidden] -- gate and up rows alternate in groups of 16, so that any 32 consecutive rows hold
+    16 gate columns and the same 16 up columns (`epilogue` of the C descriptor)."""
+    r = torch.arange(2 * inter, device=device)
+    return (r % 32 // 16) * inter + r // 32 * 16 + r % 16
+
+
+def interleave_gate_up(w13: torch.Tensor) -> torch.Tensor:
+    """[..., 2*inter, hidden] weights in the usual [gate; up] order -> the same rows interleaved for the fused SiLU*mul
+    epilogue (a new tensor on w13's device; the block scales stay as they are)."""
+    inter = w13.shape[-2] // 2
+    if inter % 128:
+        raise RuntimeError("inter must be a multiple of 128")
+    src = w13.view(torch.uint8) if w13.dtype == torch.float8_e4m3fn else w13
+    out = src.index_select(-2, gate_up_interleave_index(inter, w13.device))
+    return out.view(w13.dtype) if w13.dtype == torch.float8_e4m3fn else out
+
+
 def gpu_numa_node(device_index: int) -> int:
     """NUMA node of the GPU's PCIe root, or -1 when the platform does not say (single-node VMs)."""
     try:
@@ -412,7 +431,8 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
                  expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False, pipeline_groups: int = 1,
-                 comm_sms: int = 24, exchange: str = "nccl", max_tokens: Optional[int] = None, top_k: Optional[int] = None):
+                 comm_sms: int = 24, exchange: str = "nccl", max_tokens: Optional[int] = None, top_k: Optional[int] = None,
+                 fused_activation: bool = False):
         """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
         (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly.
         Whether the kernel reads the pinned weights itself or the copy engine stages them is the operators' setting
@@ -424,7 +444,14 @@ class ExpertParallelMoE:
         all-to-all(v), reading the split sizes back on the host; "peer" routes, lays out and exchanges with this library's
         own kernels, which store rows straight into the owner rank's buffers over NVLink (`ep_peer.PeerExchange`; needs
         `max_tokens`, the most tokens one rank brings to a step, and `top_k`; the ranks must be processes of one node).
-        Both give the same output bit for bit."""
+        Both give the same output bit for bit.
+        `fused_activation`: the gate+up GEMM writes bf16(silu(gate) * up) itself (`epilogue="silu_mul"` of the FP8 operator),
+        so the [rows, 2*inter] intermediate is never written; `w13[0]` must then hold the rows of every expert in the
+        interleaved order of `interleave_gate_up` (a weight-preparation step; the scales stay as they are). Exact-scale
+        mode only; same output bit for bit."""
+        self.fused_activation = bool(fused_activation)
+        if self.fused_activation and ue8m0_scales:
+            raise RuntimeError("fused_activation exists for the exact fp32-scale mode only")
         if exchange not in ("nccl", "peer"):
             raise RuntimeError("exchange must be 'nccl' or 'peer'")
         self.exchange = exchange
@@ -483,11 +510,22 @@ class ExpertParallelMoE:
         w13, w2 = self._weights_of(first, self.dispatcher.experts_per_rank if count is None else count)
         m = state.padded_rows
         dev = a_q.device
-        d1 = torch.empty((m, 2 * self.inter), dtype=torch.bfloat16, device=dev)
         d2 = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=dev)
         if m == 0:
             return d2
         hw = self.ue8m0_scales
+        if self.fused_activation:
+            act = torch.empty((m, self.inter), dtype=torch.bfloat16, device=dev)
+            api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), w13, act, state.offsets, state.experts, None, epilogue="silu_mul")
+            self._mark("gemm_gate_up")
+            a2, s2 = moe_ops.quant_rows_fp8(act, rows_used=rows_used)
+            self._mark("silu_mul_requant")
+            api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None)
+            self._mark("gemm_down")
+            if self.keep_intermediates:
+                self.intermediates = dict(a_q=a_q, sfa=sfa, act=act, a2=a2, s2=s2, d2=d2, state=state, first=first)
+            return d2
+        d1 = torch.empty((m, 2 * self.inter), dtype=torch.bfloat16, device=dev)
         api.m_grouped_fp8_asym_gemm_nt_contiguous((a_q, sfa), w13, d1, state.offsets, state.experts, None, ue8m0_scales=hw)
         self._mark("gemm_gate_up")
         a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw, rows_used=rows_used)

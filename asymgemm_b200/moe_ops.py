@@ -17,16 +17,18 @@ def _stream(t: torch.Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def quant_rows_fp8(x: torch.Tensor, pow2_scales: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_rows_fp8(x: torch.Tensor, pow2_scales: bool = False, rows_used: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [rows, cols] -> (e4m3 [rows, cols], fp32 scales [rows, ceil(cols/128)]), one kernel.
-    `pow2_scales` rounds the scales up to powers of two (the quantisers' use_ue8m0=True)."""
+    `pow2_scales` rounds the scales up to powers of two (the quantisers' use_ue8m0=True). `rows_used`: device int32 tensor;
+    rows from that count on are neither read nor written."""
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
         raise RuntimeError("quant_rows_fp8 wants a contiguous 2-D bf16 CUDA tensor")
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
     sf = torch.empty((rows, (cols + 127) // 128), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.load().ag_quant_rows_fp8(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, cols, int(pow2_scales), _stream(x)))
+        _lib.check(_lib.load().ag_quant_rows_fp8_upto(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, cols, int(pow2_scales),
+                                                      rows_used.data_ptr() if rows_used is not None else None, _stream(x)))
     return q, sf
 
 

@@ -127,10 +127,12 @@ def build_workload(cfg, rank, world, device, seed=0, weights_on_device=False, hu
 MOE_SEED = 5
 
 
-def build_moe(cfg, rank, world, device, group, seed=MOE_SEED, expert_ranges=None, ue8m0=False, pipeline_groups=1):
+def build_moe(cfg, rank, world, device, group, seed=MOE_SEED, expert_ranges=None, ue8m0=False, pipeline_groups=1, fused=True):
     """This rank's shard of the FP8 MoE layer (weights quantised on the GPU, then moved to pinned host memory, on the
     GPU's NUMA node when the platform exposes one) and this rank's slice of the token batch with its routing. Expert e's
-    weights come from a generator keyed by e, so any rank can rebuild any expert for the parity check."""
+    weights come from a generator keyed by e, so any rank can rebuild any expert for the parity check. `fused`: the gate+up
+    weights are stored with gate and up rows interleaved (a weight-preparation step) and the layer fuses SiLU*mul into the
+    gate+up GEMM's drain (exact-scale mode only)."""
     from asymgemm_b200 import ep
     from asymgemm_b200.testing.moe_reference import expert_generator, expert_weights
     e_total, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
@@ -144,15 +146,18 @@ def build_moe(cfg, rank, world, device, group, seed=MOE_SEED, expert_ranges=None
     w2 = ep.pinned_empty((epr, h, i), torch.float8_e4m3fn, node)
     s13 = torch.empty((epr, 2 * i // 128, h // 128), dtype=torch.float32, device=device)
     s2 = torch.empty((epr, h // 128, i // 128), dtype=torch.float32, device=device)
+    fused = fused and not ue8m0
     for e in range(epr):
         q13, sc13, q2, sc2 = expert_weights(seed, lo + e, h, i, device, use_ue8m0=ue8m0)
+        if fused:
+            q13 = ep.interleave_gate_up(q13)
         w13[e].copy_(q13, non_blocking=True)
         s13[e] = sc13
         w2[e].copy_(q2, non_blocking=True)
         s2[e] = sc2
     torch.cuda.synchronize(device)
     layer = ep.ExpertParallelMoE(e_total, h, i, (w13, s13), (w2, s2), group, expert_ranges, ue8m0_scales=ue8m0,
-                                 pipeline_groups=pipeline_groups)
+                                 pipeline_groups=pipeline_groups, fused_activation=fused)
     t_local = cfg["tokens"] // world
     gen = expert_generator(device, seed, 100000 + rank, 3)      # this rank's tokens and router logits
     x = torch.randn((t_local, h), device=device, generator=gen).to(torch.bfloat16)
@@ -160,7 +165,7 @@ def build_moe(cfg, rank, world, device, group, seed=MOE_SEED, expert_ranges=None
     topk_w, topk_ids = torch.topk(torch.softmax(logits, dim=-1), cfg["top_k"], dim=-1)
     topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
     rows = t_local * cfg["top_k"]
-    return dict(kind="moe", layer=layer, x=x, ids=topk_ids, w=topk_w, numa_node=node, seed=seed, ue8m0=ue8m0,
+    return dict(kind="moe", layer=layer, x=x, ids=topk_ids, w=topk_w, numa_node=node, seed=seed, ue8m0=ue8m0, fused=fused,
                 flops=float(rows) * 2.0 * (2 * i * h + h * i), host_bytes=float(epr) * (2 * i * h + h * i),
                 nvlink_bytes=float(rows) * (h + h // 128 * 4 + 2 * h) * (world - 1) / world if world > 1 else 0.0)
 
@@ -571,7 +576,7 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
         ag.check_status()
     if args.exchange in ("peer", "both") and args.pipeline_groups <= 1:
         peer_layer = ep.ExpertParallelMoE(cfg["experts"], cfg["hidden"], cfg["inter"], layer.w13, layer.w2, None, ranges, ue8m0_scales=ue,
-                                          exchange="peer", max_tokens=w["x"].shape[0], top_k=cfg["top_k"])
+                                          exchange="peer", max_tokens=w["x"].shape[0], top_k=cfg["top_k"], fused_activation=w["fused"])
         pstep = lambda: peer_layer.forward(w["x"], w["ids"], w["w"])
         for _ in range(2):
             y_peer = pstep()
@@ -644,6 +649,8 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
                      "peer": "this library's kernels: histogram, plan, rows stored into the owner's layout over NVLink peer memory, results "
                              "stored back the same way; no host synchronisation"}[chosen],
     }
+    rec["activation"] = ("SiLU*mul fused into the gate+up GEMM's drain (weights stored with gate / up rows interleaved)" if w["fused"]
+                         else "separate SiLU*mul + requantisation kernel")
     if peer_ms is not None:
         rec["exchange_ms_per_step"] = {"nccl": round(nccl_all, 3) if nccl_all is not None else None, "peer": round(peer_all, 3),
                                        "outputs_bit_equal": same}

@@ -37,6 +37,11 @@ typedef enum ag_layout {
 
 typedef enum ag_d_dtype { AG_D_BF16 = 0, AG_D_FP32 = 1 } ag_d_dtype_t;
 
+typedef enum ag_epilogue {
+  AG_EPILOGUE_NONE = 0,    /* d = a x b^T */
+  AG_EPILOGUE_SILU_MUL = 1 /* fp8 gate+up GEMM of an MoE layer: d [rows, n / 2] = bf16(silu(gate) * up), see ag_gemm_desc_t.epilogue */
+} ag_epilogue_t;
+
 /* One grouped-GEMM call. Unused fields must be zero / NULL. */
 typedef struct ag_gemm_desc {
   int32_t layout;  /* ag_layout_t */
@@ -95,6 +100,16 @@ typedef struct ag_gemm_desc {
                                  With a smaller value the buffer is a ring of up to 8 slots: the copies then run further
                                  ahead of the GEMMs, which matters when a prefetch (below) fills the ring while other
                                  work keeps the link idle. */
+
+  /* ag_epilogue_t, ag_m_grouped_fp8_gemm_nt only. AG_EPILOGUE_SILU_MUL fuses the activation between the two GEMMs of an MoE
+     layer into the gate+up GEMM: b must hold the gate and up rows of every expert INTERLEAVED in groups of 16 -- weight row
+     32q + i is gate row 16q + i and weight row 32q + 16 + i is up row 16q + i (i < 16), i.e. row r of the interleaved
+     tensor is row (r % 32 / 16) * (n / 2) + r / 32 * 16 + r % 16 of the usual [gate; up] tensor -- while sfb keeps the
+     block scales of the usual tensor. d is then bf16 [rows, n / 2] and receives bf16(silu(g) * u), g and u being the bf16
+     values the unfused call would have written, silu(g) = g / (1 + exp(-g)) in fp32 (the reference's activation,
+     csrc/cpu/module.cpp:337-347): the same bits as the unfused GEMM followed by ag_silu_mul_quant_fp8's activation, without
+     the [rows, n] intermediate. n % 256 == 0. */
+  int32_t epilogue;
 } ag_gemm_desc_t;
 
 /* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked
@@ -226,6 +241,10 @@ int ag_silu_mul_quant_fp8(const void* gate_up_bf16, void* q, float* sf, int64_t 
 /* dst[dst_rows ? dst_rows[i] : i] = src[src_rows ? src_rows[i] : i], i < rows; rows of row_bytes (multiple of 16) bytes. */
 int ag_move_rows(const void* src, void* dst, const int64_t* src_rows, const int64_t* dst_rows, int64_t rows, int64_t row_bytes,
                  void* stream);
+
+/* As ag_quant_rows_fp8 over a buffer of which only the first *rows_used rows hold data (see ag_silu_mul_quant_fp8_upto). */
+int ag_quant_rows_fp8_upto(const void* x_bf16, void* q, float* sf, int64_t rows, int64_t cols, int32_t pow2_scales, const int32_t* rows_used,
+                           void* stream);
 
 /* As ag_silu_mul_quant_fp8 over a buffer of `rows` rows of which only the first *rows_used (a device int32, read by the
  * kernel) hold data: rows past that count are neither read nor written. For layouts whose size only the device knows

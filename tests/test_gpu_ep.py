@@ -81,6 +81,10 @@ def _case(rank, world, device, weight_path="stream"):
         assert torch.equal(peer.forward(x, ids, wts), y), "peer exchange, third call"
     finally:
         peer.peer.close()
+    # the activation fused into the gate+up GEMM's drain (weights interleaved gate / up): same output bit for bit
+    w13_il = ep.interleave_gate_up(layer.w13[0].to(device)).cpu().pin_memory()
+    fused = ep.ExpertParallelMoE(num_experts, hidden, inter, (w13_il, layer.w13[1]), layer.w2, fused_activation=True)
+    assert torch.equal(fused.forward(x, ids, wts), y), "fused activation"
     if weight_path == "staged":
         # the copy engine moves the same bytes the kernel would read: same result, also when the staging buffers are reused
         import asymgemm_b200 as ag

@@ -359,6 +359,42 @@ def test_fp8_hardware_ue8m0_scaling_contiguous(tile, b_on_host):
     assert (a != b).mean() < 0.05
 
 
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6], indirect=True)
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_fp8_fused_silu_mul_epilogue_equals_gemm_plus_activation_kernel(tile, b_on_host):
+    """The gate+up GEMM with the activation fused into its drain (weights interleaved gate / up in groups of 16) against the
+    plain GEMM followed by the activation kernel: bf16(silu(gate) * up) must be the same bits, in every tile configuration,
+    with ragged rows, a long segment and an empty expert; valid rows only are written."""
+    from asymgemm_b200 import ep, moe_ops
+    rows = [300, 0, 1, 129, 2300, 64]
+    inter, k = 384, 640
+    c = H.make_contiguous_case("fp8", rows, 2 * inter, k, seed=71, b_on_host=b_on_host)
+    d1 = torch.zeros((c["m_total"], 2 * inter), dtype=torch.bfloat16, device="cuda")
+    args = ((c["a"], c["sfa"]), (c["b"], c["sfb"]))
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous(*args, d1, c["offsets"], c["experts"], c["list_size"])
+    q_ref, s_ref = moe_ops.silu_mul_quant_fp8(d1, inter)
+    b_il = ep.interleave_gate_up(c["b"].cuda())
+    b_il = b_il if not b_on_host else H.pin(b_il)
+    act = torch.full((c["m_total"], inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (b_il, c["sfb"]), act, c["offsets"], c["experts"], c["list_size"],
+                                             epilogue="silu_mul")
+    torch.cuda.synchronize()
+    mask = torch.from_numpy(H.valid_row_mask(c["segments"], c["m_total"])).cuda()
+    assert torch.isnan(act[~mask]).all()
+    q, s = moe_ops.quant_rows_fp8(act)
+    assert torch.equal(s[mask], s_ref[mask]) and torch.equal(q.view(torch.uint8)[mask], q_ref.view(torch.uint8)[mask])
+    # and against torch's formulation of the activation on the unfused output (exp implementations may differ in the last bit)
+    g, u = d1[:, :inter].float(), d1[:, inter:].float()
+    want = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
+    assert (act[mask].float() - want[mask].float()).abs().max() <= 2 ** -7 * want[mask].float().abs().max()
+    assert (act[mask] != want[mask]).float().mean() < 1e-2
+    with pytest.raises(RuntimeError, match="n % 256"):
+        c2 = H.make_contiguous_case("fp8", [64], 128, 128, seed=72)
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((c2["a"], c2["sfa"]), (c2["b"], c2["sfb"]),
+                                                 torch.zeros((c2["m_total"], 64), dtype=torch.bfloat16, device="cuda"),
+                                                 c2["offsets"], c2["experts"], c2["list_size"], epilogue="silu_mul")
+
+
 def test_c_abi_error_surfaces_as_runtime_error_through_the_operator():
     """A descriptor the library refuses (a tile configuration that does not exist for the operand kind) comes back as the
     RuntimeError the reference API raises, with the library's message, and leaves the context usable."""

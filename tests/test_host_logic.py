@@ -216,6 +216,22 @@ def test_link_probe_candidate_sets():
     assert lp.choose_devices(8, 8)["devices"] == list(range(8))         # nothing to choose: no probe, no GPU needed
 
 
+def test_gate_up_interleave_index():
+    """Row order of the fused-activation weights: every 32 consecutive rows are 16 gate rows and the matching 16 up rows."""
+    from asymgemm_b200 import ep
+    inter = 256
+    idx = ep.gate_up_interleave_index(inter)
+    assert sorted(idx.tolist()) == list(range(2 * inter))
+    assert idx[:16].tolist() == list(range(16)) and idx[16:32].tolist() == list(range(inter, inter + 16))
+    assert idx[32:48].tolist() == list(range(16, 32)) and idx[48:64].tolist() == list(range(inter + 16, inter + 32))
+    w = torch.arange(2 * inter * 4, dtype=torch.float32).view(2 * inter, 4)
+    wi = ep.interleave_gate_up(w)
+    for r in (0, 15, 16, 31, 32, 100, 2 * inter - 1):
+        assert torch.equal(wi[r], w[(r % 32 // 16) * inter + r // 32 * 16 + r % 16])
+    with pytest.raises(RuntimeError):
+        ep.interleave_gate_up(torch.zeros(2 * 100, 8))
+
+
 def test_hot_expert_cache_table_split():
     from asymgemm_b200.expert_cache import HotExpertCache
     c = HotExpertCache.__new__(HotExpertCache)
@@ -235,11 +251,11 @@ def test_torch_extension_loads_and_registers_the_launch_op():
     from asymgemm_b200 import _lib
     ops = _lib.torch_ops()
     schema = str(ops.m_grouped_gemm_nt.default._schema)
-    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema and "int num_sms" in schema
+    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema and "int num_sms" in schema and "int epilogue" in schema
     z = torch.zeros(4, 4)
     with pytest.raises(NotImplementedError):
         ops.m_grouped_gemm_nt(0, 0, z, None, z, None, z, None, None, 0, None, 4, 4, 4, 1, None,
-                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0, 0)
+                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0, 0, 0)
 
 
 def test_auto_weight_path_rule():
