@@ -186,7 +186,7 @@ def load() -> ctypes.CDLL:
                                c_void_p, c_void_p, c_void_p, c_void_p]
     lib.ag_ep_plan.restype = c_int32
     lib.ag_ep_dispatch.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_void_p, c_int32, c_int32, c_void_p,
-                                   c_void_p, c_int64, POINTER(EpPeers), c_void_p]
+                                   c_void_p, c_int64, c_void_p, POINTER(EpPeers), c_void_p]
     lib.ag_ep_dispatch.restype = c_int32
     lib.ag_ep_return.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, POINTER(EpPeers), c_void_p]
     lib.ag_ep_return.restype = c_int32

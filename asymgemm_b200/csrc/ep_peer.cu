@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
                                                           const long long* __restrict__ ids, long long pairs, int top_k, int vec_per_row,
                                                           int sf_per_row, const int* __restrict__ range_lo, int world, int me,
                                                           const int* __restrict__ send_base, int* __restrict__ cursors, long long cap_rows,
-                                                          PeerTable peers) {
+                                                          long long* __restrict__ pair_row, PeerTable peers) {
   __shared__ int lo[kMaxRanks + 1];
   if (threadIdx.x <= world) lo[threadIdx.x] = range_lo[threadIdx.x];
   __syncthreads();
@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
   if (lane == 0) slot = atomicAdd(&cursors[e], 1);
   slot = __shfl_sync(0xffffffffu, slot, 0);
   const long long dest = static_cast<long long>(send_base[e]) + slot;
+  if (pair_row != nullptr && lane == 0) pair_row[p] = dest < cap_rows ? dest : 0;   // one rank: where this pair's result will be
   if (dest >= cap_rows) return;   // the plan kernel has flagged the overflow
   const long long t = p / top_k;
   const uint4* src = x_q + t * vec_per_row;
@@ -270,7 +271,7 @@ int ag_ep_plan(const int32_t* counts_all, const int32_t* range_lo, int32_t world
 
 int ag_ep_dispatch(const void* x_q, const float* sfx, const int64_t* ids, int64_t tokens, int32_t top_k, int64_t row_bytes, int32_t sf_per_row,
                    const int32_t* range_lo, int32_t world, int32_t rank, const int32_t* send_base, int32_t* cursors, int64_t cap_rows,
-                   const ag_ep_peers_t* peers, void* stream) {
+                   int64_t* pair_row, const ag_ep_peers_t* peers, void* stream) {
   if (!x_q || !sfx || !ids || !range_lo || !send_base || !cursors || tokens < 0 || top_k <= 0 || row_bytes <= 0 || row_bytes % 16 != 0 ||
       sf_per_row <= 0 || !aligned16(x_q) || rank < 0 || rank >= world || cap_rows <= 0)
     return agb_fail(AG_E_INVALID, "bad arguments (rows must be 16-byte multiples and 16-byte aligned)");
@@ -281,7 +282,7 @@ int ag_ep_dispatch(const void* x_q, const float* sfx, const int64_t* ids, int64_
   if (pairs >= (1LL << 32)) return agb_fail(AG_E_INVALID, "more than 2^32 (token, slot) pairs per rank");
   agb::ep_dispatch_kernel<<<static_cast<unsigned>((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x_q), sfx, reinterpret_cast<const long long*>(ids), pairs, top_k, static_cast<int>(row_bytes / 16), sf_per_row,
-      range_lo, world, rank, send_base, cursors, cap_rows, t);
+      range_lo, world, rank, send_base, cursors, cap_rows, reinterpret_cast<long long*>(pair_row), t);
   return launch_check();
 }
 

@@ -549,6 +549,11 @@ class ExpertParallelMoE:
         state = DispatchState(None, [], [], None, None, px.cap_rows, px.offsets, px.experts, tokens, top_k)
         self._mark("layout")
         out = self.experts_forward(a_q, px.sfa, state, rows_used=px.rows_used[:1])
+        if px.pair_row is not None:      # one rank: every result already lies in this rank's memory
+            self._mark("return")
+            y = moe_ops.combine_topk(out, px.pair_row, topk_weights, tokens, top_k)
+            self._mark("combine")
+            return y
         px.send_back(out)
         self._mark("return")
         y = moe_ops.combine_topk(px.ret.view(torch.bfloat16).view(px.pairs_cap, self.hidden), None, topk_weights, tokens, top_k)

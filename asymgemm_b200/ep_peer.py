@@ -112,6 +112,8 @@ class PeerExchange:
         self.experts = torch.full((self.epr + 1,), -1, dtype=torch.int32, device=device)
         self.rows_used = torch.zeros(2, dtype=torch.int32, device=device)
         self._token = torch.zeros(1, dtype=torch.int32, device=device)
+        # one rank: row of every pair in the layout, so that the results are combined where they lie (no return copy)
+        self.pair_row = torch.zeros(pairs, dtype=torch.int64, device=device) if self.world == 1 else None
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=group)      # every rank has mapped every buffer before anyone stores into one
@@ -156,7 +158,9 @@ class PeerExchange:
         with torch.cuda.device(self.device):
             _lib.check(lib.ag_ep_dispatch(x_q.data_ptr(), sfx.data_ptr(), self._ids.data_ptr(), tokens, self.top_k, self.row_bytes,
                                           self.sf_per_row, self.range_lo.data_ptr(), self.world, self.rank, self.send_base.data_ptr(),
-                                          self.cursors.data_ptr(), self.cap_rows, ctypes.byref(self.peers), self._stream()))
+                                          self.cursors.data_ptr(), self.cap_rows,
+                                          self.pair_row.data_ptr() if self.pair_row is not None else None,
+                                          ctypes.byref(self.peers), self._stream()))
         self.rendezvous()
 
     def send_back(self, out: torch.Tensor) -> None:

@@ -306,10 +306,12 @@ int ag_ep_plan(const int32_t* counts_all, const int32_t* range_lo, int32_t world
                int32_t* status, void* stream);
 
 /* Every (token, slot) pair of this rank: the token's row x_q [tokens, row_bytes] and scales sfx [tokens, sf_per_row] are
- * stored into the next free row of the pair's expert on the owner rank, with the pair's return address beside it. */
+ * stored into the next free row of the pair's expert on the owner rank, with the pair's return address beside it.
+ * pair_row (optional, int64 [tokens * top_k]) receives the row each pair went to: with one rank the results can then be
+ * combined straight out of the layout (ag_combine_topk with pos = pair_row) and ag_ep_return is not needed. */
 int ag_ep_dispatch(const void* x_q, const float* sfx, const int64_t* ids, int64_t tokens, int32_t top_k, int64_t row_bytes, int32_t sf_per_row,
                    const int32_t* range_lo, int32_t world, int32_t rank, const int32_t* send_base, int32_t* cursors, int64_t cap_rows,
-                   const ag_ep_peers_t* peers, void* stream);
+                   int64_t* pair_row, const ag_ep_peers_t* peers, void* stream);
 
 /* Every valid row of this rank's result `out` [cap_rows, row_bytes] is stored into its pair's slot of the source rank's `ret`. */
 int ag_ep_return(const void* out, const int64_t* my_meta, const int32_t* rows_used, int64_t cap_rows, int64_t row_bytes, int32_t world,
