@@ -117,6 +117,20 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(const int* __rest
   }
 }
 
+// Warp-wide copy of one row of `vecs` 16-byte vectors, four loads in flight per lane before the stores go out: remote
+// stores are posted, so the load latency is what has to be covered.
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs, int lane) {
+  int i = lane;
+  for (; i + 96 < vecs; i += 128) {
+    const uint4 v0 = src[i], v1 = src[i + 32], v2 = src[i + 64], v3 = src[i + 96];
+    dst[i] = v0;
+    dst[i + 32] = v1;
+    dst[i + 64] = v2;
+    dst[i + 96] = v3;
+  }
+  for (; i < vecs; i += 32) dst[i] = src[i];
+}
+
 __device__ __forceinline__ int owner_of(const int* range_lo, int world, int e) {
   int r = 0;
   while (r + 1 < world && e >= range_lo[r + 1]) ++r;
@@ -148,7 +162,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
   const long long t = p / top_k;
   const uint4* src = x_q + t * vec_per_row;
   uint4* dst = static_cast<uint4*>(peers.a[o]) + dest * vec_per_row;
-  for (int i = lane; i < vec_per_row; i += 32) dst[i] = src[i];
+  copy_row(src, dst, vec_per_row, lane);
   const float* ssrc = sfx + t * sf_per_row;
   float* sdst = static_cast<float*>(peers.sfa[o]) + dest * sf_per_row;
   for (int i = lane; i < sf_per_row; i += 32) sdst[i] = ssrc[i];
@@ -167,7 +181,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const uint4* __restrict_
   const long long p = m & 0xffffffffLL;
   const uint4* src = out + r * vec_per_row;
   uint4* dst = static_cast<uint4*>(peers.ret[s]) + p * vec_per_row;
-  for (int i = lane; i < vec_per_row; i += 32) dst[i] = src[i];
+  copy_row(src, dst, vec_per_row, lane);
 }
 
 }  // namespace agb

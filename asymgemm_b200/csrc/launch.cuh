@@ -22,7 +22,7 @@ constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
     {32, 8, 4, 4},   // 2: as 1 with longer contiguous runs per row
     {64, 2, 8, 4},   // 3: B streamed from host memory (default: 51.0 GB/s of a 55.6 GB/s copy peak on the FP8 7168x4096 case)
     {128, 1, 8, 4},  // 4: FP8 / INT8 with B resident in device memory: scaled accumulators in registers, one tile per item
-    {256, 1, 3, 6},  // 5: B resident in device memory, 256-column items: BF16 keeps two 128 x 256 accumulators in TMEM (a weight
+    {256, 1, 4, 4},  // 5: B resident in device memory, 256-column items: BF16 keeps two 128 x 256 accumulators in TMEM (a weight
                      //    stage serves 256 rows, an activation stage 256 columns: twice the flops per operand byte of 0);
                      //    FP8 / INT8 keep one 128 x 256 tile's scaled accumulators in the registers of two drain warpgroups
     {128, 1, 4, 8},  // 6: B resident in device memory, 128-column items with a deep activation ring: the hardware-scaled kinds
@@ -105,8 +105,7 @@ cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
     case 4:
       if constexpr (KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 8, true>(grid, stream, ma, mb, ms, p);
       else return cudaErrorInvalidValue;
-    case 5:
-      return launch_one<KIND, 256, 1, 3, KindTraits<KIND>::sw_scale, 6>(grid, stream, ma, mb, ms, p);
+    case 5: return launch_one<KIND, 256, 1, 4, KindTraits<KIND>::sw_scale, 4>(grid, stream, ma, mb, ms, p);
     case 6:
       if constexpr (!KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 4, false, 8>(grid, stream, ma, mb, ms, p);
       else return cudaErrorInvalidValue;

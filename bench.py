@@ -51,7 +51,10 @@ ELEM_BYTES = {"fp8": 1.0, "bf16": 2.0, "int8": 1.0, "fp4": 0.5}
 # DRAM bytes (read + write) per padded row of A/D, from one ncu capture of a cut-down case of each workload with the
 # default tile configuration (dram__bytes_read.sum + dram__bytes_write.sum over the padded rows of that launch): HBM
 # traffic grows with the rows of the launch, not with the weights, which never touch HBM.
-NCU_DRAM_BYTES_PER_ROW = {"c3_fp8": 18.4e3}
+# (bytes, which rows): contiguous workloads scale with the padded rows of A / D, the masked one with its valid rows.
+# Captured cuts: c3_fp8 16 experts, c2_bf16 / c2b_bf16 / c4_fp4 32 experts, c1_int8 whole (its 25 MB of D stay in L2).
+NCU_DRAM_BYTES_PER_ROW = {"c3_fp8": (18.8e3, "padded"), "c2_bf16": (6.58e3, "padded"), "c2b_bf16": (3.47e3, "padded"),
+                          "c1_int8": (2.29e3, "padded"), "c4_fp4": (8.56e3, "valid")}
 
 
 def rows_per_expert(cfg, seed=0):
@@ -195,6 +198,7 @@ def build_masked_fp4(cfg, rank, world, device, seed=0):
     active = sum(1 for c in counts if c > 0)
     return dict(kind="fp4", a=a, sfa=sfa, b=b, sfb=sfb, d=torch.empty((g, stride, n), dtype=torch.bfloat16, device=device),
                 masked_m=torch.tensor(counts, dtype=torch.int32, device=device), counts=counts, g=g, n=n, k=k, m_total=g * stride,
+                valid_rows=valid,
                 # the weight scales are re-laid out once and then stay on the device, so only the packed values stream per call;
                 # host_bytes_with_scales is the figure that counts the (host-resident) scale bytes of the API tensors as well
                 flops=2.0 * n * k * valid, host_bytes=active * n * k * 0.5, host_bytes_with_scales=active * n * (k * 0.5 + k / 16.0),
@@ -1039,10 +1043,12 @@ def main():
             "roofline": {"bound": "host_link", "achieved": round(ach, 2), "peak": round(link_peak, 2), "unit": "GB/s",
                          "frac": round(ach / link_peak, 4),
                          "frac_of_peak_all_ranks_at_once": round(ach / link_peak_together, 4) if link_peak_together > 0 else None,
-                         "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload] * rank0_w["m_total"] / 1e9, 3)
+                         "traffic": (round(NCU_DRAM_BYTES_PER_ROW[args.workload][0]
+                                           * rank0_w["m_total" if NCU_DRAM_BYTES_PER_ROW[args.workload][1] == "padded" else "valid_rows"] / 1e9, 3)
                                      if args.workload in NCU_DRAM_BYTES_PER_ROW and not moe and args.weights == "host" else None),
-                         "traffic_unit": "GB of HBM traffic per launch: ncu dram bytes per padded row of a cut-down capture of this workload "
-                                         "x the padded rows of this launch (traffic grows with rows, not with the weights)",
+                         "traffic_unit": "GB of HBM traffic per launch: ncu dram bytes per row (padded rows; valid rows for the masked "
+                                         "layout) of a cut-down capture of this workload x the rows of this launch (traffic grows with "
+                                         "rows, not with the weights, which never touch HBM)",
                          "traffic_model": traffic_model,
                          "algorithmic_gb": round(rank0_w["host_bytes"] / 1e9, 3),
                          "note": "algorithmic bytes = each active expert's weights once (N*K*bytes); the kernel is bound by the PCIe "
