@@ -80,14 +80,26 @@ class PeerExchange:
             if self.world > 1:
                 handles: List[Optional[bytes]] = [None] * self.world
                 dist.all_gather_object(handles, bytes(handle), group=group)
+                failure = ""
                 for r in range(self.world):
                     if r == self.rank:
                         continue
                     peer = ctypes.c_void_p()
                     buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
-                    _lib.check(lib.ag_peer_open(buf, ctypes.byref(peer)))
+                    if lib.ag_peer_open(buf, ctypes.byref(peer)) != 0:
+                        failure = f"rank {self.rank} could not map rank {r}'s buffers: {_lib.last_error()}"
+                        break
                     self._opened.append(peer.value)
                     bases[r] = peer.value
+                # every rank learns whether every rank could map every buffer, so that all of them fail together
+                ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0:
+                    for p in self._opened:
+                        lib.ag_peer_close(p)
+                    lib.ag_peer_free(self._own)
+                    self._own = None
+                    raise RuntimeError(failure or "another rank could not map the exchange buffers (CUDA IPC between the GPUs of one node is needed)")
         self.peers = _lib.EpPeers()
         for r in range(self.world):
             self.peers.a[r] = bases[r] + self._offsets[0]

@@ -3,6 +3,10 @@ from .math import (  # noqa: F401
     ceil_div,
     ceil_to_ue8m0,
     per_block_cast_to_fp8,
+    per_channel_cast_to_fp8,
+    per_custom_dims_cast_to_fp8,
+    per_token_cast_to_fp4,
+    transpose_packed_fp4,
     per_channel_cast_to_int8,
     per_token_cast_to_fp8,
     per_token_cast_to_int8,

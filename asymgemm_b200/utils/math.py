@@ -1,8 +1,9 @@
 """Quantisers that define the scale formats the operators accept.
 
-Same formats as the reference's ``asym_gemm/utils/math.py`` (per_token_cast_to_fp8 :24-34,
-per_block_cast_to_fp8 :47-57, per_token_cast_to_int8 :60-74, per_token_cast_to_nvfp4_e4m3 :122-139), written
-independently: a tensor quantised by either implementation is accepted by the operators.
+Same formats as the reference's ``asym_gemm/utils/math.py`` (per_token_cast_to_fp8 :24-34, per_channel_cast_to_fp8 :37-45,
+per_block_cast_to_fp8 :47-57, per_token_cast_to_int8 :60-74, per_custom_dims_cast_to_fp8 :82-88, per_token_cast_to_fp4
+:103-119, per_token_cast_to_nvfp4_e4m3 :122-139, transpose_packed_fp4 :142-155), written independently: a tensor quantised
+by either implementation is accepted by the operators.
 """
 from __future__ import annotations
 
@@ -116,3 +117,50 @@ def per_token_cast_to_nvfp4_e4m3(x: torch.Tensor, gran_k: int = 16) -> Tuple[tor
     scaled = blocks * (1.0 / dec.unsqueeze(2))
     codes = encode_e2m1(scaled).view(rows, -1)
     return pack_e2m1(codes)[:, : cols // 2].contiguous(), sf
+
+
+def per_channel_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[M, N] with M % gran_k == 0 -> (e4m3 [M, N], fp32 scales [M/gran_k, N]): one scale per column per block of gran_k rows."""
+    assert x.dim() == 2 and x.shape[0] % gran_k == 0
+    rows, cols = x.shape
+    view = x.view(rows // gran_k, gran_k, cols)
+    sf = view.abs().float().amax(dim=1).clamp(1e-4) / FP8_MAX
+    if use_ue8m0:
+        sf = ceil_to_ue8m0(sf)
+    return (view * (1.0 / sf.unsqueeze(1))).to(torch.float8_e4m3fn).view(rows, cols), sf
+
+
+def per_custom_dims_cast_to_fp8(x: torch.Tensor, dims: Tuple[int, ...], use_ue8m0: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One scale per index along `dims` (amax over all other dimensions): (e4m3 like x, fp32 scales of the kept dims)."""
+    reduce_over = tuple(i for i in range(x.dim()) if i not in set(dims))
+    sf = x.abs().float().amax(dim=reduce_over, keepdim=True).clamp(1e-4) / FP8_MAX
+    if use_ue8m0:
+        sf = ceil_to_ue8m0(sf)
+    return (x * (1.0 / sf)).to(torch.float8_e4m3fn), sf.squeeze()
+
+
+def per_token_cast_to_fp4(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[M, K] -> (packed E2M1 uint8 [M, K/2], fp32 scales [M, ceil(K/gran_k)]); scale = amax/6 per row per K block,
+    optionally rounded up to a power of two."""
+    assert x.dim() == 2 and x.shape[1] % 2 == 0
+    rows, cols = x.shape
+    blocks = _pad_cols(x, gran_k).view(rows, -1, gran_k)
+    sf = blocks.abs().float().amax(dim=2).clamp_min(1e-4) / FP4_MAX
+    if use_ue8m0:
+        sf = ceil_to_ue8m0(sf)
+    codes = encode_e2m1(blocks * (1.0 / sf.unsqueeze(2))).view(rows, -1)
+    return pack_e2m1(codes)[:, : cols // 2].contiguous(), sf
+
+
+def unpack_e2m1(packed: torch.Tensor) -> torch.Tensor:
+    """[.., K/2] bytes -> [.., K] codes (low nibble = even index)."""
+    out = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), dtype=torch.uint8, device=packed.device)
+    out[..., 0::2] = packed & 0xF
+    out[..., 1::2] = (packed >> 4) & 0xF
+    return out
+
+
+def transpose_packed_fp4(a: torch.Tensor) -> torch.Tensor:
+    """Packed E2M1 [M, N/2] -> packed [N, M/2]: the transpose of the 4-bit matrix, re-packed along its new rows."""
+    assert a.dtype == torch.uint8 and a.dim() == 2 and a.shape[0] % 2 == 0
+    return pack_e2m1(unpack_e2m1(a).t().contiguous())

@@ -578,9 +578,16 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
         ag.check_status()
         nccl_ms = timed(step, steps, barrier)
         ag.check_status()
+    peer_layer, peer_error = None, None
     if args.exchange in ("peer", "both") and args.pipeline_groups <= 1:
-        peer_layer = ep.ExpertParallelMoE(cfg["experts"], cfg["hidden"], cfg["inter"], layer.w13, layer.w2, None, ranges, ue8m0_scales=ue,
-                                          exchange="peer", max_tokens=w["x"].shape[0], top_k=cfg["top_k"], fused_activation=w["fused"])
+        try:      # construction fails on every rank together or on none (ep_peer.PeerExchange)
+            peer_layer = ep.ExpertParallelMoE(cfg["experts"], cfg["hidden"], cfg["inter"], layer.w13, layer.w2, None, ranges, ue8m0_scales=ue,
+                                              exchange="peer", max_tokens=w["x"].shape[0], top_k=cfg["top_k"], fused_activation=w["fused"])
+        except RuntimeError as e:
+            peer_error = str(e)[:300]
+            if args.exchange == "peer":
+                raise
+    if peer_layer is not None:
         pstep = lambda: peer_layer.forward(w["x"], w["ids"], w["w"])
         for _ in range(2):
             y_peer = pstep()
@@ -655,6 +662,8 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
     }
     rec["activation"] = ("SiLU*mul fused into the gate+up GEMM's drain (weights stored with gate / up rows interleaved)" if w["fused"]
                          else "separate SiLU*mul + requantisation kernel")
+    if peer_error is not None:
+        rec["peer_exchange_unavailable"] = peer_error
     if peer_ms is not None:
         rec["exchange_ms_per_step"] = {"nccl": round(nccl_all, 3) if nccl_all is not None else None, "peer": round(peer_all, 3),
                                        "outputs_bit_equal": same}

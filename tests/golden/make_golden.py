@@ -93,13 +93,34 @@ def segments_table(rows):
     return np.array(offsets, np.int32), np.array(experts, np.int32), start, segs
 
 
+def extra_quantisers(M, x, w):
+    """The reference's remaining quantisers (asym_gemm/utils/math.py:37-45,82-88,103-119,142-155) on the shared inputs."""
+    xs = x[:256]                                    # per_channel_cast_to_fp8 wants rows % 128 == 0
+    out = {}
+    for tag, ue in (("f32", False), ("ue8m0", True)):
+        q, s = M.per_channel_cast_to_fp8(xs, use_ue8m0=ue)
+        out[f"chan_q_{tag}"], out[f"chan_s_{tag}"] = bits(q), s.numpy()
+        q, s = M.per_custom_dims_cast_to_fp8(w, (0, 2), use_ue8m0=ue)
+        out[f"dims_q_{tag}"], out[f"dims_s_{tag}"] = bits(q), s.numpy()
+        q, s = M.per_token_cast_to_fp4(xs, use_ue8m0=ue, gran_k=128)
+        out[f"fp4_q_{tag}"], out[f"fp4_s_{tag}"] = q.numpy(), s.numpy()
+    packed, _ = M.per_token_cast_to_fp4(xs, use_ue8m0=False, gran_k=128)
+    out["fp4_transposed"] = M.transpose_packed_fp4(packed).numpy()
+    np.savez_compressed(HERE / "quantisers_extra.npz", **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of bytedance-iaas/AsymGEMM (its quantisers and test-side "
                                                        "references are imported from there)")
+    ap.add_argument("--only-extra", action="store_true", help="write quantisers_extra.npz only (from the committed inputs.npz)")
     args = ap.parse_args()
     ref = Path(args.reference)
     M, numeric, fp4, int8 = _install_reference(ref)
+    if args.only_extra:
+        g0 = np.load(HERE / "inputs.npz")
+        extra_quantisers(M, torch.from_numpy(g0["x"].astype(np.float32)), torch.from_numpy(g0["w"].astype(np.float32)))
+        return
 
     torch.manual_seed(0)
     np.random.seed(0)
@@ -112,6 +133,7 @@ def main():
     w = (torch.randn((g, n, k)) * 0.02).half().float()
     common = dict(offsets=offsets, experts=experts, rows=np.array(rows, np.int32))
     np.savez_compressed(HERE / "inputs.npz", x=x.numpy().astype(np.float16), w=w.numpy().astype(np.float16), **common)
+    extra_quantisers(M, x, w)
 
     def per_seg(fn):
         out = torch.zeros((m_total, n), dtype=torch.float32)

@@ -53,6 +53,26 @@ def test_nvfp4_quantiser_matches_reference():
     assert (np.abs(deq - x.numpy()) <= scale * 1.0 + 1e-6).all()
 
 
+def test_remaining_quantisers_match_reference():
+    """per_channel_cast_to_fp8, per_custom_dims_cast_to_fp8, per_token_cast_to_fp4 and transpose_packed_fp4 against the
+    reference's outputs on the shared inputs (fixture written by tests/golden/make_golden.py from the reference's functions)."""
+    from asymgemm_b200.utils import per_channel_cast_to_fp8, per_custom_dims_cast_to_fp8, per_token_cast_to_fp4, transpose_packed_fp4
+    x, w = _inputs()
+    xs = x[:256]
+    g = np.load(GOLD / "quantisers_extra.npz")
+    for tag, ue in (("f32", False), ("ue8m0", True)):
+        q, s = per_channel_cast_to_fp8(xs, ue)
+        assert np.array_equal(q.view(torch.uint8).numpy(), g[f"chan_q_{tag}"]) and np.array_equal(s.numpy(), g[f"chan_s_{tag}"])
+        q, s = per_custom_dims_cast_to_fp8(w, (0, 2), ue)
+        assert np.array_equal(q.view(torch.uint8).numpy(), g[f"dims_q_{tag}"]) and np.array_equal(s.numpy(), g[f"dims_s_{tag}"])
+        q, s = per_token_cast_to_fp4(xs, ue, 128)
+        assert np.array_equal(q.numpy(), g[f"fp4_q_{tag}"]) and np.array_equal(s.numpy(), g[f"fp4_s_{tag}"])
+    packed, _ = per_token_cast_to_fp4(xs, False, 128)
+    t = transpose_packed_fp4(packed)
+    assert np.array_equal(t.numpy(), g["fp4_transposed"])
+    assert torch.equal(transpose_packed_fp4(t), packed)          # an involution on even-sized matrices
+
+
 def test_contiguous_layout_builder():
     off, exp, list_size, total, segs = build_contiguous_layout([130, 0, 1, 256], device="cpu")
     assert off.tolist() == [0, 256, 256, 384, 384, 640]
