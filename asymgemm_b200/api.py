@@ -537,17 +537,37 @@ def _fp4_blocked(sf: torch.Tensor, groups: int, rows: int, k16: int, device: tor
     return out
 
 
+def _fp4_expand_scales(sf: torch.Tensor, rows: int, k16: int, gran_mn: int, gran_k: int, device: torch.device, what: str) -> torch.Tensor:
+    """Scales given at a coarser granularity than one per row and 16 elements are replicated to that granularity, as the
+    reference does before its kernel (csrc/apis/gemm.hpp:271-297): [.., rows/gran_mn, k/gran_k] -> [.., rows, k/16]."""
+    rep_k = gran_k // 16
+    want = (-(-rows // gran_mn), -(-(k16 * 16) // gran_k))
+    _require(tuple(sf.shape[-2:]) == want, f"{what} must end in {want} for this recipe, got {tuple(sf.shape[-2:])}")
+    out = (sf if sf.is_cuda else sf.to(device)).view(torch.uint8)
+    if rep_k > 1:
+        out = out.repeat_interleave(rep_k, dim=-1)[..., :k16]
+    if gran_mn > 1:
+        out = out.repeat_interleave(gran_mn, dim=-2)[..., :rows, :]
+    return out.contiguous().view(torch.float8_e4m3fn)
+
+
 def _fp4_prepare(a, b, d, masked: bool, recipe):
+    """Checks of the NVFP4 operators. Returns (g, m, n, k, k16, sfa, sfb) with both scale tensors at one scale per row and
+    16 elements: recipe (1, 1, 16) passes them through, a coarser recipe (gran_mn_a, gran_mn_b, gran_k), gran_k a multiple
+    of 16, replicates them first."""
     a_q, sfa = a
     b_q, sfb = b
     g, m, n, k = _common_checks(a_q, b_q, d, masked=masked, k_div=2)
     _require(a_q.dtype == torch.uint8 and b_q.dtype == torch.uint8, "a and b must be packed E2M1 in uint8 (two values per byte)")
-    if recipe is not None:
-        _require(tuple(recipe) == (1, 1, 16), f"Unknown SF transformation for recipe {tuple(recipe)}")
     for t in (sfa, sfb):
         _require(t.dtype in (torch.float8_e4m3fn, torch.uint8), "NVFP4 scales must be float8_e4m3fn (or their uint8 bytes)")
     _require(k % 32 == 0, "k must be a multiple of 32")
     k16 = k // 16
+    gm_a, gm_b, gk = (1, 1, 16) if recipe is None else tuple(int(v) for v in recipe)
+    _require(gm_a >= 1 and gm_b >= 1 and gk >= 16 and gk % 16 == 0, f"Unknown SF transformation for recipe {tuple(recipe) if recipe else None}")
+    if (gm_a, gm_b, gk) != (1, 1, 16):
+        sfa = _fp4_expand_scales(sfa, m, k16, gm_a, gk, a_q.device, "sfa")
+        sfb = _fp4_expand_scales(sfb, n, k16, gm_b, gk, a_q.device, "sfb")
     rows_shape = (g, m) if masked else (m,)
     _require(tuple(sfa.shape) == (*rows_shape, k16), f"sfa must be {(*rows_shape, k16)}, got {tuple(sfa.shape)}")
     _require(tuple(sfb.shape) == (g, n, k16), f"sfb must be {(g, n, k16)}, got {tuple(sfb.shape)}")
@@ -555,7 +575,7 @@ def _fp4_prepare(a, b, d, masked: bool, recipe):
     _require(sfb.is_contiguous() and (sfb.is_cuda or sfb.is_pinned()), "sfb must be contiguous and on CUDA or pinned")
     if masked:
         _require(m % 128 == 0, "masked NVFP4 needs M_max to be a multiple of 128")
-    return g, m, n, k, k16
+    return g, m, n, k, k16, sfa, sfb
 
 
 def m_grouped_fp4_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=None, recipe=None, compiled_dims: str = "nk",
@@ -565,13 +585,13 @@ def m_grouped_fp4_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=N
     ``alpha`` (extension): product of the tensor-level fp32 scales, applied to the fp32 accumulator before rounding.
     Every segment must start on a multiple of 128 rows (the contiguous layout's alignment).
     """
-    g, m, n, k, k16 = _fp4_prepare(a, b, d, False, recipe)
+    g, m, n, k, k16, sfa, sfb = _fp4_prepare(a, b, d, False, recipe)
     _check_index_tensors(offsets, experts, g)
     if m == 0:
         return
     dev = a[0].device
-    sfa_b = _fp4_blocked(a[1], 1, m, k16, dev, cache=False)
-    sfb_b = _fp4_blocked(b[1], g, n, k16, dev, cache=True)
+    sfa_b = _fp4_blocked(sfa, 1, m, k16, dev, cache=False)
+    sfb_b = _fp4_blocked(sfb, g, n, k16, dev, cache=sfb is b[1])
     segs = _list_size_to_segments(list_size, offsets, experts)
     _launch(_lib.KIND_NVFP4, "ag_m_grouped_fp4_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
             offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, alpha=alpha)
@@ -580,13 +600,13 @@ def m_grouped_fp4_asym_gemm_nt_contiguous(a, b, d, offsets, experts, list_size=N
 def m_grouped_fp4_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk",
                                       disable_ue8m0_cast: bool = True, *, alpha: float = 1.0) -> None:
     """Masked NVFP4 (csrc/apis/gemm.hpp:302-365)."""
-    g, m, n, k, k16 = _fp4_prepare(a, b, d, True, recipe)
+    g, m, n, k, k16, sfa, sfb = _fp4_prepare(a, b, d, True, recipe)
     _require(masked_m.is_cuda and masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == g,
              "masked_m must be a contiguous int32 CUDA tensor with one entry per group")
     if m == 0 or expected_m == 0:
         return
     dev = a[0].device
-    sfa_b = _fp4_blocked(a[1], 1, g * m, k16, dev, cache=False)
-    sfb_b = _fp4_blocked(b[1], g, n, k16, dev, cache=True)
+    sfa_b = _fp4_blocked(sfa, 1, g * m, k16, dev, cache=False)
+    sfb_b = _fp4_blocked(sfb, g, n, k16, dev, cache=sfb is b[1])
     _launch(_lib.KIND_NVFP4, "ag_m_grouped_fp4_gemm_nt", layout=_lib.LAYOUT_MASKED, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b, d=d,
             masked_m=masked_m, m=m, n=n, k=k, g=g, rows_hint=int(expected_m) * g, alpha=alpha)

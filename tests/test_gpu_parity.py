@@ -395,6 +395,30 @@ def test_fp8_fused_silu_mul_epilogue_equals_gemm_plus_activation_kernel(tile, b_
                                                  c2["offsets"], c2["experts"], c2["list_size"], epilogue="silu_mul")
 
 
+def test_nvfp4_coarser_scale_recipe_is_replicated():
+    """Recipe (1, 1, 32): one E4M3 scale per 32 elements. The operator replicates every scale over its two 16-element
+    groups (the reference does the same before its kernel, csrc/apis/gemm.hpp:271-275), so the result equals the
+    (1, 1, 16) call on the replicated scale tensors bit for bit."""
+    c = H.make_contiguous_case("fp4", [200, 0, 130], 256, 512, seed=81)
+    sfa32 = c["sfa"].view(torch.uint8)[:, 0::2].contiguous().view(torch.float8_e4m3fn)            # keep every other scale
+    sfb32 = H.pin(c["sfb"].view(torch.uint8)[:, :, 0::2].contiguous()).view(torch.float8_e4m3fn)
+    sfa16 = sfa32.view(torch.uint8).repeat_interleave(2, dim=-1).contiguous().view(torch.float8_e4m3fn)
+    sfb16 = H.pin(sfb32.view(torch.uint8).repeat_interleave(2, dim=-1).contiguous()).view(torch.float8_e4m3fn)
+    d32 = torch.zeros((c["m_total"], 256), dtype=torch.bfloat16, device="cuda")
+    d16 = torch.zeros_like(d32)
+    ag.m_grouped_fp4_asym_gemm_nt_contiguous((c["a"], sfa32), (c["b"], sfb32), d32, c["offsets"], c["experts"], c["list_size"],
+                                             recipe=(1, 1, 32), disable_ue8m0_cast=True)
+    ag.m_grouped_fp4_asym_gemm_nt_contiguous((c["a"], sfa16), (c["b"], sfb16), d16, c["offsets"], c["experts"], c["list_size"],
+                                             recipe=(1, 1, 16), disable_ue8m0_cast=True)
+    torch.cuda.synchronize()
+    assert torch.equal(d32.view(torch.int16), d16.view(torch.int16)) and d16.abs().sum() > 0
+    ref = oracle.gemm_nvfp4(c["a"].cpu().numpy(), H.np_bits(sfa16), c["b"].numpy(), H.np_bits(sfb16), c["segments"])
+    _check("fp4", d32.float().cpu().numpy(), ref, c["segments"])
+    with pytest.raises(RuntimeError, match="Unknown SF transformation"):
+        ag.m_grouped_fp4_asym_gemm_nt_contiguous((c["a"], sfa32), (c["b"], sfb32), d32, c["offsets"], c["experts"], c["list_size"],
+                                                 recipe=(1, 1, 24))
+
+
 def test_c_abi_error_surfaces_as_runtime_error_through_the_operator():
     """A descriptor the library refuses (a tile configuration that does not exist for the operand kind) comes back as the
     RuntimeError the reference API raises, with the library's message, and leaves the context usable."""
