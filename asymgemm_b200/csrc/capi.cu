@@ -131,6 +131,7 @@ struct LaunchPlan {
   int n_tiles = 0, kb_count = 0;
   int split_rows = 0;        // > 0: device-resident b, segments are cut into chunks of this many rows (no item ever replays)
   int grid = 0;
+  int b_box_rows = 0;        // weight rows one TMA load brings (half a tile for the pair kernel)
   uint64_t kpad = 0;         // bytes of one scratch row: K bytes padded to whole weight stages
   uint64_t scratch_need = 0; // 0 = this launch has no use for scratch
 };
@@ -151,6 +152,12 @@ int plan_launch(int kind, const ag_gemm_desc_t* g, bool host_b, LaunchPlan* out)
     if (kind == 3) AG_REQUIRE(g->k % 32 == 0, "nvfp4 needs k to be a multiple of 32 (got %lld)", static_cast<long long>(g->k));
     if (masked) AG_REQUIRE(g->m % 128 == 0, "block-scaled masked layout needs M_max to be a multiple of 128 (got %lld)", static_cast<long long>(g->m));
   }
+  const bool pair = pl.tile == agb::kTileDevicePair;
+  if (pair) {
+    AG_REQUIRE(!host_b, "tile_config %d (CTA pairs) is for b resident in device memory", pl.tile + 1);
+    AG_REQUIRE(!g->no_split, "tile_config %d (CTA pairs) always splits long segments into row chunks; no_split cannot be combined with it", pl.tile + 1);
+    AG_REQUIRE(grid_cap >= 2, "tile_config %d (CTA pairs) needs at least two SMs", pl.tile + 1);
+  }
   const agb::TileConfig tc = agb::tile_config_of(kind, pl.tile);
   pl.bn = tc.bn;
   pl.ka = tc.ka;
@@ -162,7 +169,15 @@ int plan_launch(int kind, const ag_gemm_desc_t* g, bool host_b, LaunchPlan* out)
   const long long segments = masked ? g->num_groups : g->max_segments;
   const long long seg_items = pl.split_rows > 0 ? rows_total / pl.split_rows + segments : segments;
   const long long items = seg_items * pl.n_tiles;
-  pl.grid = static_cast<int>(items < grid_cap ? items : grid_cap);
+  AG_REQUIRE(items < (1LL << 31), "the problem has %lld work items; the kernels index them with 32 bits", items);
+  if (pair) {   // items are taken by pairs of CTAs
+    const long long pairs = items < grid_cap / 2 ? items : grid_cap / 2;
+    pl.grid = static_cast<int>(2 * pairs);
+    pl.b_box_rows = pl.bn / 2;
+  } else {
+    pl.grid = static_cast<int>(items < grid_cap ? items : grid_cap);
+    pl.b_box_rows = pl.bn;
+  }
   if (pl.grid < 0) pl.grid = 0;
   pl.kpad = static_cast<uint64_t>((pl.kb_count + pl.ka - 1) / pl.ka) * pl.ka * 128;
   pl.scratch_need = pl.split_rows > 0 ? 0 : static_cast<uint64_t>(pl.grid) * pl.bn * pl.kpad;
@@ -263,7 +278,7 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
 
   CUtensorMap ma, mb, ms;
   if (int rc = encode_bytes_2d(&ma, g->a, kbytes, static_cast<uint64_t>(rows_total), kbytes, 128, "a")) return rc;
-  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * b_groups, kbytes, bn, "b")) return rc;
+  if (int rc = encode_bytes_2d(&mb, b_dev, kbytes, static_cast<uint64_t>(g->n) * b_groups, kbytes, plan.b_box_rows, "b")) return rc;
   if (p.use_scratch) {
     if (int rc = encode_bytes_2d(&ms, g->scratch, kpad, static_cast<uint64_t>(grid) * bn, kpad, bn, "scratch")) return rc;
   } else {

@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include "mgrouped_kernel.cuh"
+#include "mgrouped_pair_kernel.cuh"
 
 namespace agb {
 
@@ -15,7 +16,7 @@ constexpr bool kind_is_sw_scaled(int kind) { return kind == 1 || kind == 2; }
 struct TileConfig {
   int bn, ka, sb, sa;
 };
-constexpr int kNumTileConfigs = 7;
+constexpr int kNumTileConfigs = 8;
 constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
     {128, 1, 8, 4},  // 0: B resident in device memory, 128-column items
     {32, 4, 8, 4},   // 1: B streamed from host memory, fewest host pages in flight per CTA
@@ -27,13 +28,17 @@ constexpr TileConfig kTileConfigs[kNumTileConfigs] = {
                      //    FP8 / INT8 keep one 128 x 256 tile's scaled accumulators in the registers of two drain warpgroups
     {128, 1, 4, 8},  // 6: B resident in device memory, 128-column items with a deep activation ring: the hardware-scaled kinds
                      //    keep three row tiles per weight stage, so one K step consumes three activation stages
+    {256, 1, 6, 6},  // 7: B resident in device memory, 256-column items on PAIRS of CTAs (mgrouped_pair_kernel.cuh): each SM loads
+                     //    half of the weight tile and the tensor cores read both halves; BF16, FP8 (fp32 scales) and INT8
 };
 constexpr int kTileDeviceRegAcc = 4;
 constexpr int kTileDeviceWide = 5;
 constexpr int kTileDeviceDeepA = 6;
+constexpr int kTileDevicePair = 7;
 constexpr bool tile_reg_acc(int kind, int tile) { return kind_is_sw_scaled(kind) && (tile == kTileDeviceRegAcc || tile == kTileDeviceWide); }
 // rows of one accumulator chunk (what one item covers when long segments are split)
 constexpr int chunk_tiles_of(int kind, int tile, int bn) {
+  if (tile == kTileDevicePair) return kind_is_sw_scaled(kind) ? 2 : 4;   // 256 rows per pair and accumulator
   return kind_is_block_scaled(kind) ? (512 - 64) / bn : (kind_is_sw_scaled(kind) ? (tile_reg_acc(kind, tile) ? 1 : 512 / bn - 2) : 512 / bn);
 }
 // NVFP4 also stages 2 KB of scale factors per K atom and operand, so its host-streaming configuration uses
@@ -47,11 +52,11 @@ constexpr bool tile_supported(int kind, int tile) {
   if (tile < 0 || tile >= kNumTileConfigs) return false;
   if (kind_is_block_scaled(kind)) return tile == 0 || tile == 3 || tile == kTileDeviceDeepA;   // 128 or 64 columns per item
   if (kind_is_sw_scaled(kind)) return tile != kTileDeviceDeepA;
-  return tile != kTileDeviceRegAcc;
+  return tile != kTileDeviceRegAcc;   // the pair kernel (8) exists for every kind that is not block-scaled
 }
 inline const char* tile_support_text(int kind) {
   return kind_is_block_scaled(kind) ? "hardware block-scaled kinds have tile_config 1, 4 and 7"
-         : kind_is_sw_scaled(kind) ? "fp8 and int8 have tile_config 1 .. 6" : "bf16 has tile_config 1 .. 4, 6 and 7";
+         : kind_is_sw_scaled(kind) ? "fp8 and int8 have tile_config 1 .. 6 and 8" : "bf16 has tile_config 1 .. 4 and 6 .. 8";
 }
 // Configuration chosen when the caller does not force one.
 // Device-resident weights take 256-column items where the kind has them and N is wide enough to fill one
@@ -95,6 +100,27 @@ cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, con
   return cudaGetLastError();
 }
 
+// The pair kernel: `grid` counts CTAs and is even; clusters of two are a compile-time attribute of the kernel.
+template <Kind KIND>
+cudaError_t launch_pair(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p) {
+  constexpr int SA = KindTraits<KIND>::sw_scale ? 6 : 8, SB = KindTraits<KIND>::sw_scale ? 6 : 4;
+  using L = PairSmem<SA, SB>;
+  static_assert(L::dyn_bytes <= 232448, "pair configuration does not fit in shared memory");
+  auto kernel = mgrouped_pair_kernel<KIND, SA, SB>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::dyn_bytes);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  if (grid < 2 || (grid & 1)) return cudaErrorInvalidValue;
+  kernel<<<grid, PAIR_THREADS, L::dyn_bytes, stream>>>(ma, mb, p);
+  return cudaGetLastError();
+}
+
 template <Kind KIND>
 cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
   switch (tile) {
@@ -108,6 +134,9 @@ cudaError_t launch_kind_impl(AGB_LAUNCH_ARGS) {
     case 5: return launch_one<KIND, 256, 1, 4, KindTraits<KIND>::sw_scale, 4>(grid, stream, ma, mb, ms, p);
     case 6:
       if constexpr (!KindTraits<KIND>::sw_scale) return launch_one<KIND, 128, 1, 4, false, 8>(grid, stream, ma, mb, ms, p);
+      else return cudaErrorInvalidValue;
+    case 7:
+      if constexpr (!KindTraits<KIND>::block_scaled) return launch_pair<KIND>(grid, stream, ma, mb, p);
       else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }

@@ -97,31 +97,154 @@ struct Item {
   int nt;
 };
 
-// Row range and weight index of segment `seg`. Returns 0 past the end of the segment list.
-__device__ __forceinline__ int read_segment(const GemmParams& p, int seg, int& expert, int& row0, int& rows) {
-  if (seg >= p.max_segments) return 0;
+// ----------------------------------------------------------------------------- work list of a CTA
+// Which (segment, row chunk, n-tile) items a CTA works on follows from the segment list in device memory. Every role of the
+// CTA needs that sequence, and the roles that matter are single threads whose every instruction is on the critical path of
+// the tensor core: walking the segment list there (dependent loads, divisions) cost a quarter of the run time with 128
+// segments. So all threads of the CTA build the list once, in shared memory, before the roles start:
+//   1. the raw segment entries are copied in (3 ints per segment: contiguous = expert, row begin, row end; masked = rows),
+//   2. one warp turns the items per segment into running sums,
+//   3. thread i finds item `first + i * stride` by bisection in the sums and writes {expert, row0, rows, n-tile}.
+// A role then reads one int4 per item. Lists longer than the table, or segment lists longer than the cache, fall back
+// to the walk (fetch_item), which enumerates the items in exactly the same order.
+struct SegCache {
+  const int* data = nullptr;
+  int count = 0;
+};
+
+struct WorkList {
+  const int4* items = nullptr;   // {expert, row0, rows, n-tile}; rows < 0 ends the list
+  int count = 0;                 // entries built; beyond them the roles walk the segment list
+  long long first = 0, stride = 1;   // this CTA's i-th item is item `first + i * stride` of the launch
+  SegCache segs;
+};
+
+// Expert, first row and row count of a segment from its raw entry. `report`: flag an expert index outside B.
+__device__ __forceinline__ void decode_segment(const GemmParams& p, int seg, int raw0, int raw1, int raw2, bool report, int& expert, int& row0,
+                                               int& rows) {
   if (p.layout == LAYOUT_MASKED) {
     expert = seg;
     row0 = seg * p.m_max;
-    const int r = __ldg(p.masked_m + seg);
-    rows = r < 0 ? 0 : (r > p.m_max ? p.m_max : r);
+    rows = raw0 < 0 ? 0 : (raw0 > p.m_max ? p.m_max : raw0);
     if (static_cast<unsigned>(seg - p.expert_lo) >= static_cast<unsigned>(p.expert_n)) rows = 0;  // another launch's expert
   } else {
-    const int e = __ldg(p.experts + seg);
-    if (e < 0) return 0;
-    expert = e;
-    int r0 = __ldg(p.offsets + 2 * seg), r1 = __ldg(p.offsets + 2 * seg + 1);
+    expert = raw0;
+    int r0 = raw1, r1 = raw2;
     if (r0 < 0) r0 = 0;
     if (r1 > p.rows_total) r1 = static_cast<int>(p.rows_total);
     row0 = r0;
     rows = r1 > r0 ? r1 - r0 : 0;
-    if (e >= p.num_groups) {  // would read outside B: flag it and skip
-      atomicCAS(p.status, 0, ST_BAD_EXPERT | (static_cast<int>(blockIdx.x) << 8));
+    if (raw0 >= p.num_groups) {  // would read outside B: flag it and skip
+      if (report) atomicCAS(p.status, 0, ST_BAD_EXPERT | (static_cast<int>(blockIdx.x) << 8));
       rows = 0;
-    } else if (static_cast<unsigned>(e - p.expert_lo) >= static_cast<unsigned>(p.expert_n)) {
+    } else if (static_cast<unsigned>(raw0 - p.expert_lo) >= static_cast<unsigned>(p.expert_n)) {
       rows = 0;  // another launch's expert
     }
   }
+}
+
+// Items of a segment with `rows` valid rows: its row chunks x n-tiles when segments are split, one per n-tile otherwise.
+__device__ __forceinline__ int items_of_segment(const GemmParams& p, int rows) {
+  return p.split_rows > 0 ? ((rows + p.split_rows - 1) / p.split_rows) * p.n_tiles : p.n_tiles;
+}
+
+// Called by every thread of the CTA, before the first __syncthreads() that precedes the roles. `seg_data` holds
+// 3 * SEG_CAP ints, `seg_first` SEG_CAP + 2 ints (the last one is scratch), `items` ITEM_CAP entries.
+template <int SEG_CAP, int ITEM_CAP>
+__device__ __forceinline__ WorkList build_work_list(const GemmParams& p, int* seg_data, int* seg_first, int4* items, long long first,
+                                                    long long stride) {
+  WorkList wl;
+  wl.first = first;
+  wl.stride = stride;
+  if constexpr (SEG_CAP == 0 || ITEM_CAP == 0) return wl;
+  const int cached = min(p.max_segments, SEG_CAP);
+  int* list_end = seg_first + SEG_CAP + 1;           // index of the first negative expert (contiguous layout)
+  if (threadIdx.x == 0) *list_end = cached;
+  __syncthreads();
+  for (int seg = threadIdx.x; seg < cached; seg += blockDim.x) {
+    if (p.layout == LAYOUT_MASKED) {
+      seg_data[3 * seg] = __ldg(p.masked_m + seg);
+    } else {
+      const int e = __ldg(p.experts + seg);
+      seg_data[3 * seg] = e;
+      seg_data[3 * seg + 1] = __ldg(p.offsets + 2 * seg);
+      seg_data[3 * seg + 2] = __ldg(p.offsets + 2 * seg + 1);
+      if (e < 0) atomicMin(list_end, seg);
+    }
+  }
+  wl.segs.data = seg_data;
+  wl.segs.count = cached;
+  __syncthreads();
+  if (p.max_segments > SEG_CAP) return wl;           // the whole list does not fit: every role walks it
+  const int nseg = *list_end;
+  for (int seg = threadIdx.x; seg < nseg; seg += blockDim.x) {
+    int expert, row0, rows;
+    decode_segment(p, seg, seg_data[3 * seg], seg_data[3 * seg + 1], seg_data[3 * seg + 2], true, expert, row0, rows);
+    seg_first[seg] = items_of_segment(p, rows);
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {                            // exclusive running sums, 32 segments per step
+    int carry = 0;
+    for (int base = 0; base < nseg; base += 32) {
+      const int seg = base + static_cast<int>(threadIdx.x);
+      const int v = seg < nseg ? seg_first[seg] : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (static_cast<int>(threadIdx.x) >= d) incl += up;
+      }
+      if (seg < nseg) seg_first[seg] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (threadIdx.x == 0) seg_first[nseg] = carry;
+  }
+  __syncthreads();
+  const long long total = seg_first[nseg];
+  for (int i = threadIdx.x; i < ITEM_CAP; i += blockDim.x) {
+    const long long id = first + static_cast<long long>(i) * stride;
+    int4 v = make_int4(0, 0, -1, 0);
+    if (id < total) {
+      int lo = 0, hi = nseg;                         // the last segment whose first item is <= id
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_first[mid] <= id) lo = mid; else hi = mid;
+      }
+      int expert, row0, rows;
+      decode_segment(p, lo, seg_data[3 * lo], seg_data[3 * lo + 1], seg_data[3 * lo + 2], false, expert, row0, rows);
+      const int local = static_cast<int>(id - seg_first[lo]);
+      const int chunk = p.split_rows > 0 ? local / p.n_tiles : 0;
+      v.x = expert;
+      v.w = local - chunk * p.n_tiles;
+      v.y = row0 + chunk * p.split_rows;
+      v.z = p.split_rows > 0 ? min(p.split_rows, rows - chunk * p.split_rows) : rows;
+    }
+    items[i] = v;
+  }
+  wl.items = items;
+  wl.count = ITEM_CAP;
+  return wl;                                         // the caller's __syncthreads() publishes the table
+}
+
+// Row range and weight index of segment `seg`. Returns 0 past the end of the segment list.
+__device__ __forceinline__ int read_segment(const GemmParams& p, const SegCache& sc, int seg, int& expert, int& row0, int& rows) {
+  if (seg >= p.max_segments) return 0;
+  int raw0, raw1 = 0, raw2 = 0;
+  if (seg < sc.count) {
+    raw0 = sc.data[3 * seg];
+    raw1 = sc.data[3 * seg + 1];
+    raw2 = sc.data[3 * seg + 2];
+  } else if (p.layout == LAYOUT_MASKED) {
+    raw0 = __ldg(p.masked_m + seg);
+  } else {
+    raw0 = __ldg(p.experts + seg);
+    if (raw0 >= 0) {
+      raw1 = __ldg(p.offsets + 2 * seg);
+      raw2 = __ldg(p.offsets + 2 * seg + 1);
+    }
+  }
+  if (p.layout != LAYOUT_MASKED && raw0 < 0) return 0;
+  decode_segment(p, seg, raw0, raw1, raw2, true, expert, row0, rows);
   return 1;
 }
 
@@ -129,6 +252,9 @@ __device__ __forceinline__ int read_segment(const GemmParams& p, int seg, int& e
 struct ItemCursor {
   int seg = 0;
   long long first = 0;  // index of the first item of segment `seg`
+  SegCache cache;       // where the first segments' entries can be read from shared memory
+  __device__ ItemCursor() {}
+  __device__ explicit ItemCursor(const SegCache& c) : cache(c) {}
 };
 
 // Maps item index -> work. Returns 0 when the CTA has run out of work, 1 otherwise (rows may still be 0: skip).
@@ -140,14 +266,14 @@ __device__ __forceinline__ int fetch_item(const GemmParams& p, long long item, I
   if (p.split_rows <= 0) {
     const int seg = static_cast<int>(item / p.n_tiles);
     it.nt = static_cast<int>(item - static_cast<long long>(seg) * p.n_tiles);
-    return read_segment(p, seg, it.expert, it.row0, it.rows);
+    return read_segment(p, cur.cache, seg, it.expert, it.row0, it.rows);
   }
   while (true) {
     int expert, row0, rows;
-    if (!read_segment(p, cur.seg, expert, row0, rows)) return 0;
-    const long long chunks = (rows + p.split_rows - 1) / p.split_rows;
+    if (!read_segment(p, cur.cache, cur.seg, expert, row0, rows)) return 0;
+    const long long count = items_of_segment(p, rows);
     const long long local = item - cur.first;
-    if (local < chunks * p.n_tiles) {
+    if (local < count) {
       const int chunk = static_cast<int>(local / p.n_tiles);
       it.nt = static_cast<int>(local - static_cast<long long>(chunk) * p.n_tiles);
       it.expert = expert;
@@ -155,9 +281,23 @@ __device__ __forceinline__ int fetch_item(const GemmParams& p, long long item, I
       it.rows = min(p.split_rows, rows - chunk * p.split_rows);
       return 1;
     }
-    cur.first += chunks * p.n_tiles;
+    cur.first += count;
     ++cur.seg;
   }
+}
+
+// The i-th item of this CTA: from the table where it reaches, from the walk beyond it.
+__device__ __forceinline__ int get_item(const GemmParams& p, const WorkList& wl, int i, ItemCursor& cur, Item& it) {
+  if (i < wl.count) {
+    const int4 v = wl.items[i];
+    if (v.z < 0) return 0;
+    it.expert = v.x;
+    it.row0 = v.y;
+    it.rows = v.z;
+    it.nt = v.w;
+    return 1;
+  }
+  return fetch_item(p, wl.first + static_cast<long long>(i) * wl.stride, cur, it);
 }
 
 struct WaitCtx {
@@ -246,6 +386,8 @@ struct SfStage {
   static constexpr int b = KIND == Kind::NVFP4 ? SF_ATOM_BYTES * KA : (KIND == Kind::FP8_UE8M0 ? SF_BLOCK_BYTES : 0);
 };
 
+constexpr int work_list_bytes(int segs, int items) { return segs * 12 + (segs + 2) * 4 + 16 + items * 16; }
+
 template <int BN, int KA, int SA, int SB, int SFA_BYTES = 0, int SFB_BYTES = 0>
 struct SmemLayout {
   static constexpr int a_stage = BM * ATOM_BYTES;
@@ -261,7 +403,14 @@ struct SmemLayout {
   static constexpr int num_bars = 2 * SA + 2 * SB + 32 + 1;
   static constexpr int sfb_off = bar_off + num_bars * 8;          // 4 warps x BN floats (INT8 column scales)
   static constexpr int misc_off = sfb_off + 4 * BN * 4;           // tmem base, abort flag
-  static constexpr int total = misc_off + 16;
+  // work list (build_work_list): as large as what is left of the 227 KB allows
+  static constexpr int work_off = misc_off + 16;
+  static constexpr int work_room = 232448 - 1024 - work_off;
+  static constexpr int seg_cap = work_room >= work_list_bytes(1024, 512) ? 1024 : (work_room >= work_list_bytes(256, 128) ? 256 : 0);
+  static constexpr int item_cap = seg_cap / 2;
+  static constexpr int seg_first_off = work_off + seg_cap * 12;
+  static constexpr int items_off = (seg_first_off + (seg_cap + 2) * 4 + 15) / 16 * 16;
+  static constexpr int total = items_off + item_cap * 16;
   static constexpr int dyn_bytes = total + 1024;                  // slack for manual 1024-byte alignment
 };
 
@@ -396,6 +545,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     prefetch_tmap(&tmap_b);
     prefetch_tmap(&tmap_s);
   }
+  const WorkList work = build_work_list<L::seg_cap, L::item_cap>(p, reinterpret_cast<int*>(smem + L::work_off), reinterpret_cast<int*>(smem + L::seg_first_off),
+                                                                reinterpret_cast<int4*>(smem + L::items_off), blockIdx.x, gridDim.x);
   if (warp == 2) {
     tmem_alloc(tmem_base_smem, TMEM_COLS);
     tmem_relinquish();
@@ -414,11 +565,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t jt = 0;  // stage uses so far
       bool ok = true;
-      ItemCursor cursor;
+      ItemCursor cursor(work.segs);
       const uint64_t pol_stream = l2_policy_evict_first();
-      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+      for (int wi = 0; ok; ++wi) {
         Item it;
-        if (!fetch_item(p, item, cursor, it)) break;
+        if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         const int chunks = (mtiles + CHUNK_TILES - 1) / CHUNK_TILES;
@@ -491,10 +642,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t it_a = 0;
       bool ok = true;
-      ItemCursor cursor;
-      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+      ItemCursor cursor(work.segs);
+      for (int wi = 0; ok; ++wi) {
         Item it;
-        if (!fetch_item(p, item, cursor, it)) break;
+        if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
@@ -526,10 +677,17 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (lane == 0) {
       uint32_t it_a = 0, jt = 0, rt = 0, slot_phase = 0;
       bool ok = true;
-      ItemCursor cursor;
-      for (long long item = blockIdx.x; ok; item += gridDim.x) {
+      ItemCursor cursor(work.segs);
+      // One thread issues everything the tensor core does, and every instruction of it (barrier test, MMA, commit) costs
+      // this thread tens of cycles. So the loop keeps them few: the barriers of the NEXT step are tested (non-blocking)
+      // before the MMAs of this step are issued, which hides their round trip, and the operand descriptors are the
+      // descriptor of stage 0 plus an offset in its address field.
+      const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
+      const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
+      bool a_seen = false, b_seen = false, r_seen = false;   // "the barrier of the coming step was already complete"
+      for (int wi = 0; ok; ++wi) {
         Item it;
-        if (!fetch_item(p, item, cursor, it)) break;
+        if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
         for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
@@ -537,25 +695,33 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             const uint32_t sb = jt % SB;
             const int bx = kb % KA;
-            if (bx == 0) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+            if (bx == 0) {
+              if (!b_seen) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+              b_seen = false;
+            }
             if (!ok) break;
-            const uint32_t b_addr = smem_u32(smem_b + sb * L::b_stage + bx * L::b_box);
+            const bool b_last_use = bx == KA - 1 || kb == kb_count - 1;   // the stage is released after this K atom
+            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage + bx * L::b_box) >> 4);
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
               const uint32_t sa = it_a % SA;
-              ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
+              if (!a_seen) ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
               if (!ok) break;
               uint32_t d_col;
               if constexpr (T::sw_scale) {
                 const uint32_t rs = rt % RAW_SLOTS;
-                ok = wait_bar(&tm_empty[rs], ((rt / RAW_SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                if (!r_seen) ok = wait_bar(&tm_empty[rs], ((rt / RAW_SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
                 d_col = (RAW_SLOT0 + rs) * BN;
               } else {
                 if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
                 d_col = mt * BN;
               }
               if (!ok) break;
+              // a look at the next step's barriers; the answers are needed only after this step's MMAs are on their way
+              a_seen = mbar_test_wait(&a_full[(it_a + 1) % SA], ((it_a + 1) / SA) & 1);
+              if (mt == mc - 1 && b_last_use) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);
+              if constexpr (T::sw_scale) r_seen = mbar_test_wait(&tm_empty[(rt + 1) % RAW_SLOTS], (((rt + 1) / RAW_SLOTS) & 1) ^ 1);
               tc_fence_after_sync();
-              const uint32_t a_addr = smem_u32(smem_a + sa * L::a_stage);
+              const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
               uint32_t sfa_col = 0, sfb_col = 0;
               if constexpr (T::block_scaled) {
                 // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
@@ -575,8 +741,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               }
 #pragma unroll
               for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
-                const uint64_t da = make_kmajor_sw128_desc(a_addr + j * MMA_K_BYTES);
-                const uint64_t db = make_kmajor_sw128_desc(b_addr + j * MMA_K_BYTES);
+                const uint64_t da = a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
+                const uint64_t db = b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
                 const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
                 if constexpr (KIND == Kind::NVFP4) {
                   umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
@@ -595,7 +761,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
               }
             }
-            if (ok && (bx == KA - 1 || kb == kb_count - 1)) {
+            if (ok && b_last_use) {
               umma_commit(&b_empty[sb]);
               ++jt;
             }
@@ -616,10 +782,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t rt = 0, slot_phase = 0;
     bool ok = true;
-    ItemCursor cursor;
-    for (long long item = blockIdx.x; ok; item += gridDim.x) {
+    ItemCursor cursor(work.segs);
+    for (int wi = 0; ok; ++wi) {
       Item it;
-      if (!fetch_item(p, item, cursor, it)) break;
+      if (!get_item(p, work, wi, cursor, it)) break;
       if (it.rows <= 0) continue;
       const int mtiles = (it.rows + BM - 1) / BM;
       const int n0 = it.nt * BN;
@@ -641,7 +807,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // FP8 only: the 128x128 weight block of this warpgroup's columns. With the fused activation the columns are
           // interleaved gate / up rows of the weight, which lie in two different blocks (see GemmParams::epilogue).
           const bool fused = KIND == Kind::FP8 && p.epilogue != 0;
-          const int blk_g = fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7;
+          const int blk_g = min(fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7, p.sfb_rows - 1);   // columns past n belong to no block
           const int blk_u = fused ? ((p.n >> 1) + ((n0 + col_base) >> 1)) >> 7 : blk_g;
           const float* sfb_blk = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_g) * p.sf_k;
           const float* sfb_blk_u = p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_u) * p.sf_k;
@@ -742,7 +908,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             float sb_scalar = 0.f, sb_up = 0.f;
             const bool fused = KIND == Kind::FP8 && p.epilogue != 0;
             if constexpr (KIND == Kind::FP8) {
-              const int blk_g = fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7;
+              const int blk_g = min(fused ? (n0 + col_base) >> 8 : (n0 + col_base) >> 7, p.sfb_rows - 1);   // columns past n belong to no block
               const int blk_u = fused ? ((p.n >> 1) + ((n0 + col_base) >> 1)) >> 7 : blk_g;
               sb_scalar = __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_g) * p.sf_k + kb);
               sb_up = fused ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + blk_u) * p.sf_k + kb) : sb_scalar;

@@ -471,8 +471,8 @@ def measure_device_resident(device, peaks, steps=20):
     out = {"note": "weights resident in HBM; peak = bf16_tflops of MEASURED_PEAKS.json (x2 for 8-bit operands), of measured" if peaks else
                    "weights resident in HBM; peak = 1590 TFLOP/s bf16 (x2 for 8-bit), of fallback"}
     bf16_peak = peaks.get("bf16_tflops", 1590.0)
-    cases = [("fp8", "c3_fp8", False, (0, 5, 6), 2.0, 32), ("fp8_ue8m0", "c3_fp8", True, (0, 7), 2.0, 32),
-             ("bf16", "c2_bf16", False, (0, 1, 6, 7), 1.0, 128)]
+    cases = [("fp8", "c3_fp8", False, (0, 5, 6, 8), 2.0, 32), ("fp8_ue8m0", "c3_fp8", True, (0, 7), 2.0, 32),
+             ("bf16", "c2_bf16", False, (0, 1, 6, 7, 8), 1.0, 128)]
     for name, wl, ue, tiles, mult, experts in cases:
         cfg = dict(WORKLOADS[wl])
         cfg["tokens"] = max(1, cfg["tokens"] * experts // cfg["experts"])

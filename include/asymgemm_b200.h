@@ -55,7 +55,8 @@ typedef struct ag_gemm_desc {
   void* d;         /* device. [rows, N] bf16 or fp32, row-major, written in place */
 
   /* contiguous layout: segment i covers rows [offsets[2i], offsets[2i+1]) and uses weight experts[i];
-     the list ends at the first negative expert id or after max_segments entries. */
+     the list ends at the first negative expert id or after max_segments entries. Both arrays must hold max_segments
+     (2 * max_segments) readable entries: the kernels copy the whole list into shared memory with all threads at once. */
   const int32_t* offsets; /* device */
   const int32_t* experts; /* device */
   int32_t max_segments;
@@ -83,7 +84,9 @@ typedef struct ag_gemm_desc {
                           1 = 128 columns per item (device-resident b), 2 = 32 columns x 512 B of K per stage
                           (host-resident b), 3 = 32 x 1024 B, 4 = 64 x 256 B, 5 = 128 columns with the scaled accumulators in registers
                           (fp8 / int8 with device-resident b), 6 = 256 columns per item (device-resident b; bf16, fp8, int8),
-                          7 = 128 columns with a deep activation ring (device-resident b; bf16 and the hardware-scaled kinds) */
+                          7 = 128 columns with a deep activation ring (device-resident b; bf16 and the hardware-scaled kinds),
+                          8 = 256 columns per item on pairs of CTAs that share one 256 x 256 tcgen05.mma.cta_group::2 (device-resident b;
+                          bf16, fp8, int8; not with no_split; at least two SMs) */
   int32_t no_split;    /* device-resident b only: 1 = keep one item per (segment, n-tile) instead of splitting long segments into
                           accumulator-sized row chunks across CTAs (tests / tuning); ignored for host-resident b */
 
