@@ -300,6 +300,18 @@ __device__ __forceinline__ int get_item(const GemmParams& p, const WorkList& wl,
   return fetch_item(p, wl.first + static_cast<long long>(i) * wl.stride, cur, it);
 }
 
+// Position of a user's n-th step in the activation ring. With two MMA issuers the ring is split in halves, one per issuer,
+// so that every barrier has ONE consumer who sees each of its phases: a phase test by parity is only valid while the tester
+// is less than two phases away from the barrier, and an issuer that has no step for a while (a chunk with a single row
+// tile belongs to the other one) would otherwise run ahead of the producer by more than that.
+template <int SA, bool DUAL>
+struct ARing {
+  static constexpr uint32_t PER = DUAL ? SA / 2 : SA;
+  static_assert(!DUAL || (SA % 2 == 0 && SA >= 2), "two issuers need an even number of activation stages");
+  __device__ static uint32_t stage(uint32_t user, uint32_t n) { return (DUAL ? user * PER : 0u) + n % PER; }
+  __device__ static uint32_t phase(uint32_t n) { return (n / PER) & 1u; }
+};
+
 struct WaitCtx {
   int* status;
   volatile int* abort_flag;
@@ -400,7 +412,7 @@ struct SmemLayout {
   static constexpr int sfa_off = b_off + SB * b_stage;
   static constexpr int sfb2_off = sfa_off + SA * sfa_stage;
   static constexpr int bar_off = sfb2_off + SB * sfb_stage;
-  static constexpr int num_bars = 2 * SA + 2 * SB + 32 + 1;
+  static constexpr int num_bars = 2 * SA + 2 * SB + 32 + 2;
   static constexpr int sfb_off = bar_off + num_bars * 8;          // 4 warps x BN floats (INT8 column scales)
   static constexpr int misc_off = sfb_off + 4 * BN * 4;           // tmem base, abort flag
   // work list (build_work_list): as large as what is left of the 227 KB allows
@@ -508,6 +520,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
   constexpr uint32_t IDESC = KIND == Kind::NVFP4 ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);   // FP8_UE8M0: per K atom
   constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, BN, REG_ACC>();   // one arrival per drain warp
+  constexpr bool DUAL_ISSUE = !T::block_scaled;                                // two MMA-issuing threads (see the issuer role)
+  using AR = ARing<SA, DUAL_ISSUE>;
+  constexpr uint32_t B_EMPTY_ARRIVALS = (DUAL_ISSUE && !REG_ACC) ? 2 : 1;      // issuers that release a weight stage
+  static_assert(!(DUAL_ISSUE && REG_ACC) || KA == 1, "with register accumulators a weight stage serves exactly one step");
+  static_assert(!(DUAL_ISSUE && REG_ACC) || (SB % 2 == 0 && RAW_SLOTS % 2 == 0), "alternating issuers must always meet the same stages and slots");
   constexpr uint32_t SF_COL0 = NUM_SLOTS * BN;   // first TMEM column of the scale-factor area
   constexpr int SPILL_DELAY = SB > 2 ? SB - 2 : 1;
 
@@ -526,7 +543,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint64_t* b_empty = b_full + SB;
   uint64_t* tm_full = b_empty + SB;    // [16] hardware-accumulated: per accumulator slot; sw_scale: [0..1] = raw slots
   uint64_t* tm_empty = tm_full + 16;   // [16]
-  uint64_t* done_bar = tm_empty + 16;  // MMA thread drains its own pipeline through this one on abort
+  uint64_t* done_bar = tm_empty + 16;  // [2] an MMA thread drains its own pipeline through its one on abort
   float* sfb_smem = reinterpret_cast<float*>(smem + L::sfb_off);
   uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(smem + L::misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::misc_off + 4);
@@ -536,9 +553,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], B_EMPTY_ARRIVALS); }
     for (int i = 0; i < 16; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], DRAIN_ARRIVALS); }
     mbar_init(done_bar, 1);
+    mbar_init(done_bar + 1, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmap_a);
@@ -640,7 +658,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ===================================================================== A producer
     if (lane == 0) {
-      uint32_t it_a = 0;
+      uint32_t it_a = 0, used0 = 0, used1 = 0;   // steps so far: all, and per issuer
       bool ok = true;
       ItemCursor cursor(work.segs);
       for (int wi = 0; ok; ++wi) {
@@ -652,8 +670,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const int mc = min(CHUNK_TILES, mtiles - m0);
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
-              const uint32_t s = it_a % SA;
-              ok = wait_bar(&a_empty[s], ((it_a / SA) & 1) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
+              const uint32_t user = DUAL_ISSUE ? ((T::sw_scale ? it_a : static_cast<uint32_t>(mt)) & 1u) : 0u;   // as in the issuer role
+              uint32_t& used = user ? used1 : used0;
+              const uint32_t s = AR::stage(user, used);
+              ok = wait_bar(&a_empty[s], AR::phase(used) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
               if (!ok) break;
               mbar_arrive_expect_tx(&a_full[s], L::a_stage + L::sfa_stage);
               const int a_row = it.row0 + (m0 + mt) * BM;
@@ -663,28 +683,38 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                              L::sfa_stage, &a_full[s]);
               }
               tma_load_2d(smem_a + s * L::a_stage, &tmap_a, &a_full[s], kb * ATOM_BYTES, a_row);
+              ++used;
             }
           }
         }
       }
       if (!ok) {
-        const uint32_t first = it_a > SA ? it_a - SA : 0;
-        for (uint32_t q = first; q < it_a; ++q) wait_bar(&a_full[q % SA], (q / SA) & 1, wc, ST_TIMEOUT_DRAIN, false);
+        for (uint32_t user = 0; user < (DUAL_ISSUE ? 2u : 1u); ++user) {
+          const uint32_t used = user ? used1 : used0;
+          for (uint32_t q = used > AR::PER ? used - AR::PER : 0; q < used; ++q)
+            wait_bar(&a_full[AR::stage(user, q)], AR::phase(q), wc, ST_TIMEOUT_DRAIN, false);
+        }
       }
     }
-  } else if (warp == 2) {
-    // ===================================================================== MMA issuer
+  } else if (warp == 2 || (DUAL_ISSUE && warp == 3)) {
+    // ===================================================================== MMA issuer(s)
+    // One thread issues what the tensor core does, and every instruction of it (barrier test, MMA, commit, the loop's own
+    // arithmetic) costs that thread tens of cycles: a single issuer spends about 950 cycles on a step of four MMAs that
+    // the tensor core finishes in 512. So two threads (warps 2 and 3) share the steps: with accumulators in TMEM each row
+    // tile belongs to one issuer (the order of the additions into a tile is that thread's program order); with software
+    // scaling the steps alternate, each into its own raw slot. Both walk the same sequence and keep the same counters.
+    // The block-scaled kinds stay with one issuer: their scale copies into TMEM are ordered with the MMAs by issue order.
     if (lane == 0) {
-      uint32_t it_a = 0, jt = 0, rt = 0, slot_phase = 0;
+      const uint32_t issuer = warp - 2;
+      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0;   // own: steps this issuer has taken
       bool ok = true;
       ItemCursor cursor(work.segs);
-      // One thread issues everything the tensor core does, and every instruction of it (barrier test, MMA, commit) costs
-      // this thread tens of cycles. So the loop keeps them few: the barriers of the NEXT step are tested (non-blocking)
-      // before the MMAs of this step are issued, which hides their round trip, and the operand descriptors are the
-      // descriptor of stage 0 plus an offset in its address field.
+      // the operand descriptors are the descriptor of stage 0 plus an offset in its address field
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
       const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
-      bool a_seen = false, b_seen = false, r_seen = false;   // "the barrier of the coming step was already complete"
+      // single issuer: the barriers of the NEXT step are tested (non-blocking) before the MMAs of this step are issued,
+      // which hides their round trip ("the barrier of the coming step was already complete")
+      bool a_seen = false, b_seen = false, r_seen = false;
       for (int wi = 0; ok; ++wi) {
         Item it;
         if (!get_item(p, work, wi, cursor, it)) break;
@@ -695,7 +725,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             const uint32_t sb = jt % SB;
             const int bx = kb % KA;
-            if (bx == 0) {
+            // Register accumulators: one step per K atom and stage, so a weight stage has one user and the other issuer
+            // leaves it alone. Otherwise both issuers wait for every stage and both release it (b_empty counts two).
+            const bool b_mine = !(DUAL_ISSUE && REG_ACC) || (rt & 1u) == issuer;
+            if (bx == 0 && b_mine) {
               if (!b_seen) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
               b_seen = false;
             }
@@ -703,66 +736,71 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const bool b_last_use = bx == KA - 1 || kb == kb_count - 1;   // the stage is released after this K atom
             const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage + bx * L::b_box) >> 4);
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
-              const uint32_t sa = it_a % SA;
-              if (!a_seen) ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
-              if (!ok) break;
-              uint32_t d_col;
-              if constexpr (T::sw_scale) {
-                const uint32_t rs = rt % RAW_SLOTS;
-                if (!r_seen) ok = wait_bar(&tm_empty[rs], ((rt / RAW_SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
-                d_col = (RAW_SLOT0 + rs) * BN;
-              } else {
-                if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
-                d_col = mt * BN;
-              }
-              if (!ok) break;
-              // a look at the next step's barriers; the answers are needed only after this step's MMAs are on their way
-              a_seen = mbar_test_wait(&a_full[(it_a + 1) % SA], ((it_a + 1) / SA) & 1);
-              if (mt == mc - 1 && b_last_use) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);
-              if constexpr (T::sw_scale) r_seen = mbar_test_wait(&tm_empty[(rt + 1) % RAW_SLOTS], (((rt + 1) / RAW_SLOTS) & 1) ^ 1);
-              tc_fence_after_sync();
-              const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
-              uint32_t sfa_col = 0, sfb_col = 0;
-              if constexpr (T::block_scaled) {
-                // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
-                constexpr int BLOCKS = KIND == Kind::NVFP4 ? 4 : 1;   // 512-byte blocks per stage and operand
-                sfa_col = SF_COL0 + (it_a & 1) * 16;
-                sfb_col = SF_COL0 + 32 + (kb & 1) * 16;
-                const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
-#pragma unroll
-                for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
-                if (mt == 0) {
-                  const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + (KIND == Kind::NVFP4 ? bx * SF_ATOM_BYTES : 0));
-#pragma unroll
-                  for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
-                }
-                // a 64-row weight tile uses half of its 128-row scale block: words 0-1 or 2-3 of each lane
-                if constexpr (BN == 64) sfb_col += ((it.nt & 1) ? 2 : 0);
-              }
-#pragma unroll
-              for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
-                const uint64_t da = a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
-                const uint64_t db = b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
-                const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
-                if constexpr (KIND == Kind::NVFP4) {
-                  umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
-                } else if constexpr (KIND == Kind::FP8_UE8M0) {
-                  // all four MMAs of this K atom use the atom's scale byte: byte (kb % 4) of the scale words
-                  umma_mxfp8(tmem_base + d_col, da, db, make_idesc_mxfp8(BN, kb & 3), tmem_base + sfa_col, tmem_base + sfb_col, acc);
+              const bool mine = !DUAL_ISSUE || ((T::sw_scale ? rt : static_cast<uint32_t>(mt)) & 1u) == issuer;
+              if (mine) {
+                const uint32_t sa = AR::stage(issuer, own);
+                if (!a_seen) ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
+                if (!ok) break;
+                uint32_t d_col;
+                if constexpr (T::sw_scale) {
+                  const uint32_t rs = rt % RAW_SLOTS;
+                  if (!r_seen) ok = wait_bar(&tm_empty[rs], ((rt / RAW_SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                  d_col = (RAW_SLOT0 + rs) * BN;
                 } else {
-                  umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+                  if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                  d_col = mt * BN;
+                }
+                if (!ok) break;
+                if constexpr (!DUAL_ISSUE) {
+                  a_seen = mbar_test_wait(&a_full[AR::stage(0, own + 1)], AR::phase(own + 1));
+                  if (mt == mc - 1 && b_last_use) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);
+                  if constexpr (T::sw_scale) r_seen = mbar_test_wait(&tm_empty[(rt + 1) % RAW_SLOTS], (((rt + 1) / RAW_SLOTS) & 1) ^ 1);
+                }
+                tc_fence_after_sync();
+                const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
+                uint32_t sfa_col = 0, sfb_col = 0;
+                if constexpr (T::block_scaled) {
+                  // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
+                  constexpr int BLOCKS = KIND == Kind::NVFP4 ? 4 : 1;   // 512-byte blocks per stage and operand
+                  sfa_col = SF_COL0 + (it_a & 1) * 16;
+                  sfb_col = SF_COL0 + 32 + (kb & 1) * 16;
+                  const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
+#pragma unroll
+                  for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
+                  if (mt == 0) {
+                    const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + (KIND == Kind::NVFP4 ? bx * SF_ATOM_BYTES : 0));
+#pragma unroll
+                    for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
+                  }
+                  // a 64-row weight tile uses half of its 128-row scale block: words 0-1 or 2-3 of each lane
+                  if constexpr (BN == 64) sfb_col += ((it.nt & 1) ? 2 : 0);
+                }
+#pragma unroll
+                for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
+                  const uint64_t da = a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
+                  const uint64_t db = b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4));
+                  const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
+                  if constexpr (KIND == Kind::NVFP4) {
+                    umma_nvfp4(tmem_base + d_col, da, db, IDESC, tmem_base + sfa_col + 4 * j, tmem_base + sfb_col + 4 * j, acc);
+                  } else if constexpr (KIND == Kind::FP8_UE8M0) {
+                    // all four MMAs of this K atom use the atom's scale byte: byte (kb % 4) of the scale words
+                    umma_mxfp8(tmem_base + d_col, da, db, make_idesc_mxfp8(BN, kb & 3), tmem_base + sfa_col, tmem_base + sfb_col, acc);
+                  } else {
+                    umma<T::mma>(tmem_base + d_col, da, db, IDESC, acc);
+                  }
+                }
+                umma_commit(&a_empty[sa]);
+                ++own;
+                if constexpr (T::sw_scale) {
+                  umma_commit(&tm_full[rt % RAW_SLOTS]);
+                } else {
+                  if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
                 }
               }
-              umma_commit(&a_empty[sa]);
-              if constexpr (T::sw_scale) {
-                umma_commit(&tm_full[rt % RAW_SLOTS]);
-                ++rt;
-              } else {
-                if (kb == kb_count - 1) umma_commit(&tm_full[mt]);
-              }
+              if constexpr (T::sw_scale) ++rt;
             }
             if (ok && b_last_use) {
-              umma_commit(&b_empty[sb]);
+              if (b_mine) umma_commit(&b_empty[sb]);
               ++jt;
             }
           }
@@ -770,8 +808,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
       if (!ok) {  // aborting: wait until the tensor pipe has retired what this thread issued
-        umma_commit(done_bar);
-        wait_bar(done_bar, 0, wc, ST_TIMEOUT_DRAIN, false);
+        umma_commit(done_bar + issuer);
+        wait_bar(done_bar + issuer, 0, wc, ST_TIMEOUT_DRAIN, false);
       }
     }
   }

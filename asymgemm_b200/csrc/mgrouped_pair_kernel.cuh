@@ -9,8 +9,9 @@
 // signal the first CTA's mbarrier (cp.async.bulk.tensor with .cta_group::2). Only the MMA thread's tcgen05.commit goes to
 // the barriers of both CTAs at once.
 //
-// Roles per CTA as in mgrouped_kernel.cuh: warp 0 weight producer, warp 1 activation producer, warp 2 TMEM allocation and
-// (in the first CTA of the pair only) the single MMA-issuing thread, warps 4-11 two drain warpgroups of 128 columns each.
+// Roles per CTA as in mgrouped_kernel.cuh: warp 0 weight producer, warp 1 activation producer, warp 2 TMEM allocation,
+// warps 2 and 3 (in the first CTA of the pair only) one MMA-issuing thread each, warps 4-11 two drain warpgroups of 128
+// columns each.
 // Work: an item is (segment, chunk of 256 * MT rows, 256-column tile), taken by pairs in turn; CTA r of the pair owns
 // rows (2 * mt + r) * 128 ... of the chunk. BF16 accumulates MT = 2 row tiles per CTA in TMEM (2 x 256 columns); FP8 and
 // INT8 keep one row tile's scaled accumulators in registers and use the two 256-column TMEM slots for raw per-K-block
@@ -118,6 +119,8 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int SLOTS = TMEM_COLS / PAIR_BN;                   // 2: accumulators (BF16) or raw products (FP8 / INT8)
   constexpr uint32_t IDESC = make_idesc_pair(T::d_fmt, T::ab_fmt, PAIR_BN);
   constexpr int COLS = PAIR_BN / 2;                            // columns per drain warpgroup
+  static_assert(SB % 2 == 0 && SLOTS % 2 == 0, "alternating issuers must always meet the same stages and slots");
+  using AR = ARing<SA, true>;                                  // the activation ring is split between the two issuers
   constexpr uint32_t STAGE_TX_A = 2 * L::a_stage, STAGE_TX_B = 2 * L::b_stage;   // both CTAs' loads land on the first CTA's barrier
 
   extern __shared__ uint8_t smem_dyn[];
@@ -141,7 +144,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], T::sw_scale ? 1 : 2); }   // issuers that release a stage
     for (int i = 0; i < 4; ++i) { mbar_init(&tm_full[i], 1); mbar_init(&tm_empty[i], 2 * 8); }   // 8 drain warps per CTA
     *abort_flag = 0;
     fence_mbar_init();
@@ -188,7 +191,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ===================================================================== activation producer: this CTA's 128 rows of each tile
     if (lane == 0) {
-      uint32_t it_a = 0;
+      uint32_t it_a = 0, used0 = 0, used1 = 0;   // steps so far: all, and per issuer (ARing)
       bool ok = true;
       ItemCursor cursor(work.segs);
       for (int wi = 0; ok; ++wi) {
@@ -198,28 +201,30 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);      // 256-row tiles of the pair in this chunk (<= MT)
         for (int kb = 0; kb < kb_count && ok; ++kb) {
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
-            const uint32_t s = it_a % SA;
-            ok = wait_bar(&a_empty[s], ((it_a / SA) & 1) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
+            const uint32_t user = (T::sw_scale ? it_a : static_cast<uint32_t>(mt)) & 1u;   // as in the issuer role
+            uint32_t& used = user ? used1 : used0;
+            const uint32_t s = AR::stage(user, used);
+            ok = wait_bar(&a_empty[s], AR::phase(used) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
             if (!ok) break;
             if (rank == 0) mbar_arrive_expect_tx(&a_full[s], STAGE_TX_A);
             const int a_row = it.row0 + (2 * mt + static_cast<int>(rank)) * BM;
             tma_load_2d_pair(smem_a + s * L::a_stage, &tmap_a, in_first(&a_full[s]), kb * ATOM_BYTES, a_row);
+            ++used;
           }
         }
       }
     }
-  } else if (warp == 2) {
-    // ===================================================================== MMA issuer (first CTA of the pair only)
+  } else if (warp == 2 || warp == 3) {
+    // ===================================================================== MMA issuers (first CTA of the pair only)
+    // Two issuing threads, as in the single-CTA kernel: with accumulators in TMEM each row tile belongs to one of them,
+    // with register accumulators the K blocks alternate (each into its own raw slot, and each weight stage has one user).
     if (lane == 0 && rank == 0) {
-      uint32_t it_a = 0, jt = 0, rt = 0, slot_phase = 0;
+      const uint32_t issuer = warp - 2;
+      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0;   // own: steps this issuer has taken
       bool ok = true;
       ItemCursor cursor(work.segs);
-      auto commit_both = [&](uint64_t* bar) { umma_commit_pair(bar); };
-      // as in the single-CTA kernel: barriers of the next step are tested before this step's MMAs are issued, and the
-      // descriptors are those of stage 0 plus an offset in the address field
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
       const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
-      bool a_seen = false, b_seen = false, r_seen = false;
       for (int wi = 0; ok; ++wi) {
         Item it;
         if (!get_item(p, work, wi, cursor, it)) break;
@@ -227,44 +232,45 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);
         for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
           const uint32_t sb = jt % SB;
-          if (!b_seen) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
-          b_seen = false;
+          const bool b_mine = !T::sw_scale || (rt & 1u) == issuer;
+          if (b_mine) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
           if (!ok) break;
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage) >> 4);
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
-            const uint32_t sa = it_a % SA;
-            if (!a_seen) ok = wait_bar(&a_full[sa], (it_a / SA) & 1, wc, ST_TIMEOUT_A_FULL);
-            if (!ok) break;
-            uint32_t d_col;
-            if constexpr (T::sw_scale) {
-              const uint32_t rs = rt % SLOTS;
-              if (!r_seen) ok = wait_bar(&tm_empty[rs], ((rt / SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
-              d_col = rs * PAIR_BN;
-            } else {
-              if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
-              d_col = mt * PAIR_BN;
-            }
-            if (!ok) break;
-            a_seen = mbar_test_wait(&a_full[(it_a + 1) % SA], ((it_a + 1) / SA) & 1);
-            if (mt == mc - 1) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);
-            if constexpr (T::sw_scale) r_seen = mbar_test_wait(&tm_empty[(rt + 1) % SLOTS], (((rt + 1) / SLOTS) & 1) ^ 1);
-            tc_fence_after_sync();
-            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
+            const bool mine = ((T::sw_scale ? rt : static_cast<uint32_t>(mt)) & 1u) == issuer;
+            if (mine) {
+              const uint32_t sa = AR::stage(issuer, own);
+              ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
+              if (!ok) break;
+              uint32_t d_col;
+              if constexpr (T::sw_scale) {
+                const uint32_t rs = rt % SLOTS;
+                ok = wait_bar(&tm_empty[rs], ((rt / SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                d_col = rs * PAIR_BN;
+              } else {
+                if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                d_col = mt * PAIR_BN;
+              }
+              if (!ok) break;
+              tc_fence_after_sync();
+              const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
 #pragma unroll
-            for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
-              const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
-              umma_pair<T::mma>(tmem_base + d_col, a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)),
-                                b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)), IDESC, acc);
+              for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
+                const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
+                umma_pair<T::mma>(tmem_base + d_col, a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)),
+                                  b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)), IDESC, acc);
+              }
+              umma_commit_pair(&a_empty[sa]);
+              ++own;
+              if constexpr (T::sw_scale) {
+                umma_commit_pair(&tm_full[rt % SLOTS]);
+              } else {
+                if (kb == kb_count - 1) umma_commit_pair(&tm_full[mt]);
+              }
             }
-            commit_both(&a_empty[sa]);
-            if constexpr (T::sw_scale) {
-              commit_both(&tm_full[rt % SLOTS]);
-              ++rt;
-            } else {
-              if (kb == kb_count - 1) commit_both(&tm_full[mt]);
-            }
+            if constexpr (T::sw_scale) ++rt;
           }
-          if (ok) commit_both(&b_empty[sb]);
+          if (ok && b_mine) umma_commit_pair(&b_empty[sb]);
         }
         if constexpr (!T::sw_scale) slot_phase ^= (1u << mc) - 1u;
       }
