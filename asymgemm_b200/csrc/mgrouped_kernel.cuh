@@ -32,6 +32,7 @@
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
 // shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
 #pragma once
+#include <utility>
 #include <cuda_bf16.h>
 
 #include <type_traits>
@@ -311,6 +312,11 @@ struct ARing {
   __device__ static uint32_t stage(uint32_t user, uint32_t n) { return (DUAL ? user * PER : 0u) + n % PER; }
   __device__ static uint32_t phase(uint32_t n) { return (n / PER) & 1u; }
 };
+
+template <typename F, int... I>
+__device__ __forceinline__ void for_each_index(std::integer_sequence<int, I...>, F&& f) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
 
 struct WaitCtx {
   int* status;
@@ -906,9 +912,25 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               __syncwarp();
               if (lane == 0) mbar_arrive(&tm_empty[rs]);
             };
-            {
-              // columns per TMEM load: 128 accumulator registers per thread leave room for 16 staging registers, not 32
-              constexpr int LW = COLS >= 128 ? 16 : 32;
+            if constexpr (COLS >= 128) {
+              // 128 accumulator registers per thread leave room for 16 staging registers: two buffers of 8 columns, so that the
+              // load of the next piece is in flight while this one is scaled and added (one buffer of 16 left the warp idle
+              // for a TMEM round trip eight times per K block)
+              constexpr int LW = 8, NP = COLS / LW;
+              uint32_t ra[LW], rb[LW];
+              tmem_ld_cols(raw_addr, ra);
+              auto step = [&](auto cc_tag) {
+                constexpr int cc = decltype(cc_tag)::value;
+                auto& cur = (cc & 1) ? rb : ra;
+                auto& nxt = (cc & 1) ? ra : rb;
+                tmem_wait_ld_into(cur);
+                if constexpr (cc + 1 < NP) tmem_ld_cols(raw_addr + (cc + 1) * LW, nxt);
+                else release_slot();
+                accumulate(cur, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, sb_up, kb);
+              };
+              for_each_index(std::make_integer_sequence<int, NP>{}, step);
+            } else {
+              constexpr int LW = 32;
               auto piece = [&](auto cc_tag) {
                 constexpr int cc = decltype(cc_tag)::value;
                 uint32_t r[LW];
@@ -917,14 +939,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 if (cc == COLS / LW - 1) release_slot();
                 accumulate(r, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, sb_up, kb);
               };
-              piece(std::integral_constant<int, 0>{});
-              if constexpr (COLS / LW > 1) piece(std::integral_constant<int, 1>{});
-              if constexpr (COLS / LW > 2) { piece(std::integral_constant<int, 2>{}); piece(std::integral_constant<int, 3>{}); }
-              if constexpr (COLS / LW > 4) {
-                piece(std::integral_constant<int, 4>{}); piece(std::integral_constant<int, 5>{});
-                piece(std::integral_constant<int, 6>{}); piece(std::integral_constant<int, 7>{});
-              }
-              static_assert(COLS / LW <= 8, "pieces are written out up to eight");
+              for_each_index(std::make_integer_sequence<int, COLS / LW>{}, piece);
             }
             if constexpr (KIND == Kind::INT8) __syncwarp();  // everyone is done with sfb_buf before the next block refills it
           }
