@@ -26,8 +26,9 @@
 // factors copied into TMEM by tcgen05.cp); FP8 and INT8 produce one raw product per 128-wide K block that the drain warps
 // scale in fp32 (block scales are arbitrary fp32 numbers) and add to accumulators kept in TMEM, or in registers (REG_ACC).
 //
-// Warp roles: warp 0 = B producer (+ scratch spill), warp 1 = A producer, warp 2 = TMEM allocator + single-thread
-// tcgen05.mma issuer, warp 3 idle, warps 4-7 (and 8-11 where a second drain warpgroup pays, see drain_wgs_of) = TMEM drain.
+// Warp roles: warp 0 = B producer (+ scratch spill), warp 1 = A producer (one lane per MMA issuer), warp 2 = TMEM allocator,
+// warps 2 and 3 = one tcgen05.mma-issuing thread each (one issuer for the block-scaled kinds), warps 4-7 (and 8-11 where a
+// second drain warpgroup pays, see drain_wgs_of) = TMEM drain.
 //
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
 // shared abort flag that all roles poll, waits for its own copies in flight, frees TMEM and returns.
@@ -663,8 +664,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp == 1) {
     // ===================================================================== A producer
-    if (lane == 0) {
-      uint32_t it_a = 0, used0 = 0, used1 = 0;   // steps so far: all, and per issuer
+    // With two issuers, two lanes: each feeds one issuer's half of the ring (the lanes run as divergent threads of the warp,
+    // so the issue cost of one lane's barrier test and TMA instruction overlaps with the other's).
+    if (lane < (DUAL_ISSUE ? 2 : 1)) {
+      const uint32_t me = lane;
+      uint32_t it_a = 0, used = 0;   // steps so far: all, and those of this lane's issuer
       bool ok = true;
       ItemCursor cursor(work.segs);
       for (int wi = 0; ok; ++wi) {
@@ -677,7 +681,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
               const uint32_t user = DUAL_ISSUE ? ((T::sw_scale ? it_a : static_cast<uint32_t>(mt)) & 1u) : 0u;   // as in the issuer role
-              uint32_t& used = user ? used1 : used0;
+              if (user != me) continue;
               const uint32_t s = AR::stage(user, used);
               ok = wait_bar(&a_empty[s], AR::phase(used) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
               if (!ok) break;
@@ -695,11 +699,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
       if (!ok) {
-        for (uint32_t user = 0; user < (DUAL_ISSUE ? 2u : 1u); ++user) {
-          const uint32_t used = user ? used1 : used0;
-          for (uint32_t q = used > AR::PER ? used - AR::PER : 0; q < used; ++q)
-            wait_bar(&a_full[AR::stage(user, q)], AR::phase(q), wc, ST_TIMEOUT_DRAIN, false);
-        }
+        for (uint32_t q = used > AR::PER ? used - AR::PER : 0; q < used; ++q)
+          wait_bar(&a_full[AR::stage(me, q)], AR::phase(q), wc, ST_TIMEOUT_DRAIN, false);
       }
     }
   } else if (warp == 2 || (DUAL_ISSUE && warp == 3)) {
