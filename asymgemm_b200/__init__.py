@@ -8,6 +8,7 @@ from .api import (  # noqa: F401
     check_status,
     get_mk_alignment_for_contiguous_layout,
     get_num_sms,
+    launch_sm_cap,
     m_grouped_bf16_asym_gemm_nt_contiguous,
     m_grouped_bf16_asym_gemm_nt_masked,
     m_grouped_fp4_asym_gemm_nt_contiguous,

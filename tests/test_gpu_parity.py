@@ -595,3 +595,37 @@ def test_prefetch_of_staged_weights_is_used_or_discarded_correctly():
     finally:
         ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
     ag.check_status()
+
+
+@pytest.mark.parametrize("kind", ["fp8", "bf16", "fp4"])
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_segment_list_longer_than_the_shared_memory_table(kind, b_on_host):
+    """1100 segments (more than the 1024 whose entries a CTA keeps in shared memory; NVFP4 keeps 256): every role then walks
+    the segment list in device memory instead of reading the per-CTA item table, and must enumerate the same items."""
+    rng = np.random.default_rng(5)
+    rows = [int(r) for r in rng.choice([0, 1, 3, 17, 128, 130], size=1100)]
+    n, k = 64, 128
+    c = H.make_contiguous_case(kind, rows, n, k, seed=91, b_on_host=b_on_host)
+    d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _run_contiguous(c, d)
+    ag.check_status()
+    d_np = d.float().cpu().numpy()
+    _check(kind, d_np, c["ref"], c["segments"])
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], c["m_total"])]).all()
+
+
+@pytest.mark.parametrize("kind", ["fp8", "bf16", "fp4"])
+@pytest.mark.parametrize("b_on_host", [True, False])
+def test_more_items_per_cta_than_the_shared_memory_table(kind, b_on_host):
+    """One CTA for 600 to 2000 items, depending on the tile (the table holds 512 per CTA; NVFP4 128): the first items come from the table, the rest from
+    the walk, and the two must join without a gap or a repeat."""
+    rows = [200, 0, 1, 129, 300, 64, 513, 130] * 8
+    n, k = 2048, 128
+    c = H.make_contiguous_case(kind, rows, n, k, seed=92, b_on_host=b_on_host)
+    d = torch.full((c["m_total"], n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    with ag.launch_sm_cap(1):
+        _run_contiguous(c, d)
+    ag.check_status()
+    d_np = d.float().cpu().numpy()
+    _check(kind, d_np, c["ref"], c["segments"])
+    assert np.isnan(d_np[~H.valid_row_mask(c["segments"], c["m_total"])]).all()
