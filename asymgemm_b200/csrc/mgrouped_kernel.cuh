@@ -527,7 +527,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int RAW_SLOT0 = REG_ACC ? 0 : CHUNK_TILES;               // first raw slot
   constexpr uint32_t IDESC = KIND == Kind::NVFP4 ? make_idesc_nvfp4(BN) : make_idesc(T::d_fmt, T::ab_fmt, BN);   // FP8_UE8M0: per K atom
   constexpr uint32_t DRAIN_ARRIVALS = 4 * drain_wgs_of<KIND, BN, REG_ACC>();   // one arrival per drain warp
-  constexpr bool DUAL_ISSUE = !T::block_scaled;                                // two MMA-issuing threads (see the issuer role)
+  // two MMA-issuing threads (see the issuer role); the block-scaled kinds need a second set of scale-factor columns in
+  // TMEM for the second issuer, which 128-column tiles have room for (3 x 128 accumulator columns + 2 x 64)
+  constexpr bool DUAL_ISSUE = !T::block_scaled || BN == 128;
+  static_assert(!(T::block_scaled && DUAL_ISSUE) || NUM_SLOTS * BN + 2 * SF_TMEM_COLS <= TMEM_COLS, "no room for the second issuer's scale factors");
   using AR = ARing<SA, DUAL_ISSUE>;
   constexpr uint32_t B_EMPTY_ARRIVALS = (DUAL_ISSUE && !REG_ACC) ? 2 : 1;      // issuers that release a weight stage
   static_assert(!(DUAL_ISSUE && REG_ACC) || KA == 1, "with register accumulators a weight stage serves exactly one step");
@@ -719,9 +722,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       // the operand descriptors are the descriptor of stage 0 plus an offset in its address field
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
       const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
-      // single issuer: the barriers of the NEXT step are tested (non-blocking) before the MMAs of this step are issued,
-      // which hides their round trip ("the barrier of the coming step was already complete")
+      // the barriers of this issuer's NEXT step are tested (non-blocking) before the MMAs of this step are issued, which hides
+      // their round trip ("the barrier of the coming step was already complete")
       bool a_seen = false, b_seen = false, r_seen = false;
+      const uint32_t sf_base = SF_COL0 + (T::block_scaled && DUAL_ISSUE ? issuer * SF_TMEM_COLS : 0u);   // this issuer's scale columns
       for (int wi = 0; ok; ++wi) {
         Item it;
         if (!get_item(p, work, wi, cursor, it)) break;
@@ -758,8 +762,8 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   d_col = mt * BN;
                 }
                 if (!ok) break;
+                a_seen = mbar_test_wait(&a_full[AR::stage(issuer, own + 1)], AR::phase(own + 1));
                 if constexpr (!DUAL_ISSUE) {
-                  a_seen = mbar_test_wait(&a_full[AR::stage(0, own + 1)], AR::phase(own + 1));
                   if (mt == mc - 1 && b_last_use) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);
                   if constexpr (T::sw_scale) r_seen = mbar_test_wait(&tm_empty[(rt + 1) % RAW_SLOTS], (((rt + 1) / RAW_SLOTS) & 1) ^ 1);
                 }
@@ -769,12 +773,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 if constexpr (T::block_scaled) {
                   // scale factors: shared memory -> TMEM, in issue order ahead of the MMAs that read them
                   constexpr int BLOCKS = KIND == Kind::NVFP4 ? 4 : 1;   // 512-byte blocks per stage and operand
-                  sfa_col = SF_COL0 + (it_a & 1) * 16;
-                  sfb_col = SF_COL0 + 32 + (kb & 1) * 16;
+                  sfa_col = sf_base + (own & 1) * 16;
+                  sfb_col = sf_base + 32 + (kb & 1) * 16;
                   const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
 #pragma unroll
                   for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
-                  if (mt == 0) {
+                  if (mt == (DUAL_ISSUE ? static_cast<int>(issuer) : 0)) {   // this issuer's first tile of the K atom
                     const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + (KIND == Kind::NVFP4 ? bx * SF_ATOM_BYTES : 0));
 #pragma unroll
                     for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));
