@@ -132,7 +132,7 @@ int ag_m_grouped_fp8_gemm_nt(const ag_gemm_desc_t* desc);
  * (use_ue8m0=True); no per-block arithmetic in the drain, so it is the faster path when rows per expert are many.
  * `sfa` and `sfb` are DEVICE buffers in the blocked layout written by ag_fp8_sf_to_blocked_ue8m0 (sfa: groups = 1, rows =
  * all rows of A, rows_per_scale = 1; sfb: groups = G, rows = N, rows_per_scale = 128). Segments must start on multiples
- * of 128 rows; masked M_max % 128 == 0; tile_config 0, 1 or 4. */
+ * of 128 rows; masked M_max % 128 == 0; tile_config 0, 1, 4 or 7. */
 int ag_m_grouped_fp8_ue8m0_gemm_nt(const ag_gemm_desc_t* desc);
 uint64_t ag_fp8_sf_blocked_bytes(int64_t groups, int64_t rows, int64_t kb);
 int ag_fp8_sf_to_blocked_ue8m0(const float* src, void* dst, int64_t groups, int64_t rows, int64_t kb, int32_t rows_per_scale, void* stream);
