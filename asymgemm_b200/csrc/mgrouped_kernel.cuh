@@ -586,6 +586,10 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const WaitCtx wc{p.status, abort_flag, p.timeout_ns};
   const int kb_count = p.kb_count;                       // 128-byte K atoms
   const int ks_count = (kb_count + KA - 1) / KA;         // B stages along K
+  // Tile ownership may alternate between chunks only while the two issuers cannot drift a whole chunk apart: both release
+  // every weight stage, so they stay within SB stages of each other, and a chunk must be at least that long. (An issuer that
+  // met an accumulator slot's barrier only every other chunk could otherwise be two phases away from it.)
+  const bool flip_ok = ks_count >= SB;
 
   if (warp < 4) {
   if (warp == 0) {
@@ -671,7 +675,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // so the issue cost of one lane's barrier test and TMA instruction overlaps with the other's).
     if (lane < (DUAL_ISSUE ? 2 : 1)) {
       const uint32_t me = lane;
-      uint32_t it_a = 0, used = 0;   // steps so far: all, and those of this lane's issuer
+      uint32_t it_a = 0, used = 0, chunk_no = 0;   // steps so far: all, and those of this lane's issuer; chunks so far
       bool ok = true;
       ItemCursor cursor(work.segs);
       for (int wi = 0; ok; ++wi) {
@@ -679,11 +683,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
-        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
+        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES, ++chunk_no) {
           const int mc = min(CHUNK_TILES, mtiles - m0);
+          const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
-              const uint32_t user = DUAL_ISSUE ? ((T::sw_scale ? it_a : static_cast<uint32_t>(mt)) & 1u) : 0u;   // as in the issuer role
+              const uint32_t user = DUAL_ISSUE ? ((T::sw_scale ? it_a : static_cast<uint32_t>(mt) + flip) & 1u) : 0u;   // as in the issuer role
               if (user != me) continue;
               const uint32_t s = AR::stage(user, used);
               ok = wait_bar(&a_empty[s], AR::phase(used) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
@@ -716,7 +721,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // The block-scaled kinds stay with one issuer: their scale copies into TMEM are ordered with the MMAs by issue order.
     if (lane == 0) {
       const uint32_t issuer = warp - 2;
-      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0;   // own: steps this issuer has taken
+      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0, chunk_no = 0;   // own: steps this issuer has taken
       bool ok = true;
       ItemCursor cursor(work.segs);
       // the operand descriptors are the descriptor of stage 0 plus an offset in its address field
@@ -731,8 +736,12 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mtiles = (it.rows + BM - 1) / BM;
-        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES) {
+        for (int m0 = 0; m0 < mtiles && ok; m0 += CHUNK_TILES, ++chunk_no) {
           const int mc = min(CHUNK_TILES, mtiles - m0);
+          // With accumulators in TMEM a row tile belongs to one issuer for the whole chunk; which one alternates from chunk to
+          // chunk, because tile 0 exists in every chunk and tile 1 only in full ones (fixed ownership left one issuer with
+          // up to two thirds of the steps).
+          const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;
           for (int kb = 0; kb < kb_count && ok; ++kb) {
             const uint32_t sb = jt % SB;
             const int bx = kb % KA;
@@ -747,7 +756,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const bool b_last_use = bx == KA - 1 || kb == kb_count - 1;   // the stage is released after this K atom
             const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage + bx * L::b_box) >> 4);
             for (int mt = 0; mt < mc; ++mt, ++it_a) {
-              const bool mine = !DUAL_ISSUE || ((T::sw_scale ? rt : static_cast<uint32_t>(mt)) & 1u) == issuer;
+              const bool mine = !DUAL_ISSUE || ((T::sw_scale ? rt : static_cast<uint32_t>(mt) + flip) & 1u) == issuer;
               if (mine) {
                 const uint32_t sa = AR::stage(issuer, own);
                 if (!a_seen) ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
@@ -778,7 +787,7 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   const uint32_t sfa_addr = smem_u32(smem_sfa + sa * L::sfa_stage);
 #pragma unroll
                   for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfa_col + 4 * j, make_sf_desc(sfa_addr + j * SF_BLOCK_BYTES));
-                  if (mt == (DUAL_ISSUE ? static_cast<int>(issuer) : 0)) {   // this issuer's first tile of the K atom
+                  if (mt == (DUAL_ISSUE ? static_cast<int>(issuer ^ flip) : 0)) {   // this issuer's first tile of the K atom
                     const uint32_t sfb_addr = smem_u32(smem_sfb + sb * L::sfb_stage + (KIND == Kind::NVFP4 ? bx * SF_ATOM_BYTES : 0));
 #pragma unroll
                     for (int j = 0; j < BLOCKS; ++j) tmem_cp_32x128b_warpx4(tmem_base + sfb_col + 4 * j, make_sf_desc(sfb_addr + j * SF_BLOCK_BYTES));

@@ -164,6 +164,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t tmem_base = *tmem_base_smem;
   const WaitCtx wc{p.status, abort_flag, p.timeout_ns};
   const int kb_count = p.kb_count;
+  const bool flip_ok = kb_count >= SB;   // the issuers stay within SB weight stages of each other: a chunk must be at least that long
 
   // the same barrier in the first CTA (where both CTAs' loads and drain arrivals are counted) and in the other CTA
   auto in_first = [&](uint64_t* bar) { return map_to_cta(smem_u32(bar), 0); };
@@ -191,7 +192,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ===================================================================== activation producer: this CTA's 128 rows of each tile
     if (lane == 0) {
-      uint32_t it_a = 0, used0 = 0, used1 = 0;   // steps so far: all, and per issuer (ARing)
+      uint32_t it_a = 0, used0 = 0, used1 = 0, chunk_no = 0;   // steps so far: all, and per issuer (ARing); chunks so far
       bool ok = true;
       ItemCursor cursor(work.segs);
       for (int wi = 0; ok; ++wi) {
@@ -199,9 +200,11 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);      // 256-row tiles of the pair in this chunk (<= MT)
+        const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;
+        ++chunk_no;
         for (int kb = 0; kb < kb_count && ok; ++kb) {
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
-            const uint32_t user = (T::sw_scale ? it_a : static_cast<uint32_t>(mt)) & 1u;   // as in the issuer role
+            const uint32_t user = (T::sw_scale ? it_a : static_cast<uint32_t>(mt) + flip) & 1u;   // as in the issuer role
             uint32_t& used = user ? used1 : used0;
             const uint32_t s = AR::stage(user, used);
             ok = wait_bar(&a_empty[s], AR::phase(used) ^ 1, wc, ST_TIMEOUT_A_EMPTY);
@@ -220,7 +223,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // with register accumulators the K blocks alternate (each into its own raw slot, and each weight stage has one user).
     if (lane == 0 && rank == 0) {
       const uint32_t issuer = warp - 2;
-      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0;   // own: steps this issuer has taken
+      uint32_t it_a = 0, own = 0, jt = 0, rt = 0, slot_phase = 0, chunk_no = 0;   // own: steps this issuer has taken
       bool ok = true;
       ItemCursor cursor(work.segs);
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
@@ -230,6 +233,8 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);
+        const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;   // tile ownership alternates between chunks (see the single-CTA kernel)
+        ++chunk_no;
         for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
           const uint32_t sb = jt % SB;
           const bool b_mine = !T::sw_scale || (rt & 1u) == issuer;
@@ -237,7 +242,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (!ok) break;
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage) >> 4);
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
-            const bool mine = ((T::sw_scale ? rt : static_cast<uint32_t>(mt)) & 1u) == issuer;
+            const bool mine = ((T::sw_scale ? rt : static_cast<uint32_t>(mt) + flip) & 1u) == issuer;
             if (mine) {
               const uint32_t sa = AR::stage(issuer, own);
               ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
