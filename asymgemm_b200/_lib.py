@@ -101,6 +101,7 @@ EXPORTS = [
     "ag_link_probe_run",
     "ag_link_probe_destroy",
     "ag_selftest_wait_limit",
+    "ag_probe_mma_issue",
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
     "ag_silu_mul_quant_fp8_upto",
@@ -204,6 +205,8 @@ def load() -> ctypes.CDLL:
     lib.ag_combine_topk_f32.restype = c_int32
     lib.ag_selftest_wait_limit.argtypes = [c_uint32, c_void_p, c_void_p]
     lib.ag_selftest_wait_limit.restype = c_int32
+    lib.ag_probe_mma_issue.argtypes = [c_int32, c_int32, c_int32, ctypes.POINTER(ctypes.c_double)]
+    lib.ag_probe_mma_issue.restype = c_int32
     lib.ag_prefetch_staged_weights.argtypes = [c_void_p, c_uint64, c_int32, c_void_p, c_uint64, c_uint64, c_void_p, c_int32]
     lib.ag_prefetch_staged_weights.restype = c_int32
     lib.ag_prepare_weights.argtypes = [c_void_p, c_uint64, c_int32]

@@ -326,6 +326,15 @@ int ag_ep_return(const void* out, const int64_t* my_meta, const int32_t* rows_us
  * (csrc/ep_steal/ep_steal_sync.cu:63-64) and whose device asserts trap (asym_gemm/include/asym_gemm/common/utils.cuh:24-40). */
 int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
 
+/* Issue-rate probe of the tensor core, on every SM of the current device: `issuers` (1 or 2) threads per CTA each run the
+ * inner sequence of the kernels' MMA role -- wait for an operand stage, four tcgen05.mma of M128 x N`n_cols` (128 or 256) x K16
+ * in bf16, commit -- for `steps` steps against producers that only arrive on the barriers (no loads; the operands are
+ * whatever shared memory holds, the accumulators are discarded). *cycles_per_step = SM cycles per step of four MMAs, worst
+ * CTA; the tensor core's own time for a step is 2 * n_cols cycles. Synchronous (allocates two small device buffers, frees
+ * them before it returns); every wait inside is bounded. Reference counterpart: none -- this is the measurement behind the
+ * two MMA-issuing threads of the kernels. */
+int ag_probe_mma_issue(int32_t issuers, int32_t n_cols, int32_t steps, double* cycles_per_step);
+
 /* Copy-only ceiling for SM-issued reads of pinned memory: streams a `bytes` pinned buffer laid out as rows of `row_bytes`
  * through shared memory with the weight producer's TMA pattern (each CTA owns columns of `box_rows` rows and walks K in
  * 128-byte boxes, `boxes_per_stage` per stage) on `num_ctas` CTAs (0 = all SMs), best of `reps`. Reference counterpart:

@@ -629,3 +629,15 @@ def test_more_items_per_cta_than_the_shared_memory_table(kind, b_on_host):
     d_np = d.float().cpu().numpy()
     _check(kind, d_np, c["ref"], c["segments"])
     assert np.isnan(d_np[~H.valid_row_mask(c["segments"], c["m_total"])]).all()
+
+
+def test_two_issuers_keep_the_tensor_core_busy_where_one_does_not():
+    """The issue-rate probe behind the kernels' two MMA-issuing threads: with the issuer's own instruction sequence and no
+    loads, two threads reach the tensor core's rate for 256-column MMAs (512 cycles per step of four); one thread needs
+    more cycles per step than two."""
+    from asymgemm_b200.testing import probes
+    one, two = probes.mma_issue_cycles(1, 256), probes.mma_issue_cycles(2, 256)
+    assert 500.0 <= two <= 540.0, (one, two)
+    assert one >= two - 1.0, (one, two)
+    with pytest.raises(RuntimeError, match="issuers must be 1 or 2"):
+        probes.mma_issue_cycles(3)
