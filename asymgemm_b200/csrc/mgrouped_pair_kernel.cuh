@@ -406,6 +406,14 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
 
   // ===================================================================== common exit: both CTAs are done before TMEM goes
+  if (*abort_flag) {
+    // A wait of this CTA ran out. Loads of its producers and MMAs of the pair may still be in flight, and their completion
+    // is counted on barriers of the first CTA, which the second cannot wait on: give them a fixed 200 us (they take a few)
+    // before shared memory and TMEM are given back.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();
