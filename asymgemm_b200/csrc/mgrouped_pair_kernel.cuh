@@ -228,6 +228,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       ItemCursor cursor(work.segs);
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a));
       const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
+      bool a_seen = false, b_seen = false;   // the barrier of this issuer's coming step was already complete (tested ahead)
       for (int wi = 0; ok; ++wi) {
         Item it;
         if (!get_item(p, work, wi, cursor, it)) break;
@@ -238,14 +239,15 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
           const uint32_t sb = jt % SB;
           const bool b_mine = !T::sw_scale || (rt & 1u) == issuer;
-          if (b_mine) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+          if (b_mine && !b_seen) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
+          b_seen = false;
           if (!ok) break;
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * L::b_stage) >> 4);
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
             const bool mine = ((T::sw_scale ? rt : static_cast<uint32_t>(mt) + flip) & 1u) == issuer;
             if (mine) {
               const uint32_t sa = AR::stage(issuer, own);
-              ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
+              if (!a_seen) ok = wait_bar(&a_full[sa], AR::phase(own), wc, ST_TIMEOUT_A_FULL);
               if (!ok) break;
               uint32_t d_col;
               if constexpr (T::sw_scale) {
@@ -257,6 +259,9 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 d_col = mt * PAIR_BN;
               }
               if (!ok) break;
+              // a look at this issuer's next barriers; the answers are needed only after this step's MMAs are on their way
+              a_seen = mbar_test_wait(&a_full[AR::stage(issuer, own + 1)], AR::phase(own + 1));
+              if constexpr (!T::sw_scale) b_seen = mbar_test_wait(&b_full[(jt + 1) % SB], ((jt + 1) / SB) & 1);   // at most one tile per K atom is this issuer's
               tc_fence_after_sync();
               const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
 #pragma unroll
