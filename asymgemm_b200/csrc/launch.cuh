@@ -103,10 +103,13 @@ cudaError_t launch_one(int grid, cudaStream_t stream, const CUtensorMap& ma, con
 // The pair kernel: `grid` counts CTAs and is even; clusters of two are a compile-time attribute of the kernel.
 template <Kind KIND>
 cudaError_t launch_pair(int grid, cudaStream_t stream, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p) {
-  constexpr int SA = KindTraits<KIND>::sw_scale ? 6 : 8, SB = KindTraits<KIND>::sw_scale ? 6 : 4;
-  using L = PairSmem<SA, SB>;
+  // BF16: stages of two K atoms (8 MMAs per barrier round trip and commit: the commits that go to both CTAs are what the
+  // issuers of a pair spend most on), two per issuer for the activations, two for the weights; FP8 / INT8: single atoms
+  constexpr bool sw = KindTraits<KIND>::sw_scale;
+  constexpr int SA = sw ? 6 : 4, SB = sw ? 6 : 2, KA = sw ? 1 : 2;
+  using L = PairSmem<SA, SB, KA>;
   static_assert(L::dyn_bytes <= 232448, "pair configuration does not fit in shared memory");
-  auto kernel = mgrouped_pair_kernel<KIND, SA, SB>;
+  auto kernel = mgrouped_pair_kernel<KIND, SA, SB, KA>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

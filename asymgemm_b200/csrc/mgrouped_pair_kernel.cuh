@@ -88,10 +88,12 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(uint32_t d_fmt, uint32_t 
 constexpr int PAIR_BN = 256;          // columns of the pair's tile
 constexpr int PAIR_THREADS = 384;
 
-template <int SA, int SB>
+template <int SA, int SB, int KA>
 struct PairSmem {
-  static constexpr int a_stage = BM * ATOM_BYTES;                 // 128 rows x 128 B of this CTA's activation rows
-  static constexpr int b_stage = (PAIR_BN / 2) * ATOM_BYTES;      // this CTA's 128 of the 256 weight rows
+  static constexpr int a_box = BM * ATOM_BYTES;                   // 128 rows x 128 B of this CTA's activation rows: one K atom
+  static constexpr int b_box = (PAIR_BN / 2) * ATOM_BYTES;        // this CTA's 128 of the 256 weight rows: one K atom
+  static constexpr int a_stage = KA * a_box;                      // a stage holds KA K-adjacent atoms: one barrier round trip and
+  static constexpr int b_stage = KA * b_box;                      // one commit per KA x 4 MMAs
   static constexpr int a_off = 0;
   static constexpr int b_off = SA * a_stage;
   static constexpr int bar_off = b_off + SB * b_stage;
@@ -109,11 +111,12 @@ struct PairSmem {
 template <Kind KIND>
 __host__ __device__ constexpr int pair_tiles_per_cta() { return KindTraits<KIND>::sw_scale ? 1 : 2; }
 
-template <Kind KIND, int SA, int SB>
+template <Kind KIND, int SA, int SB, int KA>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using T = KindTraits<KIND>;
-  using L = PairSmem<SA, SB>;
+  using L = PairSmem<SA, SB, KA>;
+  static_assert(!T::sw_scale || KA == 1, "software scaling hands every 128-byte K block to the drain");
   static_assert(!T::block_scaled, "the pair kernel serves BF16, FP8 (exact scales) and INT8");
   constexpr int MT = pair_tiles_per_cta<KIND>();               // row tiles per CTA and item
   constexpr int SLOTS = TMEM_COLS / PAIR_BN;                   // 2: accumulators (BF16) or raw products (FP8 / INT8)
@@ -163,8 +166,9 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_smem;
   const WaitCtx wc{p.status, abort_flag, p.timeout_ns};
-  const int kb_count = p.kb_count;
-  const bool flip_ok = kb_count >= SB;   // the issuers stay within SB weight stages of each other: a chunk must be at least that long
+  const int kb_count = p.kb_count;                       // 128-byte K atoms
+  const int ks_count = (kb_count + KA - 1) / KA;         // stages along K (atoms past the end of K arrive as zeros and are not multiplied)
+  const bool flip_ok = ks_count >= SB;   // the issuers stay within SB weight stages of each other: a chunk must be at least that long
 
   // the same barrier in the first CTA (where both CTAs' loads and drain arrivals are counted) and in the other CTA
   auto in_first = [&](uint64_t* bar) { return map_to_cta(smem_u32(bar), 0); };
@@ -180,12 +184,14 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (!get_item(p, work, wi, cursor, it)) break;
         if (it.rows <= 0) continue;
         const int b_row = (it.expert - p.expert_lo) * p.n + it.nt * PAIR_BN + static_cast<int>(rank) * (PAIR_BN / 2);
-        for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+        for (int ks = 0; ks < ks_count && ok; ++ks, ++jt) {
           const uint32_t s = jt % SB;
           ok = wait_bar(&b_empty[s], ((jt / SB) & 1) ^ 1, wc, ST_TIMEOUT_B_EMPTY);
           if (!ok) break;
           if (rank == 0) mbar_arrive_expect_tx(&b_full[s], STAGE_TX_B);
-          tma_load_2d_pair(smem_b + s * L::b_stage, &tmap_b, in_first(&b_full[s]), kb * ATOM_BYTES, b_row);
+#pragma unroll
+          for (int bx = 0; bx < KA; ++bx)
+            tma_load_2d_pair(smem_b + s * L::b_stage + bx * L::b_box, &tmap_b, in_first(&b_full[s]), (ks * KA + bx) * ATOM_BYTES, b_row);
         }
       }
     }
@@ -202,7 +208,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);      // 256-row tiles of the pair in this chunk (<= MT)
         const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;
         ++chunk_no;
-        for (int kb = 0; kb < kb_count && ok; ++kb) {
+        for (int ks = 0; ks < ks_count && ok; ++ks) {
           for (int mt = 0; mt < mc; ++mt, ++it_a) {
             const uint32_t user = (T::sw_scale ? it_a : static_cast<uint32_t>(mt) + flip) & 1u;   // as in the issuer role
             uint32_t& used = user ? used1 : used0;
@@ -211,7 +217,9 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (!ok) break;
             if (rank == 0) mbar_arrive_expect_tx(&a_full[s], STAGE_TX_A);
             const int a_row = it.row0 + (2 * mt + static_cast<int>(rank)) * BM;
-            tma_load_2d_pair(smem_a + s * L::a_stage, &tmap_a, in_first(&a_full[s]), kb * ATOM_BYTES, a_row);
+#pragma unroll
+            for (int bx = 0; bx < KA; ++bx)
+              tma_load_2d_pair(smem_a + s * L::a_stage + bx * L::a_box, &tmap_a, in_first(&a_full[s]), (ks * KA + bx) * ATOM_BYTES, a_row);
             ++used;
           }
         }
@@ -236,7 +244,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int mc = (it.rows + 2 * BM - 1) / (2 * BM);
         const uint32_t flip = flip_ok ? (chunk_no & 1u) : 0u;   // tile ownership alternates between chunks (see the single-CTA kernel)
         ++chunk_no;
-        for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+        for (int ks = 0; ks < ks_count && ok; ++ks, ++jt) {
           const uint32_t sb = jt % SB;
           const bool b_mine = !T::sw_scale || (rt & 1u) == issuer;
           if (b_mine && !b_seen) ok = wait_bar(&b_full[sb], (jt / SB) & 1, wc, ST_TIMEOUT_B_FULL);
@@ -255,7 +263,7 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 ok = wait_bar(&tm_empty[rs], ((rt / SLOTS) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
                 d_col = rs * PAIR_BN;
               } else {
-                if (kb == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
+                if (ks == 0) ok = wait_bar(&tm_empty[mt], ((slot_phase >> mt) & 1) ^ 1, wc, ST_TIMEOUT_TM_EMPTY);
                 d_col = mt * PAIR_BN;
               }
               if (!ok) break;
@@ -265,17 +273,21 @@ mgrouped_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               tc_fence_after_sync();
               const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((sa * L::a_stage) >> 4);
 #pragma unroll
-              for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
-                const uint32_t acc = T::sw_scale ? (j > 0) : (kb > 0 || j > 0);
-                umma_pair<T::mma>(tmem_base + d_col, a_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)),
-                                  b_desc + static_cast<uint64_t>(j * (MMA_K_BYTES >> 4)), IDESC, acc);
+              for (int bx = 0; bx < KA; ++bx) {
+                if (ks * KA + bx >= kb_count) break;   // past the end of K
+#pragma unroll
+                for (int j = 0; j < ATOM_BYTES / MMA_K_BYTES; ++j) {
+                  const uint32_t acc = T::sw_scale ? (j > 0) : (ks > 0 || bx > 0 || j > 0);
+                  umma_pair<T::mma>(tmem_base + d_col, a_desc + static_cast<uint64_t>((bx * L::a_box + j * MMA_K_BYTES) >> 4),
+                                    b_desc + static_cast<uint64_t>((bx * L::b_box + j * MMA_K_BYTES) >> 4), IDESC, acc);
+                }
               }
               umma_commit_pair(&a_empty[sa]);
               ++own;
               if constexpr (T::sw_scale) {
                 umma_commit_pair(&tm_full[rt % SLOTS]);
               } else {
-                if (kb == kb_count - 1) umma_commit_pair(&tm_full[mt]);
+                if (ks == ks_count - 1) umma_commit_pair(&tm_full[mt]);
               }
             }
             if constexpr (T::sw_scale) ++rt;
