@@ -64,7 +64,8 @@ inline const char* tile_support_text(int kind) {
 constexpr int default_tile(int kind, bool host_b, long long n) {
   if (host_b) return kTileHost;
   if (kind_is_block_scaled(kind)) return kTileDeviceDeepA;   // two issuers, four activation stages each: FP8/UE8M0 1205 against 1140 TFLOP/s
-  if (n >= 256) return kTileDeviceWide;
+  if (n >= 256 && kind != 2) return kTileDeviceWide;   // INT8 keeps 128-column items: int-to-float conversion and per-column scales on top of the
+                                                       // 128 accumulators spill at 256 columns (measured 706 against 344 TFLOP/s)
   return kind_is_sw_scaled(kind) ? kTileDeviceRegAcc : kTileDevice;
 }
 

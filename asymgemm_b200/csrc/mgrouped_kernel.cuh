@@ -884,12 +884,23 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   if (n0 + col_base + c0 + j < p.n) dst[j] = static_cast<int>(r[j]);
               }
             }
+            float col_scale[KIND == Kind::INT8 ? W : 1];
+            if constexpr (KIND == Kind::INT8) {   // this piece's column scales: 16-byte shared-memory reads (the buffer and c0 are aligned)
+#pragma unroll
+              for (int q4 = 0; q4 < W / 4; ++q4) {
+                const float4 v = reinterpret_cast<const float4*>(sfb_buf + c0)[q4];
+                col_scale[4 * q4] = v.x;
+                col_scale[4 * q4 + 1] = v.y;
+                col_scale[4 * q4 + 2] = v.z;
+                col_scale[4 * q4 + 3] = v.w;
+              }
+            }
 #pragma unroll
             for (int j = 0; j < W; ++j) {
               float prod, scale;
               if constexpr (KIND == Kind::INT8) {
                 prod = static_cast<float>(static_cast<int>(r[j]));
-                scale = sa * sfb_buf[c0 + j];
+                scale = sa * col_scale[j];
               } else {
                 prod = __uint_as_float(r[j]);
                 scale = sa * (((c0 + j) & 16) ? sb_up : sb_scalar);   // columns 16..31 of every 32 are up rows when fused
@@ -897,23 +908,30 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               acc[c0 + j] = fmaf(prod, scale, acc[c0 + j]);
             }
           };
+          // INT8: the per-column weight scales of a K block, one per lane and 32 columns, fetched one block ahead like the others
+          float sfc_next[COLS / 32];
+          auto fetch_column_scales = [&](int kb) {
+#pragma unroll
+            for (int j = 0; j < COLS / 32; ++j) {
+              const int col = n0 + col_base + j * 32 + lane;
+              sfc_next[j] = col < p.n ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + col) * p.sf_k + kb) : 0.f;
+            }
+          };
+          if constexpr (KIND == Kind::INT8) fetch_column_scales(0);
           for (int kb = 0; kb < kb_count && ok; ++kb, ++rt) {
             const float sa = sa_next, sb_scalar = sb_next, sb_up = sbu_next;
+            if constexpr (KIND == Kind::INT8) {
+#pragma unroll
+              for (int j = 0; j < COLS / 32; ++j) sfb_buf[j * 32 + lane] = sfc_next[j];
+              __syncwarp();
+            }
             if (kb + 1 < kb_count) {
               sa_next = valid ? __ldg(sfa_row + kb + 1) : 0.f;
               if constexpr (KIND == Kind::FP8) {
                 sb_next = __ldg(sfb_blk + kb + 1);
                 sbu_next = __ldg(sfb_blk_u + kb + 1);
               }
-            }
-            if constexpr (KIND == Kind::INT8) {
-#pragma unroll
-              for (int j = 0; j < COLS / 32; ++j) {
-                const int col = n0 + col_base + j * 32 + lane;
-                sfb_buf[j * 32 + lane] =
-                    col < p.n ? __ldg(p.sfb + (static_cast<long long>(it.expert) * p.sfb_rows + col) * p.sf_k + kb) : 0.f;
-              }
-              __syncwarp();
+              if constexpr (KIND == Kind::INT8) fetch_column_scales(kb + 1);
             }
             const uint32_t rs = rt % RAW_SLOTS;
             ok = wait_bar(&tm_full[rs], (rt / RAW_SLOTS) & 1, wc, ST_TIMEOUT_TM_FULL);

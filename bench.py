@@ -472,9 +472,11 @@ def measure_device_resident(device, peaks, steps=20):
                    "weights resident in HBM; peak = 1590 TFLOP/s bf16 (x2 for 8-bit), of fallback"}
     bf16_peak = peaks.get("bf16_tflops", 1590.0)
     cases = [("fp8", "c3_fp8", False, (0, 5, 6, 8), 2.0, 32), ("fp8_ue8m0", "c3_fp8", True, (0, 7), 2.0, 32),
-             ("bf16", "c2_bf16", False, (0, 1, 6, 7, 8), 1.0, 128)]
+             ("bf16", "c2_bf16", False, (0, 1, 6, 7, 8), 1.0, 128), ("int8", "c3_fp8", False, (0, 5), 2.0, 32)]
     for name, wl, ue, tiles, mult, experts in cases:
         cfg = dict(WORKLOADS[wl])
+        if name == "int8":
+            cfg["kind"] = "int8"      # the FP8 configuration's shapes with INT8 operands and per-channel weight scales
         cfg["tokens"] = max(1, cfg["tokens"] * experts // cfg["experts"])
         cfg["experts"] = experts
         w = build_workload(cfg, 0, 1, device, weights_on_device=True, ue8m0=ue)
@@ -496,7 +498,7 @@ def measure_device_resident(device, peaks, steps=20):
         peak = mult * bf16_peak
         out[name] = {"tflops": round(best[0], 1), "ms_per_step": round(best[2], 4), "tile_config": best[1], "peak_tflops": round(peak, 1),
                      "frac": round(best[0] / peak, 4), "by_tile_config": per_tile,
-                     "workload": f"{wl} with {experts} experts: K={cfg['k']}, N={cfg['n']}, {w['valid_rows']} rows"}
+                     "workload": f"{wl} with {experts} experts{' and int8 operands' if name == 'int8' else ''}: K={cfg['k']}, N={cfg['n']}, {w['valid_rows']} rows"}
         del w
         torch.cuda.empty_cache()
     # NVFP4 (masked layout, scales applied by the tensor core): the C4 configuration cut to 32 experts, weights moved to HBM
