@@ -15,6 +15,8 @@
 //   * no atomics, no partial sums in D: every output element is written once, from fp32;
 //   * when B is device-resident there is no link to spare, so long segments are split into accumulator-sized row
 //     chunks that become items of their own (fetch_item, split mode) and spread over all CTAs.
+//   * which items a CTA takes is worked out once, by all of its threads, into a table in shared memory (build_work_list);
+//     the roles read one entry per item instead of walking the segment list.
 //
 // Tile shape is chosen by where B lives. Streaming from the host, throughput drops once the rows being streamed at
 // the same time (CTAs x BN) spread over more than a few thousand 4 KB host pages (measured: 148 CTAs x 128 rows ->
@@ -27,7 +29,7 @@
 // scale in fp32 (block scales are arbitrary fp32 numbers) and add to accumulators kept in TMEM, or in registers (REG_ACC).
 //
 // Warp roles: warp 0 = B producer (+ scratch spill), warp 1 = A producer (one lane per MMA issuer), warp 2 = TMEM allocator,
-// warps 2 and 3 = one tcgen05.mma-issuing thread each (one issuer for the block-scaled kinds), warps 4-7 (and 8-11 where a
+// warps 2 and 3 = one tcgen05.mma-issuing thread each (one issuer for block-scaled 64-column tiles), warps 4-7 (and 8-11 where a
 // second drain warpgroup pays, see drain_wgs_of) = TMEM drain.
 //
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the CTA records a status code, raises a
