@@ -549,6 +549,8 @@ class ExpertParallelMoE:
         state = DispatchState(None, [], [], None, None, px.cap_rows, px.offsets, px.experts, tokens, top_k)
         self._mark("layout")
         out = self.experts_forward(a_q, px.sfa, state, rows_used=px.rows_used[:1])
+        if self.prefetch_next is not None and out.is_cuda:      # staged weight path: start the next call's first copies now
+            api.prefetch_weights(self.prefetch_next, out.device)
         if px.pair_row is not None:      # one rank: every result already lies in this rank's memory
             self._mark("return")
             y = moe_ops.combine_topk(out, px.pair_row, topk_weights, tokens, top_k)

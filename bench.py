@@ -632,6 +632,26 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
     ms = peer_ms if chosen == "peer" else nccl_ms
     if chosen == "peer":
         layer = peer_layer
+    # The same layer with the weights moved by the copy engine through an 8-slot ring in HBM that the layer prefetches into
+    # while tokens are routed, exchanged and combined (set_weight_path("staged")): the transport the reference's runtime uses.
+    staged_ms = staged_same = None
+    if args.weights == "host" and not (args.pipeline_groups > 1 and world > 1):
+        ag.set_weight_path("staged", chunk_bytes=args.stage_mb << 20, slots=8)
+        layer.prefetch_next = layer.w13[0]
+        try:
+            for _ in range(2):
+                y_staged = step()
+            ag.check_status()
+            staged_ms = timed(step, steps, barrier)
+            ag.check_status()
+            flags = torch.tensor([staged_ms, 0.0 if torch.equal(y_staged, y) else 1.0], dtype=torch.float64, device=device)
+            if world > 1:
+                dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+            staged_ms, staged_same = flags[0].item(), flags[1].item() == 0.0
+        finally:
+            layer.prefetch_next = None
+            ag.set_weight_path("stream", chunk_bytes=args.stage_mb << 20, slots=args.stage_slots)
+            torch.cuda.synchronize(device)
     # per-phase breakdown: two more steps with events at the phase boundaries (unpipelined path only)
     phases = None
     if not (args.pipeline_groups > 1 and world > 1):
@@ -688,6 +708,11 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
     }
     rec["activation"] = ("SiLU*mul fused into the gate+up GEMM's drain (weights stored with gate / up rows interleaved)" if w["fused"]
                          else "separate SiLU*mul + requantisation kernel")
+    if staged_ms is not None:
+        rec["copy_engine_staged_ring"] = {"ms_per_step": round(staged_ms, 3), "weight_gbs": round(sm[2].item() / (staged_ms * 1e-3) / 1e9, 2),
+                                          "outputs_bit_equal": staged_same,
+                                          "note": "same layer and exchange with set_weight_path('staged', slots=8) and the layer's prefetch of its "
+                                                  "gate+up weights during routing / exchange / combine; the record's own numbers are the in-kernel stream"}
     if peer_error is not None:
         rec["peer_exchange_unavailable"] = peer_error
     if peer_ms is not None:
