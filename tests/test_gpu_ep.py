@@ -90,10 +90,15 @@ def _case(rank, world, device, weight_path="stream"):
         import asymgemm_b200 as ag
         ag.set_weight_path("staged", chunk_bytes=3 * 2 * inter * hidden, slots=3)      # three gate+up experts per chunk
         layer.prefetch_next = layer.w13[0]     # the next call finds its first chunks already in the ring
+        peer2 = ep.ExpertParallelMoE(num_experts, hidden, inter, layer.w13, layer.w2, exchange="peer",
+                                     max_tokens=300 + 17 * (world - 1), top_k=top_k)
+        peer2.prefetch_next = layer.w13[0]     # and the same through the peer-memory exchange
         try:
             assert torch.equal(layer.forward(x, ids, wts), y) and torch.equal(layer.forward(x, ids, wts), y)
+            assert torch.equal(peer2.forward(x, ids, wts), y) and torch.equal(peer2.forward(x, ids, wts), y), "peer exchange, staged weights"
         finally:
             layer.prefetch_next = None
+            peer2.peer.close()
             ag.set_weight_path("stream", chunk_bytes=128 << 20, slots=2)
     ref = _dense_reference(x, ids, wts, w13.to(device), s13.to(device), w2.to(device), s2.to(device), inter)
     err = float((y.float() - ref).abs().max() / ref.abs().max())
