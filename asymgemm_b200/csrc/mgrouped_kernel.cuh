@@ -946,11 +946,11 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               __syncwarp();
               if (lane == 0) mbar_arrive(&tm_empty[rs]);
             };
-            if constexpr (COLS >= 128) {
-              // 128 accumulator registers per thread leave room for 16 staging registers: two buffers of 8 columns, so that the
-              // load of the next piece is in flight while this one is scaled and added (one buffer of 16 left the warp idle
-              // for a TMEM round trip eight times per K block)
-              constexpr int LW = 8, NP = COLS / LW;
+            {
+              // Two staging buffers, so that the load of the next piece is in flight while this one is scaled and added (one buffer
+              // left the warp idle for a TMEM round trip per piece). 128 accumulator registers per thread leave room for two
+              // buffers of 8 columns, 64 accumulators for two of 16.
+              constexpr int LW = COLS >= 128 ? 8 : 16, NP = COLS / LW;
               uint32_t ra[LW], rb[LW];
               tmem_ld_cols(raw_addr, ra);
               auto step = [&](auto cc_tag) {
@@ -963,17 +963,6 @@ mgrouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 accumulate(cur, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, sb_up, kb);
               };
               for_each_index(std::make_integer_sequence<int, NP>{}, step);
-            } else {
-              constexpr int LW = 32;
-              auto piece = [&](auto cc_tag) {
-                constexpr int cc = decltype(cc_tag)::value;
-                uint32_t r[LW];
-                tmem_ld_cols(raw_addr + cc * LW, r);
-                tmem_wait_ld();
-                if (cc == COLS / LW - 1) release_slot();
-                accumulate(r, std::integral_constant<int, cc * LW>{}, sa, sb_scalar, sb_up, kb);
-              };
-              for_each_index(std::make_integer_sequence<int, COLS / LW>{}, piece);
             }
             if constexpr (KIND == Kind::INT8) __syncwarp();  // everyone is done with sfb_buf before the next block refills it
           }
