@@ -59,7 +59,7 @@ class GemmDesc(Structure):
         ("stage", c_void_p),
         ("stage_bytes", c_uint64),
         ("stage_chunk_bytes", c_uint64),
-        ("epilogue", c_int32),
+        ("epilogue", c_int32), ("scatter_meta", c_void_p), ("scatter_bases", c_void_p),
     ]
 
 

@@ -318,7 +318,7 @@ def _stage_buffer(b: torch.Tensor, g: int, device: torch.device) -> Tuple[torch.
 
 def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=None, experts=None, max_segments=0,
             masked_m=None, m: int, n: int, k: int, g: int, raw_dump=None, alpha: float = 1.0,
-            rows_hint: Optional[int] = None, epilogue: int = 0) -> None:
+            rows_hint: Optional[int] = None, epilogue: int = 0, scatter=None) -> None:
     """Every operator ends here: one call of the torch extension's op, which fills the C descriptor from the tensors and
     launches on the current stream of a's device (csrc/torch_ops.cpp). `rows_hint`: rows the call is expected to
     multiply (masked layout: expected_m * groups; contiguous: m), for the "auto" weight path."""
@@ -329,7 +329,7 @@ def _launch(kind: int, fn_name: str, *, layout: int, a, sfa, b, sfb, d, offsets=
     with torch.cuda.device(dev):
         op(kind, layout, a, sfa, b, sfb, d, offsets, experts, max_segments, masked_m, m, n, k, g, _scratch(kind, n, k, dev),
            _status_word(dev), _state["timeout_ms"], raw_dump, alpha, _state["tile_config"], _state["no_split"], stage, slot_bytes,
-           getattr(_call_caps, "num_sms", 0), epilogue)
+           getattr(_call_caps, "num_sms", 0), epilogue, None if scatter is None else scatter[0], None if scatter is None else scatter[1])
 
 
 def _check_index_tensors(offsets, experts, g):
@@ -405,7 +405,8 @@ def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], 
                                           offsets, experts, list_size=None,
                                           recipe: Optional[Tuple[int, int, int]] = None, compiled_dims: str = "nk",
                                           disable_ue8m0_cast: bool = False, *, ue8m0_scales: Optional[bool] = None,
-                                          epilogue: Optional[str] = None) -> None:
+                                          epilogue: Optional[str] = None,
+                                          scatter: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
     """FP8 E4M3 with 1x128 (A) and 128x128 (B) fp32 scales, bf16 out (csrc/apis/gemm.hpp:81-157).
 
     ``ue8m0_scales`` (extension): True = apply the scales in the tensor core as power-of-two factors (the reference's
@@ -413,6 +414,9 @@ def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], 
     ``epilogue="silu_mul"`` (extension, exact-scale mode only): the gate+up GEMM of an MoE layer with its activation fused
     into the drain: `b` holds gate and up rows interleaved in groups of 16 (`ep.interleave_gate_up`), `d` is bf16
     [M, N/2] = bf16(silu(gate) * up) -- the bits the unfused GEMM plus the activation kernel produce.
+    ``scatter=(meta, bases)`` (extension): result row r goes to row ``meta[r] & 0xffffffff`` of the buffer at address
+    ``bases[meta[r] >> 32]`` instead of ``d[r]`` (int64 CUDA tensors; negative entries drop the row); the buffers may be
+    peer memory -- the expert-parallel layer's down GEMM sends its results home this way (`scatter_meta` of the C descriptor).
     """
     _require(epilogue in (None, "silu_mul"), "epilogue must be None or 'silu_mul'")
     fused = epilogue == "silu_mul"
@@ -422,11 +426,15 @@ def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], 
     if m == 0:
         return
     segs = _list_size_to_segments(list_size, offsets, experts)
+    if scatter is not None:
+        _require(len(scatter) == 2 and all(t.is_cuda and t.dtype == torch.int64 and t.is_contiguous() for t in scatter),
+                 "scatter must be (meta, bases): contiguous int64 CUDA tensors")
+        _require(scatter[0].numel() >= m, "scatter meta needs one entry per row of a")
     if fused:
         _require(not _fp8_use_hw(ue8m0_scales), "the fused SiLU*mul epilogue exists for the exact fp32-scale mode only")
         _require(n % 256 == 0 and d.dtype == torch.bfloat16, "the fused SiLU*mul epilogue needs n % 256 == 0 and a bf16 d")
         _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
-                offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, epilogue=_lib.EPILOGUE_SILU_MUL)
+                offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, epilogue=_lib.EPILOGUE_SILU_MUL, scatter=scatter)
         return
     if _fp8_use_hw(ue8m0_scales):
         kb, dev = (k + 127) // 128, a[0].device
@@ -434,10 +442,10 @@ def m_grouped_fp8_asym_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], 
         cacheable = b[1].is_contiguous() and (b[1].is_cuda or b[1].is_pinned())
         sfb_b = _fp8_blocked_ue8m0(b[1] if cacheable else sfb, g, n, kb, 128, dev, cache=cacheable)
         _launch(_lib.KIND_FP8_UE8M0, "ag_m_grouped_fp8_ue8m0_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa_b, b=b[0], sfb=sfb_b,
-                d=d, offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
+                d=d, offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, scatter=scatter)
         return
     _launch(_lib.KIND_FP8, "ag_m_grouped_fp8_gemm_nt", layout=_lib.LAYOUT_CONTIGUOUS, a=a[0], sfa=sfa, b=b[0], sfb=sfb, d=d,
-            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g)
+            offsets=offsets, experts=experts, max_segments=segs, m=m, n=n, k=k, g=g, scatter=scatter)
 
 
 def m_grouped_fp8_asym_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, compiled_dims: str = "nk",

@@ -270,6 +270,13 @@ int run(int kind, const ag_gemm_desc_t* g, int win_lo = 0, int win_n = -1) {
   p.split_rows = plan.split_rows;
   p.epilogue = g->epilogue;
   p.d_cols = g->epilogue == AG_EPILOGUE_SILU_MUL ? static_cast<int>(g->n / 2) : static_cast<int>(g->n);
+  AG_REQUIRE((g->scatter_meta == nullptr) == (g->scatter_bases == nullptr), "scatter_meta and scatter_bases go together");
+  if (g->scatter_meta != nullptr) {
+    AG_REQUIRE(!masked, "the result scatter exists for the contiguous layout");
+    AG_REQUIRE(kind != 2 || g->raw_dump == nullptr, "raw_dump and the result scatter cannot be combined");
+  }
+  p.scatter_meta = reinterpret_cast<const long long*>(g->scatter_meta);
+  p.scatter_bases = reinterpret_cast<const long long*>(g->scatter_bases);
 
   // Replay from scratch needs the whole amount; with less (or none) long segments re-read their weight column from b.
   p.use_scratch = (g->scratch != nullptr && need > 0 && g->scratch_bytes >= need) ? 1 : 0;

@@ -92,7 +92,19 @@ struct GemmParams {
                            // gate columns 16q.., rows 32q+16..32q+31 = the same up columns) and the drain writes bf16(silu(gate) * up)
                            // into d [rows, n / 2] instead of the raw product
   int d_cols;              // row length of d in elements: n, or n / 2 with the fused activation
+  const long long* scatter_meta;    // optional, per row of the product: (buffer index << 32) | row in that buffer, negative = drop
+  const long long* scatter_bases;   // optional: addresses of the destination buffers (local or peer memory); both or neither
 };
+
+// Where row `grow` of the product goes: d's own row, or -- with a scatter table -- the row its entry names in one of the
+// destination buffers (the expert-parallel layer's combine buffers on the ranks the tokens came from). Null = not stored.
+__device__ __forceinline__ void* result_row(const GemmParams& p, long long grow, int elem_bytes) {
+  if (p.scatter_meta == nullptr) return static_cast<char*>(p.d) + grow * p.d_cols * elem_bytes;
+  const long long m = __ldg(p.scatter_meta + grow);
+  if (m < 0) return nullptr;
+  char* base = reinterpret_cast<char*>(static_cast<uintptr_t>(__ldg(p.scatter_bases + (m >> 32))));
+  return base + (m & 0xffffffffLL) * p.d_cols * elem_bytes;
+}
 
 struct Item {
   int expert;
@@ -443,7 +455,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Store 32 consecutive output columns of one row. `vals` are fp32 bit patterns.
 __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow, int col0, const uint32_t (&vals)[32]) {
   if (p.d_fp32) {
-    float* dst = reinterpret_cast<float*>(p.d) + grow * p.d_cols + col0;
+    float* row = static_cast<float*>(result_row(p, grow, 4));
+    if (row == nullptr) return;
+    float* dst = row + col0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (col0 + j * 4 < p.n) {
@@ -452,7 +466,9 @@ __device__ __forceinline__ void store_row32(const GemmParams& p, long long grow,
       }
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.d_cols + col0;
+    __nv_bfloat16* row = static_cast<__nv_bfloat16*>(result_row(p, grow, 2));
+    if (row == nullptr) return;
+    __nv_bfloat16* dst = row + col0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (col0 + j * 8 < p.n) {
@@ -487,7 +503,9 @@ __device__ __forceinline__ void store_silu_mul16(const GemmParams& p, long long 
     }
     packed[j] = pack_bf16(act[0], act[1]);
   }
-  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + grow * p.d_cols + (col0 >> 1);
+  __nv_bfloat16* row = static_cast<__nv_bfloat16*>(result_row(p, grow, 2));
+  if (row == nullptr) return;
+  __nv_bfloat16* dst = row + (col0 >> 1);
   *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
 }

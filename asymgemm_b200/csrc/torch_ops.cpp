@@ -28,7 +28,7 @@ void m_grouped_gemm_nt(int64_t kind, int64_t layout, const at::Tensor& a, const 
                        int64_t max_segments, const OptTensor& masked_m, int64_t m, int64_t n, int64_t k, int64_t num_groups,
                        const OptTensor& scratch, const at::Tensor& status, int64_t timeout_ms, const OptTensor& raw_dump,
                        double alpha, int64_t tile_config, int64_t no_split, const OptTensor& stage, int64_t stage_chunk_bytes,
-                       int64_t num_sms, int64_t epilogue) {
+                       int64_t num_sms, int64_t epilogue, const OptTensor& scatter_meta, const OptTensor& scatter_bases) {
   TORCH_CHECK(a.is_cuda(), "a must be a CUDA tensor");
   TORCH_CHECK(b.is_cuda() || b.is_pinned(), "b must be a CUDA tensor or pinned host memory (b.is_cuda() or b.is_pinned())");
   TORCH_CHECK(d.is_cuda() || d.is_pinned(), "d must be a CUDA tensor or pinned host memory");
@@ -65,6 +65,19 @@ void m_grouped_gemm_nt(int64_t kind, int64_t layout, const at::Tensor& a, const 
   }
   desc.status = static_cast<int32_t*>(status.data_ptr());
   desc.epilogue = static_cast<int32_t>(epilogue);
+  const bool has_meta = scatter_meta.has_value() && scatter_meta->defined();
+  const bool has_bases = scatter_bases.has_value() && scatter_bases->defined();
+  TORCH_CHECK(has_meta == has_bases, "scatter_meta and scatter_bases go together");
+  if (has_meta) {
+    TORCH_CHECK(scatter_meta->is_cuda() && scatter_meta->device() == a.device() && scatter_meta->scalar_type() == at::kLong &&
+                    scatter_meta->is_contiguous() && scatter_meta->numel() >= m,
+                "scatter_meta must be a contiguous int64 tensor on a's device with one entry per row of a");
+    TORCH_CHECK(scatter_bases->is_cuda() && scatter_bases->device() == a.device() && scatter_bases->scalar_type() == at::kLong &&
+                    scatter_bases->is_contiguous() && scatter_bases->numel() >= 1,
+                "scatter_bases must be a contiguous int64 tensor of buffer addresses on a's device");
+    desc.scatter_meta = static_cast<const int64_t*>(scatter_meta->data_ptr());
+    desc.scatter_bases = static_cast<const int64_t*>(scatter_bases->data_ptr());
+  }
   desc.num_sms = static_cast<int32_t>(num_sms > 0 ? num_sms : 0);   // 0: every SM, or the process-wide cap
   desc.timeout_ms = static_cast<uint32_t>(timeout_ms);
   desc.raw_dump = static_cast<int32_t*>(ptr_of(raw_dump));
@@ -103,7 +116,7 @@ TORCH_LIBRARY(asymgemm_b200, m) {
       "m_grouped_gemm_nt(int kind, int layout, Tensor a, Tensor? sfa, Tensor b, Tensor? sfb, Tensor(a!) d, Tensor? offsets, "
       "Tensor? experts, int max_segments, Tensor? masked_m, int m, int n, int k, int num_groups, Tensor? scratch, "
       "Tensor status, int timeout_ms, Tensor? raw_dump, float alpha, int tile_config, int no_split, Tensor? stage, int stage_chunk_bytes, "
-      "int num_sms, int epilogue) -> ()");
+      "int num_sms, int epilogue, Tensor? scatter_meta, Tensor? scatter_bases) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(asymgemm_b200, CUDA, m) { m.impl("m_grouped_gemm_nt", &m_grouped_gemm_nt); }

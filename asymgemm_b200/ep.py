@@ -432,7 +432,7 @@ class ExpertParallelMoE:
     def __init__(self, num_experts: int, hidden: int, inter: int, w13, w2, group: Optional[dist.ProcessGroup] = None,
                  expert_ranges: Optional[List[Tuple[int, int]]] = None, ue8m0_scales: bool = False, pipeline_groups: int = 1,
                  comm_sms: int = 24, exchange: str = "nccl", max_tokens: Optional[int] = None, top_k: Optional[int] = None,
-                 fused_activation: bool = False):
+                 fused_activation: bool = False, fused_return: bool = True):
         """`ue8m0_scales`: quantise activations with power-of-two scales and let the tensor core apply all block scales
         (the weights must then have been quantised with use_ue8m0=True); default: arbitrary fp32 scales, applied exactly.
         Whether the kernel reads the pinned weights itself or the copy engine stages them is the operators' setting
@@ -448,8 +448,12 @@ class ExpertParallelMoE:
         `fused_activation`: the gate+up GEMM writes bf16(silu(gate) * up) itself (`epilogue="silu_mul"` of the FP8 operator),
         so the [rows, 2*inter] intermediate is never written; `w13[0]` must then hold the rows of every expert in the
         interleaved order of `interleave_gate_up` (a weight-preparation step; the scales stay as they are). Exact-scale
-        mode only; same output bit for bit."""
+        mode only; same output bit for bit.
+        `fused_return` (peer exchange, more than one rank): the down GEMM's drain stores every result row straight into its
+        pair's slot of the source rank's combine buffer (`scatter` of the FP8 operator) instead of writing a local tensor
+        that a second kernel then sends home; same output bit for bit."""
         self.fused_activation = bool(fused_activation)
+        self.fused_return = bool(fused_return)
         if self.fused_activation and ue8m0_scales:
             raise RuntimeError("fused_activation exists for the exact fp32-scale mode only")
         if exchange not in ("nccl", "peer"):
@@ -501,11 +505,12 @@ class ExpertParallelMoE:
             self.phase_events.append((name, ev))
 
     def experts_forward(self, a_q: torch.Tensor, sfa: torch.Tensor, state: DispatchState, first: int = 0,
-                        count: Optional[int] = None, rows_used: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        count: Optional[int] = None, rows_used: Optional[torch.Tensor] = None, scatter=None) -> torch.Tensor:
         """Both grouped GEMMs over the contiguous layout; returns bf16 [padded_rows, hidden]. `first` / `count`: the local
         experts `state` describes (expert id 0 of its segment table = local expert `first`); default: all of them.
         `rows_used`: device int32 holding how many rows of the layout are in use when only the device knows (the
-        activation kernel then leaves the rest of the buffer alone)."""
+        activation kernel then leaves the rest of the buffer alone). `scatter` = (meta, bases): the down GEMM stores every
+        result row into the buffer and row its entry names (the source ranks' combine buffers) instead of the returned tensor."""
         from . import api
         w13, w2 = self._weights_of(first, self.dispatcher.experts_per_rank if count is None else count)
         m = state.padded_rows
@@ -520,7 +525,7 @@ class ExpertParallelMoE:
             self._mark("gemm_gate_up")
             a2, s2 = moe_ops.quant_rows_fp8(act, rows_used=rows_used)
             self._mark("silu_mul_requant")
-            api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None)
+            api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, scatter=scatter)
             self._mark("gemm_down")
             if self.keep_intermediates:
                 self.intermediates = dict(a_q=a_q, sfa=sfa, act=act, a2=a2, s2=s2, d2=d2, state=state, first=first)
@@ -530,7 +535,7 @@ class ExpertParallelMoE:
         self._mark("gemm_gate_up")
         a2, s2 = moe_ops.silu_mul_quant_fp8(d1, self.inter, pow2_scales=hw, rows_used=rows_used)
         self._mark("silu_mul_requant")
-        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw)
+        api.m_grouped_fp8_asym_gemm_nt_contiguous((a2, s2), w2, d2, state.offsets, state.experts, None, ue8m0_scales=hw, scatter=scatter)
         self._mark("gemm_down")
         if self.keep_intermediates:
             self.intermediates = dict(a_q=a_q, sfa=sfa, d1=d1, a2=a2, s2=s2, d2=d2, state=state, first=first)
@@ -548,7 +553,10 @@ class ExpertParallelMoE:
         a_q = px.a.view(torch.float8_e4m3fn).view(px.cap_rows, self.hidden)
         state = DispatchState(None, [], [], None, None, px.cap_rows, px.offsets, px.experts, tokens, top_k)
         self._mark("layout")
-        out = self.experts_forward(a_q, px.sfa, state, rows_used=px.rows_used[:1])
+        # more than one rank: the down GEMM's drain stores every result row straight into its pair's slot of the source rank's
+        # combine buffer (over NVLink, tile by tile while the GEMM runs); there is no separate return pass
+        direct = px.pair_row is None and self.fused_return
+        out = self.experts_forward(a_q, px.sfa, state, rows_used=px.rows_used[:1], scatter=(px.meta, px.ret_bases) if direct else None)
         if self.prefetch_next is not None and out.is_cuda:      # staged weight path: start the next call's first copies now
             api.prefetch_weights(self.prefetch_next, out.device)
         if px.pair_row is not None:      # one rank: every result already lies in this rank's memory
@@ -556,7 +564,10 @@ class ExpertParallelMoE:
             y = moe_ops.combine_topk(out, px.pair_row, topk_weights, tokens, top_k)
             self._mark("combine")
             return y
-        px.send_back(out)
+        if direct:
+            px.rendezvous()      # every rank's GEMM, and with it every store into this rank's combine buffer, has finished
+        else:
+            px.send_back(out)
         self._mark("return")
         y = moe_ops.combine_topk(px.ret.view(torch.bfloat16).view(px.pairs_cap, self.hidden), None, topk_weights, tokens, top_k)
         self._mark("combine")

@@ -106,6 +106,8 @@ class PeerExchange:
             self.peers.sfa[r] = bases[r] + self._offsets[1]
             self.peers.meta[r] = bases[r] + self._offsets[2]
             self.peers.ret[r] = bases[r] + self._offsets[3]
+        # addresses of every rank's combine buffer, on the device: the down GEMM stores its result rows straight into them
+        self.ret_bases = torch.tensor([int(self.peers.ret[r]) for r in range(self.world)], dtype=torch.int64, device=device)
         arena = torch.as_tensor(_DeviceMemory(self._own, total), device=device)
         self._arena = arena
         self.a = arena[self._offsets[0]: self._offsets[0] + sizes[0]]          # uint8 [cap_rows * row_bytes]

@@ -703,8 +703,8 @@ def measure_ep_layer(args, cfg, rank, world, device, barrier, ranges, link_alone
         "experts_per_rank": [hi - lo for lo, hi in ranges] if ranges is not None else [cfg["experts"] // world] * world,
         "gemm_launches_per_step": 2 * (args.pipeline_groups if world > 1 else 1),
         "exchange": {"nccl": "sort + gather + NCCL all-to-all(v), split sizes read back on the host",
-                     "peer": "this library's kernels: histogram, plan, rows stored into the owner's layout over NVLink peer memory, results "
-                             "stored back the same way; no host synchronisation"}[chosen],
+                     "peer": "this library's kernels: histogram, plan, rows stored into the owner's layout over NVLink peer memory; the down "
+                             "GEMM's drain stores every result row straight into the source rank's combine buffer; no host synchronisation"}[chosen],
     }
     rec["activation"] = ("SiLU*mul fused into the gate+up GEMM's drain (weights stored with gate / up rows interleaved)" if w["fused"]
                          else "separate SiLU*mul + requantisation kernel")

@@ -113,6 +113,18 @@ typedef struct ag_gemm_desc {
      csrc/cpu/module.cpp:337-347): the same bits as the unfused GEMM followed by ag_silu_mul_quant_fp8's activation, without
      the [rows, n] intermediate. n % 256 == 0. */
   int32_t epilogue;
+
+  /* Optional scatter of the result rows (contiguous layout; NULL = rows go to d as usual). With both pointers set, row r of
+     the product is not written to d[r] but to row (scatter_meta[r] & 0xffffffff) of the buffer whose address is
+     scatter_bases[scatter_meta[r] >> 32]; rows whose entry is negative are not written. scatter_meta: device int64 [m];
+     scatter_bases: device array of buffer addresses (as int64), each buffer [*, n] (or [*, n / 2] with the fused epilogue)
+     of d's dtype, 16-byte aligned -- memory of this GPU or of a peer GPU mapped into this process (cudaIpcOpenMemHandle /
+     peer access): the drain then stores every result row straight into its owner's buffer over NVLink, tile by tile while
+     the GEMM runs, and the expert-parallel layer needs no separate return pass (the entries are what ag_ep_dispatch wrote
+     into `meta`: (source rank << 32) | pair). Plain stores only: nothing here loads from a peer. The reference's layers
+     send results back with a collective after the GEMM (asym_gemm/training/ep_vanilla.py:262-282). */
+  const int64_t* scatter_meta;
+  const int64_t* scatter_bases;
 } ag_gemm_desc_t;
 
 /* BF16 x BF16 -> bf16/fp32. Replaces m_grouped_bf16_asym_gemm_nt_contiguous / _masked

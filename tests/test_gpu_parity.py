@@ -641,3 +641,51 @@ def test_two_issuers_keep_the_tensor_core_busy_where_one_does_not():
     assert one >= two - 1.0, (one, two)
     with pytest.raises(RuntimeError, match="issuers must be 1 or 2"):
         probes.mma_issue_cycles(3)
+
+
+@pytest.mark.parametrize("b_on_host", [True, False])
+@pytest.mark.parametrize("fused", [False, True])
+def test_fp8_result_scatter_equals_plain_gemm_plus_row_move(b_on_host, fused):
+    """`scatter=(meta, bases)`: every result row goes to the buffer and row its entry names instead of d[r] (what the
+    expert-parallel layer's down GEMM uses to send results home). Two destination buffers, a random permutation of the
+    valid rows over them, negative entries dropped: the bits of the plain GEMM, moved; nothing else is written."""
+    from asymgemm_b200 import ep
+    rows = [300, 0, 1, 129, 2300, 64]
+    n, k = (768, 640) if fused else (392, 640)
+    c = H.make_contiguous_case("fp8", rows, n, k, seed=95, b_on_host=b_on_host)
+    b = c["b"]
+    if fused:
+        b = ep.interleave_gate_up(b.cuda())
+        b = H.pin(b) if b_on_host else b
+    cols = n // 2 if fused else n
+    kw = dict(epilogue="silu_mul") if fused else {}
+    d = torch.zeros((c["m_total"], cols), dtype=torch.bfloat16, device="cuda")
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (b, c["sfb"]), d, c["offsets"], c["experts"], c["list_size"], **kw)
+    mask = torch.from_numpy(H.valid_row_mask(c["segments"], c["m_total"])).cuda()
+    valid = torch.nonzero(mask).flatten()
+    gen = torch.Generator().manual_seed(7)
+    perm = torch.randperm(valid.numel(), generator=gen).cuda()
+    dropped = perm[:37]                                     # these rows get a negative entry: not stored anywhere
+    bufs = [torch.full((valid.numel(), cols), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    meta = torch.full((c["m_total"],), -1, dtype=torch.int64, device="cuda")
+    which = (torch.arange(valid.numel(), device="cuda") % 2).to(torch.int64)
+    meta[valid[perm]] = (which << 32) | torch.arange(valid.numel(), device="cuda", dtype=torch.int64)
+    meta[valid[dropped]] = -1
+    bases = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64, device="cuda")
+    untouched = torch.full_like(d, float("nan"))
+    ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (b, c["sfb"]), untouched, c["offsets"], c["experts"], c["list_size"],
+                                             scatter=(meta, bases), **kw)
+    ag.check_status()
+    assert torch.isnan(untouched).all()                      # d itself is not written
+    src = valid[perm]
+    for i, buf in enumerate(bufs):
+        sel = (which == i)
+        sel[:37] = False
+        slots = torch.nonzero(sel).flatten()
+        assert torch.equal(buf[slots].view(torch.int16), d[src[slots]].view(torch.int16))
+        rest = torch.ones(valid.numel(), dtype=torch.bool, device="cuda")
+        rest[slots] = False
+        assert torch.isnan(buf[rest]).all()
+    with pytest.raises(RuntimeError, match="scatter"):
+        ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (b, c["sfb"]), untouched, c["offsets"], c["experts"], c["list_size"],
+                                                 scatter=(meta.int(), bases), **kw)

@@ -271,11 +271,11 @@ def test_torch_extension_loads_and_registers_the_launch_op():
     from asymgemm_b200 import _lib
     ops = _lib.torch_ops()
     schema = str(ops.m_grouped_gemm_nt.default._schema)
-    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema and "int num_sms" in schema and "int epilogue" in schema
+    assert "Tensor(a!) d" in schema and "Tensor? stage" in schema and "int stage_chunk_bytes" in schema and "int num_sms" in schema and "int epilogue" in schema and "Tensor? scatter_meta" in schema and "Tensor? scatter_bases" in schema
     z = torch.zeros(4, 4)
     with pytest.raises(NotImplementedError):
         ops.m_grouped_gemm_nt(0, 0, z, None, z, None, z, None, None, 0, None, 4, 4, 4, 1, None,
-                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0, 0, 0)
+                              torch.zeros(1, dtype=torch.int32), 0, None, 1.0, 0, 0, None, 0, 0, 0, None, None)
 
 
 def test_auto_weight_path_rule():
