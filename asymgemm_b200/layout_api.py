@@ -10,6 +10,7 @@ from __future__ import annotations
 from typing import Optional, Tuple
 
 import torch
+from .utils.layout import get_tma_aligned_size as _tma_aligned_size
 
 _state = {"tc_util": 100, "compile_mode": 0}
 
@@ -17,8 +18,7 @@ _state = {"tc_util": 100, "compile_mode": 0}
 def get_tma_aligned_size(x: int, element_size: int) -> int:
     """Smallest count >= x whose byte size is a multiple of 16 (csrc/utils/math.hpp:24-28)."""
     assert 16 % element_size == 0
-    per = 16 // element_size
-    return -(-x // per) * per
+    return _tma_aligned_size(x, element_size)
 
 
 def get_mn_major_tma_aligned_tensor(sf: torch.Tensor) -> torch.Tensor:
