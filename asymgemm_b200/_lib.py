@@ -102,6 +102,7 @@ EXPORTS = [
     "ag_link_probe_destroy",
     "ag_selftest_wait_limit",
     "ag_probe_mma_issue",
+    "ag_probe_operand_feed",
     "ag_quant_rows_fp8",
     "ag_silu_mul_quant_fp8",
     "ag_silu_mul_quant_fp8_upto",
@@ -207,6 +208,8 @@ def load() -> ctypes.CDLL:
     lib.ag_selftest_wait_limit.restype = c_int32
     lib.ag_probe_mma_issue.argtypes = [c_int32, c_int32, c_int32, ctypes.POINTER(ctypes.c_double)]
     lib.ag_probe_mma_issue.restype = c_int32
+    lib.ag_probe_operand_feed.argtypes = [c_int32, c_int32, ctypes.POINTER(ctypes.c_double)]
+    lib.ag_probe_operand_feed.restype = c_int32
     lib.ag_prefetch_staged_weights.argtypes = [c_void_p, c_uint64, c_int32, c_void_p, c_uint64, c_uint64, c_void_p, c_int32]
     lib.ag_prefetch_staged_weights.restype = c_int32
     lib.ag_prepare_weights.argtypes = [c_void_p, c_uint64, c_int32]

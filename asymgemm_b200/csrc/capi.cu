@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/asymgemm_b200.h"
 #include "launch.cuh"
@@ -628,3 +629,55 @@ const char* ag_last_error(void) { return g_err; }
 const char* ag_version(void) { return "asymgemm_b200 0.1 (sm_100a)"; }
 
 }  // extern "C"
+
+namespace agb {
+cudaError_t launch_operand_feed_probe(const CUtensorMap& ma, const CUtensorMap& mb, int sms, int items, int kb_count, int load_a, int load_b,
+                                      int rows_a, int rows_b, long long* cycles, int* failed);
+}
+
+extern "C" int ag_probe_operand_feed(int32_t load_a, int32_t load_b, double* cycles_per_k_atom) {
+  AG_REQUIRE(cycles_per_k_atom != nullptr, "cycles_per_k_atom is NULL");
+  int sms = 0;
+  if (int rc = device_sm_count(&sms)) return rc;
+  constexpr int kRowBytes = 4096, kRowsA = 65536, kRowsB = 128 * 1536, kItems = 12, kAtoms = 32;   // 256 MB + 768 MB
+  void *a = nullptr, *b = nullptr;
+  long long* cycles = nullptr;
+  int* failed = nullptr;
+  std::vector<long long> host(2 * static_cast<size_t>(sms), 0);
+  int host_failed = 0, rc = AG_OK;
+  cudaError_t e = cudaMalloc(&a, static_cast<size_t>(kRowsA) * kRowBytes);
+  if (e == cudaSuccess) e = cudaMalloc(&b, static_cast<size_t>(kRowsB) * kRowBytes);
+  if (e == cudaSuccess) e = cudaMalloc(&cycles, sizeof(long long) * 2 * sms);
+  if (e == cudaSuccess) e = cudaMalloc(&failed, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(a, 0, static_cast<size_t>(kRowsA) * kRowBytes);
+  if (e == cudaSuccess) e = cudaMemset(b, 0, static_cast<size_t>(kRowsB) * kRowBytes);
+  if (e == cudaSuccess) e = cudaMemset(cycles, 0, sizeof(long long) * 2 * sms);
+  if (e == cudaSuccess) e = cudaMemset(failed, 0, sizeof(int));
+  if (e == cudaSuccess) {
+    CUtensorMap ma, mb;
+    rc = encode_bytes_2d(&ma, a, kRowBytes, kRowsA, kRowBytes, 128, "probe a");
+    if (rc == AG_OK) rc = encode_bytes_2d(&mb, b, kRowBytes, kRowsB, kRowBytes, 256, "probe b");
+    if (rc == AG_OK) {
+      for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second pass finds the tensor maps and L2 warm
+        e = agb::launch_operand_feed_probe(ma, mb, sms, kItems, kAtoms, load_a != 0, load_b != 0, kRowsA, kRowsB, cycles, failed);
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+      }
+      if (e == cudaSuccess) e = cudaMemcpy(host.data(), cycles, sizeof(long long) * 2 * sms, cudaMemcpyDeviceToHost);
+      if (e == cudaSuccess) e = cudaMemcpy(&host_failed, failed, sizeof(int), cudaMemcpyDeviceToHost);
+    }
+  }
+  cudaFree(a);
+  cudaFree(b);
+  cudaFree(cycles);
+  cudaFree(failed);
+  if (rc != AG_OK) return rc;
+  if (e != cudaSuccess) return fail(AG_E_CUDA, "operand-feed probe: %s", cudaGetErrorString(e));
+  long long worst = 0;
+  for (long long c : host) {
+    if (c < 0) host_failed = 1;
+    worst = c > worst ? c : worst;
+  }
+  if (host_failed) return fail(AG_E_DEVICE, "the operand-feed probe gave up waiting on one of its barriers");
+  *cycles_per_k_atom = static_cast<double>(worst) / (static_cast<double>(kItems) * kAtoms);
+  return AG_OK;
+}

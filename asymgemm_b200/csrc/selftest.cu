@@ -95,6 +95,121 @@ __global__ void __launch_bounds__(128, 1) mma_issue_probe_kernel(int steps, int 
   if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Operand-feed probe: the kernels' producer / issuer rings for 256-column bf16 items -- per 128-byte K atom one 256-row weight
+// stage (32 KB) and two 128-row activation stages (16 KB each), two issuers with one row tile each, one producer lane per
+// issuer -- with REAL TMA loads from device memory and nothing else (no drain, no item bookkeeping). Groups of six CTAs
+// share activation rows and every sixth CTA shares weight rows, as CTAs of the grouped GEMM do through L2.
+__global__ void __launch_bounds__(128, 1) operand_feed_probe_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                                                     int items, int kb_count, int load_a, int load_b, int rows_a, int rows_b,
+                                                                     long long* cycles, int* failed) {
+  constexpr int SB = 4, PER = 2;   // weight ring; activation stages per issuer
+  extern __shared__ uint8_t probe_smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(probe_smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + 2 * PER * 16384;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b + SB * 32768);
+  uint64_t* a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 12, *done = bars + 16;
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 24);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&a_full[i], 1);
+      mbar_init(&a_empty[i], 1);
+      mbar_init(&b_full[i], 1);
+      mbar_init(&b_empty[i], 2);
+    }
+    mbar_init(&done[0], 1);
+    mbar_init(&done[1], 1);
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_base_smem, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_smem;
+  auto spin = [&](uint64_t* bar, uint32_t parity) {        // bounded: about a second at the most
+    for (uint32_t n = 0; n < (1u << 24); ++n)
+      if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(failed, 1);
+    return false;
+  };
+  if (warp == 0 && lane == 0) {                               // weight producer
+    bool ok = true;
+    uint32_t jt = 0;
+    for (int it = 0; it < items && ok; ++it) {
+      const int b_row = ((it * 7 + static_cast<int>(blockIdx.x) % 6) % (rows_b / 256)) * 256;
+      for (int kb = 0; kb < kb_count && ok; ++kb, ++jt) {
+        const uint32_t s = jt % SB;
+        ok = spin(&b_empty[s], ((jt / SB) & 1) ^ 1);
+        if (!ok) break;
+        if (load_b) {
+          mbar_arrive_expect_tx(&b_full[s], 32768);
+          tma_load_2d(smem_b + s * 32768, &tmap_b, &b_full[s], kb * ATOM_BYTES, b_row);
+        } else {
+          mbar_arrive(&b_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1 && lane < 2) {                         // activation producers, one lane per issuer
+    const int t = lane;
+    bool ok = true;
+    uint32_t used = 0;
+    for (int it = 0; it < items && ok; ++it) {
+      const int a_row = ((it * 25 + static_cast<int>(blockIdx.x) / 6) % (rows_a / 256)) * 256 + t * 128;
+      for (int kb = 0; kb < kb_count && ok; ++kb, ++used) {
+        const uint32_t s = t * PER + used % PER;
+        ok = spin(&a_empty[s], ((used / PER) & 1) ^ 1);
+        if (!ok) break;
+        if (load_a) {
+          mbar_arrive_expect_tx(&a_full[s], 16384);
+          tma_load_2d(smem_a + s * 16384, &tmap_a, &a_full[s], kb * ATOM_BYTES, a_row);
+        } else {
+          mbar_arrive(&a_full[s]);
+        }
+      }
+    }
+  } else if ((warp == 2 || warp == 3) && lane == 0) {        // issuers: row tile 0 and row tile 1
+    const int t = warp - 2;
+    const uint32_t idesc = make_idesc(1, 1, 256);
+    const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_u32(smem_a)), b_desc0 = make_kmajor_sw128_desc(smem_u32(smem_b));
+    const long long t0 = clock64();
+    bool ok = true;
+    uint32_t own = 0, jt = 0;
+    for (int it = 0; it < items && ok; ++it) {
+      for (int kb = 0; kb < kb_count && ok; ++kb, ++jt, ++own) {
+        const uint32_t sb = jt % SB, sa = t * PER + own % PER;
+        ok = spin(&b_full[sb], (jt / SB) & 1) && spin(&a_full[sa], (own / PER) & 1);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t da = a_desc0 + static_cast<uint64_t>((sa * 16384) >> 4), db = b_desc0 + static_cast<uint64_t>((sb * 32768) >> 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma<MmaKind::F16>(tmem_base + t * 256, da + static_cast<uint64_t>(j * 2), db + static_cast<uint64_t>(j * 2), idesc, (kb > 0 || j > 0));
+        umma_commit(&a_empty[sa]);
+        umma_commit(&b_empty[sb]);
+      }
+    }
+    umma_commit(&done[t]);
+    if (ok) ok = spin(&done[t], 0);
+    cycles[blockIdx.x * 2 + t] = ok ? clock64() - t0 : -1;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+cudaError_t launch_operand_feed_probe(const CUtensorMap& ma, const CUtensorMap& mb, int sms, int items, int kb_count, int load_a, int load_b,
+                                      int rows_a, int rows_b, long long* cycles, int* failed) {
+  const size_t smem_bytes = 4 * 16384 + 4 * 32768 + 512 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(operand_feed_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+  if (e != cudaSuccess) return e;
+  operand_feed_probe_kernel<<<sms, 128, smem_bytes>>>(ma, mb, items, kb_count, load_a, load_b, rows_a, rows_b, cycles, failed);
+  return cudaGetLastError();
+}
+
 }  // namespace agb
 
 extern "C" int ag_probe_mma_issue(int32_t issuers, int32_t n_cols, int32_t steps, double* cycles_per_step) {

@@ -347,6 +347,15 @@ int ag_selftest_wait_limit(uint32_t timeout_ms, int32_t* status, void* stream);
  * two MMA-issuing threads of the kernels. */
 int ag_probe_mma_issue(int32_t issuers, int32_t n_cols, int32_t steps, double* cycles_per_step);
 
+/* Operand-feed probe, on every SM of the current device: the kernels' producer / issuer rings for 256-column bf16 items (per
+ * 128-byte K atom one 256-row weight stage and two 128-row activation stages, two issuers) with real TMA loads from device
+ * memory (load_a / load_b != 0 switch the loads of the two operands on) and nothing else: no drain, no item bookkeeping.
+ * Groups of six CTAs share activation rows and every sixth CTA shares weight rows, as CTAs of the grouped GEMM do through
+ * L2. *cycles_per_k_atom = SM cycles per K atom (two steps of four MMAs), worst CTA; the tensor core's own time is 1024.
+ * Allocates 1 GB of device memory for the operands and frees it before it returns; synchronous; every wait is bounded.
+ * Reference counterpart: none. */
+int ag_probe_operand_feed(int32_t load_a, int32_t load_b, double* cycles_per_k_atom);
+
 /* Copy-only ceiling for SM-issued reads of pinned memory: streams a `bytes` pinned buffer laid out as rows of `row_bytes`
  * through shared memory with the weight producer's TMA pattern (each CTA owns columns of `box_rows` rows and walks K in
  * 128-byte boxes, `boxes_per_stage` per stage) on `num_ctas` CTAs (0 = all SMs), best of `reps`. Reference counterpart:

@@ -689,3 +689,12 @@ def test_fp8_result_scatter_equals_plain_gemm_plus_row_move(b_on_host, fused):
     with pytest.raises(RuntimeError, match="scatter"):
         ag.m_grouped_fp8_asym_gemm_nt_contiguous((c["a"], c["sfa"]), (b, c["sfb"]), untouched, c["offsets"], c["experts"], c["list_size"],
                                                  scatter=(meta.int(), bases), **kw)
+
+
+def test_operand_feed_probe_runs_and_loads_cost_cycles():
+    """The operand-feed probe (the kernels' rings with real TMA loads and nothing else): without loads it runs close to
+    the tensor core's 1024 cycles per K atom; with both operands loaded it cannot be faster than without."""
+    from asymgemm_b200.testing import probes
+    none, both = probes.operand_feed_cycles(False, False), probes.operand_feed_cycles(True, True)
+    assert 1000.0 <= none <= 1250.0, (none, both)
+    assert both >= none - 5.0 and both < 4000.0, (none, both)
