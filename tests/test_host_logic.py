@@ -364,3 +364,27 @@ def test_expert_range_and_layout_invariants_random():
                     seen[j] += 1
                     pos += 1
         assert seen == per_expert.tolist()
+
+
+def test_documented_ctypes_mirror_matches_the_library():
+    """The ctypes stub printed in INTEGRATION.md (for hosts without this package) is executed as written: its structure must
+    have the size the library reports for ag_gemm_desc_t, and the documented op call must name as many arguments as the
+    registered schema has."""
+    import ctypes
+    import re
+    from pathlib import Path
+    from asymgemm_b200 import _lib
+    text = (Path(__file__).resolve().parents[1] / "INTEGRATION.md").read_text()
+    m = re.search(r"class Desc\(ctypes\.Structure\):.*?\n(    _fields_ = \[.*?\]\n)", text, re.S)
+    assert m, "the ctypes stub is missing from INTEGRATION.md"
+    ns = {}
+    exec("import ctypes\nclass Desc(ctypes.Structure):\n" + m.group(1), ns)
+    lib = _lib.load()
+    lib.ag_gemm_desc_size.restype = ctypes.c_uint64
+    assert lib.ag_gemm_desc_size() == ctypes.sizeof(ns["Desc"]) == ctypes.sizeof(_lib.GemmDesc)
+    call = re.search(r"m_grouped_gemm_nt\((kind, layout.*?)\)\n", text, re.S)
+    assert call, "the op call is missing from INTEGRATION.md"
+    documented = [a.strip() for a in call.group(1).replace("\n", " ").split(",") if a.strip()]
+    schema = str(_lib.torch_ops().m_grouped_gemm_nt.default._schema)
+    registered = schema[schema.index("(") + 1: schema.rindex(") ->")].split(",")
+    assert len(documented) == len(registered) == 28, (len(documented), len(registered))
