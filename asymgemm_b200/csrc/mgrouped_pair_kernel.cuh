@@ -103,7 +103,7 @@ struct PairSmem {
   static constexpr int work_off = misc_off + 16;                  // work list (build_work_list): 1024 segments, 512 items
   static constexpr int seg_cap = 1024, item_cap = 512;
   static constexpr int seg_first_off = work_off + seg_cap * 12;
-  static constexpr int items_off = (seg_first_off + (seg_cap + 2) * 4 + 15) / 16 * 16;
+  static constexpr int items_off = (seg_first_off + (2 * seg_cap + 2) * 4 + 15) / 16 * 16;
   static constexpr int total = items_off + item_cap * 16;
   static constexpr int dyn_bytes = total + 1024;
 };
